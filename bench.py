@@ -1,0 +1,381 @@
+"""Benchmark of the LSH attention-memory hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
+
+One "step" = one pass of the query path over one batch of synthetic queries: query hashing, grouping by
+bucket, hashed attention over the indexed memory and (where the workload has a local window) the LSE merge
+with the local attention result.  ``value`` = queries/s with inputs resident in HBM; ``e2e`` = the same
+through the public API with the queries copied from pinned host memory and the result copied back inside
+the timed region.  The index build (projection + top-Z) is timed separately (``index_build``).
+
+Multi-GPU: heads (and whole memories) are independent, so under torchrun every rank serves its own memory
+of the same shape (weak scaling, no data-path collective); ``value`` is the sum over ranks divided by the
+slowest rank's time.
+
+``--impl reference`` times the CPU port of the reference algorithm (``oracle/``) on the host cores on a
+bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch
+
+METRIC = "hashed_attn_queries_per_s"
+UNIT = "queries/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()            # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+        return False
+
+    def summary(self):
+        rows = [s for s in self.samples if len(s) >= 7 and s[0].isdigit()]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        reasons = set()
+        for s in rows:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(int(s[0]) for s in rows), "sm_max_mhz": int(rows[0][1]),
+                "reasons": sorted(reasons), "samples": len(rows)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# workload
+# ---------------------------------------------------------------------------------------------------
+def dense_local_window(q, k, v, sm_scale, window):
+    """Stock-PyTorch causal sliding-window attention with LSE over the local keys (set-up, untimed): plays the
+    part of the reference's ``attention_forward`` (memory.py:302)."""
+    H, S, d = q.shape
+    o = torch.empty(H, S, d, dtype=torch.float32, device=q.device)
+    lse = torch.empty(H, S, dtype=torch.float32, device=q.device)
+    i = torch.arange(S, device=q.device)[:, None]
+    j = torch.arange(S, device=q.device)[None, :]
+    mask = (j <= i) & (j > i - window)
+    for h in range(H):
+        s = (q[h].float() @ k[h].float().T) * sm_scale
+        s.masked_fill_(~mask, float("-inf"))
+        lse[h] = torch.logsumexp(s, -1)
+        o[h] = torch.softmax(s, -1) @ v[h].float()
+    return o, lse
+
+
+def algorithmic_attention_bytes(mem, group_off, d, esize):
+    """Bytes the attention kernel has to move: per NON-EMPTY (bucket, queries) group one index + K row +
+    V row per slot, per query the q row, the o row, the hash and the LSE."""
+    nq = (group_off[1:] - group_off[:-1]).to(torch.int64)
+    blen = (mem.bucket_off[1:] - mem.bucket_off[:-1])
+    per_group = blen * (4 + 2 * d * esize)
+    return int((per_group * (nq > 0)).sum().item() + nq.sum().item() * (2 * d * esize + 8)), int((nq > 0).sum().item())
+
+
+def run_ours(args, rank, world):
+    import fast_memory_b200 as fm
+    from fast_memory_b200 import ops, synth
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    cfg = synth.config(args.workload)
+    sm_scale = cfg.d ** -0.5
+    esize = 2 if cfg.dtype != torch.float32 else 4
+    q, k, v = synth.make(cfg, seed=args.seed + rank, device=dev)
+    Hq, S, d = q.shape
+    n_queries = Hq * S
+    local = None
+    if cfg.local_window:
+        _, k_self, v_self = synth.make(cfg, seed=args.seed + 7919 + rank, device=dev, n_keys=S)
+        local = dense_local_window(q, k_self, v_self, sm_scale, cfg.local_window)
+        del k_self, v_self
+
+    # ---- index build (k-means projection once, then the timed projection + top-Z) ------------------
+    kf = k.reshape(-1, d)
+    H, N = k.shape[0], k.shape[1]
+    seg_kb = [h * N for h in range(H + 1)]
+    seg_cb = [h * cfg.n_buckets for h in range(H + 1)]
+    init = q.reshape(H, -1, d)[:, :cfg.n_buckets].reshape(-1, d) if q.shape[1] * cfg.q_groups >= cfg.n_buckets else \
+        k[:, :cfg.n_buckets].reshape(-1, d)
+    A, _ = fm.kmeans_projection(kf, init.contiguous(), cfg.kmeans_iters, seg_kb, seg_cb)
+    A = A.reshape(H, cfg.n_buckets, d)
+    torch.cuda.synchronize()
+    build_ms = []
+    for it in range(args.build_steps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        mem = fm.Memory.build(k, v, A=A, bucket_size=cfg.bucket_size)
+        e1.record()
+        torch.cuda.synchronize()
+        if it > 0 or args.build_steps == 0:
+            build_ms.append(e0.elapsed_time(e1))
+
+    # ---- query path -----------------------------------------------------------------------------
+    out_acc = torch.empty(Hq, S, d, dtype=torch.float32, device=dev) if local is not None else None
+    lse_acc = torch.empty(Hq, S, dtype=torch.float32, device=dev) if local is not None else None
+
+    def step(qd):
+        o, lse = mem.query(qd, sm_scale)
+        if local is not None:
+            out_acc.copy_(local[0])
+            lse_acc.copy_(local[1])
+            ops.lse_merge(out_acc, lse_acc, o, lse)
+            return out_acc, lse_acc
+        return o, lse
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(q)
+    barrier()
+    launches0 = fm.launch_count()
+    with ClockSampler(dev.index or 0) as clocks:
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            step(q)
+        t1.record()
+        barrier()
+        step_ms = t0.elapsed_time(t1) / args.steps
+    launches = fm.launch_count() - launches0
+
+    # ---- the dominant kernel alone (hashed attention), for the roofline -------------------------------
+    qf = q.reshape(-1, d)
+    seg_xb, max_rows = mem._query_segments(Hq, S, None, dev)
+    hashes = ops.hash_rows(qf, mem.A, seg_xb, mem._seg_cb_dev, max_rows)
+    group_off, perm = ops.group_rows(hashes, mem.total_buckets, seg_xb, mem._seg_cb_dev)
+    o_buf, l_buf = torch.empty_like(qf), torch.empty(qf.shape[0], dtype=torch.float32, device=dev)
+    kk, vv = k.reshape(-1, d), v.reshape(-1, d)
+    attn = lambda: ops.hashed_attention(qf, kk, vv, mem.table, mem.bucket_off, group_off, perm, sm_scale,
+                                        mem.max_bucket_len, out=o_buf, lse=l_buf)
+    for _ in range(3):
+        attn()
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for _ in range(args.steps):
+        attn()
+    a1.record()
+    torch.cuda.synchronize()
+    attn_ms = a0.elapsed_time(a1) / args.steps
+    attn_bytes, n_groups = algorithmic_attention_bytes(mem, group_off, d, esize)
+
+    # ---- end to end: pinned host queries in, result out, inside the timed region ------------------------
+    q_host = q.cpu().pin_memory()
+    o_host = torch.empty(Hq, S, d, dtype=cfg.dtype).pin_memory()
+    l_host = torch.empty(Hq, S, dtype=torch.float32).pin_memory()
+    q_dev = torch.empty_like(q)
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        o, lse = step(q_dev)
+        o_host.copy_(o.to(cfg.dtype) if o.dtype != cfg.dtype else o, non_blocking=True)
+        l_host.copy_(lse, non_blocking=True)
+
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+
+    if world > 1:
+        t = torch.tensor([step_ms, e2e_ms, statistics.median(build_ms)], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        step_ms, e2e_ms, build_med = t.tolist()
+    else:
+        build_med = statistics.median(build_ms)
+    if rank != 0:
+        return None
+
+    peaks = measured_peaks()
+    achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+    build_flops = 2.0 * cfg.n_buckets * N * d * H
+    res = {
+        "metric": METRIC, "value": world * n_queries / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if cfg.dtype == torch.bfloat16 else str(cfg.dtype).replace("torch.", ""),
+        "data": "synthetic",
+        "config": {"workload": f"{cfg.name}: {H} KV heads x {cfg.q_groups} groups, d={d}, N={N} keys/head, C={cfg.n_buckets}, "
+                               f"Z={cfg.bucket_size}, {S} queries/head" + (f", merged with a causal local window of {cfg.local_window}" if cfg.local_window else ""),
+                   "parallelism": f"independent memories per GPU x{world}" if world > 1 else "single GPU",
+                   "l2": f"inputs larger than L2 ({attn_bytes / 1e9:.2f} GB gathered per step)",
+                   "non_empty_groups": n_groups},
+        "clocks": clocks.summary(),
+        "e2e": {"value": world * n_queries / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": q_host.numel() * q_host.element_size(),
+                "d2h_bytes_per_step": o_host.numel() * o_host.element_size() + l_host.numel() * 4},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "hashed attention forward", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                     "traffic": None, "algorithmic_bytes": attn_bytes, "ms_per_launch": attn_ms},
+        "index_build": {"metric": "index_build_keys_per_s", "value": world * H * N / (build_med * 1e-3), "unit": "keys/s",
+                        "ms": build_med, "tflops": build_flops / (build_med * 1e-3) / 1e12,
+                        "frac_of_tensor_peak": build_flops / (build_med * 1e-3) / 1e12 / peaks["bf16_tflops"]},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        res["cpu_baseline"] = cpu_baseline(cfg, args.seed, target_s=args.cpu_seconds)
+    return res
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference algorithm on the host cores
+# ---------------------------------------------------------------------------------------------------
+def cpu_query_pass(O, cfg, A, table, q, k, v, local, sm_scale):
+    """hash + hashed attention (+ merge) for one KV head on the CPU; returns the number of queries served."""
+    H, C = 1, cfg.n_buckets
+    hashes = torch.from_numpy(O.query_hash(A, q)).long()
+    counts = torch.full((H, C), table.shape[-1])
+    o, lse = O.hashed_attention(q, k, v, table.reshape(-1), counts, hashes, sm_scale)
+    if local is not None:
+        O.update_out_and_lse(local[0], local[1].unsqueeze(-1), o, lse)
+    return q.shape[0] * q.shape[1]
+
+
+def cpu_sample(cfg, seed, n_queries):
+    """One KV head of the workload with a bounded number of queries (same distributions, C, Z, N)."""
+    from fast_memory_b200 import synth
+    from oracle import oracle as O
+    q, k, v = synth.make(cfg, seed=seed, kv_heads=1, n_queries=max(n_queries // cfg.q_groups, 1))
+    q = q.reshape(1, -1, cfg.d)
+    A = O.spherical_kmeans(k[0], (q[0] if q.shape[1] >= cfg.n_buckets else k[0])[:cfg.n_buckets], cfg.kmeans_iters)[None]
+    table = torch.from_numpy(O.build_table(A, k, cfg.bucket_size)).long()
+    local = None
+    if cfg.local_window:
+        local = (torch.zeros(1, q.shape[1], cfg.d), torch.zeros(1, q.shape[1]))
+    return O, A, table, q, k, v, local
+
+
+def cpu_baseline(cfg, seed, target_s=15.0):
+    torch.set_num_threads(os.cpu_count() or 1)
+    n_q = min(cfg.n_queries * cfg.q_groups, 8192)
+    O, A, table, q, k, v, local = cpu_sample(cfg, seed, n_q)
+    sm_scale = cfg.d ** -0.5
+    cpu_query_pass(O, cfg, A, table, q[:, :64], k, v, None, sm_scale)              # warm-up
+    t0 = time.perf_counter()
+    served, reps = 0, 0
+    while time.perf_counter() - t0 < target_s and reps < 64:
+        served += cpu_query_pass(O, cfg, A, table, q, k, v, local, sm_scale)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return {"value": served / dt, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": f"1 of {cfg.kv_heads} KV heads, {q.shape[1]} queries x {reps} passes over the full-size index "
+                      f"(N={k.shape[1]}, C={cfg.n_buckets}, Z={cfg.bucket_size}); oracle port (C + torch, all host threads)"}
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the CPU port of the reference's path on the host cores, rank 0 only."""
+    if rank != 0:
+        return None
+    from fast_memory_b200 import synth
+    cfg = synth.config(args.workload)
+    torch.set_num_threads(os.cpu_count() or 1)
+    n_q = min(cfg.n_queries * cfg.q_groups, 8192)
+    O, A, table, q, k, v, local = cpu_sample(cfg, args.seed, n_q)
+    sm_scale = cfg.d ** -0.5
+    for _ in range(args.warmup):
+        cpu_query_pass(O, cfg, A, table, q[:, :128], k, v, None, sm_scale)
+    t0 = time.perf_counter()
+    served = 0
+    for _ in range(args.steps):
+        served += cpu_query_pass(O, cfg, A, table, q, k, v, local, sm_scale)
+    dt = time.perf_counter() - t0
+    val = served / dt
+    sample = (f"each step = 1 of {cfg.kv_heads} KV heads, {q.shape[1]} queries over the full-size index "
+              f"(N={k.shape[1]}, C={cfg.n_buckets}, Z={cfg.bucket_size})")
+    return {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16" if cfg.dtype == torch.bfloat16 else "float32", "data": "synthetic",
+            "config": {"workload": f"{cfg.name} (CPU port of the reference path, bounded sample)", "sample": sample},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--build-steps", type=int, default=2)
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        res = run_reference(args, rank, world)
+    else:
+        if world > 1:
+            torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
+        res = run_ours(args, rank, world)
+        if world > 1:
+            torch.distributed.destroy_process_group()
+    if res is not None:
+        print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

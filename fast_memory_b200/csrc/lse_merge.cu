@@ -1,0 +1,97 @@
+// LSE merge of two partial attention results, in place on fp32 accumulators.
+// Stands in for update_out_and_lse of the reference (memory.py:54-71):
+//     d = blk_lse - lse;  out -= sigmoid(d) * (out - blk_out);  lse -= logsigmoid(-d)
+// i.e. lse <- log(e^lse + e^blk_lse) and out <- the convex combination weighted by e^lse, e^blk_lse.
+#include "common.cuh"
+
+namespace fm {
+
+template <typename T> __device__ __forceinline__ float load_as_f32(const void *p, size_t i)
+{
+    return Elem<T>::to_f32(reinterpret_cast<const T *>(p)[i]);
+}
+
+__device__ __forceinline__ float load_lse(const void *p, int dtype, size_t i)
+{
+    if (dtype == FM_F32) return reinterpret_cast<const float *>(p)[i];
+    if (dtype == FM_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
+    return __half2float(reinterpret_cast<const __half *>(p)[i]);
+}
+
+// One warp per row; lanes stride the head dim in 16-byte pieces.  HBM-bound: per row it moves
+// d * (8 + sizeof(T)) + 12 bytes.
+template <typename T>
+__global__ void __launch_bounds__(256)
+lse_merge_kernel(float *__restrict__ out, float *__restrict__ lse, const T *__restrict__ blk_out,
+                 const void *__restrict__ blk_lse, int lse_dtype, int64_t n_rows, int d)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = int64_t(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t r = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n_rows; r += warps) {
+        const float a = lse[r];
+        const float b = load_lse(blk_lse, lse_dtype, r);
+        // weight of the block: sigmoid(b - a); new lse: a + softplus(b - a).  -inf on a side = weight 0.
+        float w, nl;
+        if (b == -INFINITY) { w = 0.f; nl = a; }
+        else if (a == -INFINITY) { w = 1.f; nl = b; }
+        else {
+            const float dlt = b - a;
+            w = 1.f / (1.f + expf(-dlt));
+            nl = a + (dlt > 0.f ? dlt + log1pf(expf(-dlt)) : log1pf(expf(dlt)));
+        }
+        float *orow = out + r * d;
+        const T *brow = blk_out + r * d;
+        for (int c = lane * 4; c < d; c += 128) {
+            float4 o4 = *reinterpret_cast<const float4 *>(orow + c);
+            float b0, b1, b2, b3;
+            if constexpr (sizeof(T) == 4) {
+                float4 b4 = *reinterpret_cast<const float4 *>(brow + c);
+                b0 = b4.x; b1 = b4.y; b2 = b4.z; b3 = b4.w;
+            } else {
+                uint2 raw = *reinterpret_cast<const uint2 *>(brow + c);
+                const T *h = reinterpret_cast<const T *>(&raw);
+                b0 = Elem<T>::to_f32(h[0]); b1 = Elem<T>::to_f32(h[1]);
+                b2 = Elem<T>::to_f32(h[2]); b3 = Elem<T>::to_f32(h[3]);
+            }
+            o4.x -= w * (o4.x - b0);
+            o4.y -= w * (o4.y - b1);
+            o4.z -= w * (o4.z - b2);
+            o4.w -= w * (o4.w - b3);
+            *reinterpret_cast<float4 *>(orow + c) = o4;
+        }
+        if (lane == 0) lse[r] = nl;
+    }
+}
+
+}  // namespace fm
+
+extern "C" int fm_lse_merge(float *out, float *lse, const void *blk_out, int blk_dtype, const void *blk_lse,
+                            int lse_dtype, int64_t n_rows, int d, fm_stream_t stream)
+{
+    using namespace fm;
+    FM_REQUIRE(n_rows >= 0 && d > 0, "fm_lse_merge: bad sizes");
+    if (n_rows == 0) return FM_OK;
+    FM_REQUIRE(out && lse && blk_out && blk_lse, "fm_lse_merge: null pointer");
+    FM_REQUIRE(d % 4 == 0, "fm_lse_merge: head dim must be a multiple of 4");
+    FM_REQUIRE(((uintptr_t)out) % 16 == 0 && ((uintptr_t)blk_out) % 8 == 0, "fm_lse_merge: misaligned buffer");
+    if (lse_dtype != FM_F32 && lse_dtype != FM_BF16 && lse_dtype != FM_F16) {
+        set_error("fm_lse_merge: unknown lse dtype %d", lse_dtype);
+        return FM_ERR_UNSUPPORTED;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    int blocks = (int)std::min<int64_t>(ceil_div(n_rows, 8), int64_t(sm_count()) * 8);
+    switch (blk_dtype) {
+    case FM_F32:
+        lse_merge_kernel<float><<<blocks, 256, 0, st>>>(out, lse, (const float *)blk_out, blk_lse, lse_dtype, n_rows, d);
+        break;
+    case FM_BF16:
+        lse_merge_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(out, lse, (const __nv_bfloat16 *)blk_out, blk_lse, lse_dtype, n_rows, d);
+        break;
+    case FM_F16:
+        lse_merge_kernel<__half><<<blocks, 256, 0, st>>>(out, lse, (const __half *)blk_out, blk_lse, lse_dtype, n_rows, d);
+        break;
+    default: set_error("fm_lse_merge: unknown dtype %d", blk_dtype); return FM_ERR_UNSUPPORTED;
+    }
+    FM_LAUNCHED("lse_merge_kernel");
+    return FM_OK;
+}

@@ -1,0 +1,282 @@
+"""The memory module: build an LSH index over past keys/values, query it, get (O, LSE) back for merging.
+
+The reference describes this object (README.md:7) but ships it only as loose steps inside its training
+code (mem:252-283 build + hash, mem:319-332 attend + merge).  :class:`Memory` packages those steps:
+
+    mem = Memory.build(k, v, n_buckets=512, bucket_size=2048, kmeans_iters=2, kmeans_init=q)
+    o, lse = mem.query(q, sm_scale)            # o in q's dtype, lse fp32 natural log
+    out, lse = merge(o_local, lse_local, o, lse)
+
+Layout.  ``k`` / ``v`` are ``[H, N, d]`` (H = KV heads) or, for packed variable-length memories,
+``[H, N_total, d]`` with ``cu_seqlens_k``; one SEGMENT per (head, sequence).  Segment s owns buckets
+``seg_cb[s]:seg_cb[s+1]`` of the packed projection matrix ``A [total_buckets, d]`` and a slice of the flat
+bucket table of ABSOLUTE key rows (ascending inside a bucket).  Queries ``[Hq, S, d]`` with Hq a multiple
+of H fold their GQA group into the query axis (as mem:134 does).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple, Union
+
+import torch
+
+from . import _lib as L
+from . import ops
+
+IntOrSeq = Union[int, Sequence[int]]
+
+
+def _per_seq(val: IntOrSeq, n_seq: int, name: str) -> List[int]:
+    if isinstance(val, int):
+        return [val] * n_seq
+    vals = [int(x) for x in val]
+    if len(vals) != n_seq:
+        raise ValueError(f"{name}: expected {n_seq} entries, got {len(vals)}")
+    return vals
+
+
+def kmeans_projection(x: torch.Tensor, init: torch.Tensor, iters: int, seg_xb: Sequence[int],
+                      seg_cb: Sequence[int]) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Spherical k-means per segment (README.md:37-45).
+
+    x ``[rows, d]``; ``init [total_buckets, d]`` initial centroids (any scale, normalised here);
+    ``seg_xb`` / ``seg_cb``: python prefix lists.  Returns (A in x's dtype, fp32 centroids).
+    """
+    dev = L.require_cuda(x, init)
+    d = x.shape[1]
+    cent = ops.unit_rows(init.to(x.dtype).contiguous())
+    A = torch.empty(cent.shape, dtype=x.dtype, device=dev)
+    n_seg = len(seg_xb) - 1
+    xb, cb = L.host_i64(seg_xb), L.host_i64(seg_cb)
+    need = L.lib().fm_kmeans_workspace_bytes(n_seg, xb, cb, d)
+    ws = ops._ws.get("kmeans", need, dev)
+    L.check(L.lib().fm_kmeans(L.ptr(x), L.dtype_id(x.dtype), d, n_seg, xb, cb, int(iters), L.ptr(cent), L.ptr(A),
+                              L.ptr(ws), ws.numel(), L.stream_ptr(dev)), "fm_kmeans")
+    return A, cent
+
+
+class Memory:
+    """An indexed set of keys/values.  Create with :meth:`build`."""
+
+    def __init__(self):
+        self.k = self.v = self.A = None
+        self.table = self.bucket_off = None
+        self.seg_kb: List[int] = []
+        self.seg_cb: List[int] = []
+        self.seg_z: List[int] = []
+        self.table_off: List[int] = []
+        self.n_heads = self.n_seq = self.d = 0
+        self.max_bucket_len = 0
+        self._seg_cb_dev = None
+        self._q_seg_cache = {}
+
+    # ---- construction ----------------------------------------------------------------------------
+    @classmethod
+    def build(cls, k: torch.Tensor, v: torch.Tensor, *, n_buckets: Optional[IntOrSeq] = None,
+              bucket_size: IntOrSeq, A: Optional[torch.Tensor] = None, kmeans_iters: int = 2,
+              kmeans_init: Optional[torch.Tensor] = None, cu_seqlens_k: Optional[Sequence[int]] = None,
+              key_range: Optional[Tuple[int, int]] = None) -> "Memory":
+        """Index ``k`` / ``v``.
+
+        :param k, v: ``[H, N, d]`` (or ``[H, N_total, d]`` with ``cu_seqlens_k``)
+        :param n_buckets: C per sequence (int or one per sequence); not needed when ``A`` is given
+        :param bucket_size: Z per sequence; a bucket holds ``min(Z, N_seq)`` keys
+        :param A: projection matrix ``[H, C, d]`` (``[H, sum(C), d]`` packed per sequence when varlen) in k's
+            dtype.  If omitted it is built by spherical k-means with ``kmeans_iters`` iterations from
+            ``kmeans_init``
+        :param kmeans_init: rows whose first C (per segment) seed the centroids: ``[H, >=C, d]`` (varlen:
+            packed like A).  Defaults to the first C keys of each segment
+        :param key_range: keep only table entries whose per-head key index lies in ``[lo, hi)`` (the
+            filter the reference hard-codes at tk:283); uniform memories only
+        """
+        dev = L.require_cuda(k, v, A, kmeans_init)
+        if k.dim() != 3 or v.shape != k.shape:
+            raise ValueError(f"k and v must be [H, N, d] with equal shapes, got {tuple(k.shape)} {tuple(v.shape)}")
+        if k.dtype != v.dtype:
+            raise TypeError("k and v must share a dtype")
+        H, N_total, d = k.shape
+        cu = [0, N_total] if cu_seqlens_k is None else [int(x) for x in cu_seqlens_k]
+        if cu[0] != 0 or cu[-1] != N_total or any(b < a for a, b in zip(cu, cu[1:])):
+            raise ValueError("cu_seqlens_k must rise from 0 to the packed key count")
+        n_seq = len(cu) - 1
+        self = cls()
+        self.k, self.v = k.contiguous(), v.contiguous()
+        self.n_heads, self.n_seq, self.d = H, n_seq, d
+        self.cu_seqlens_k = cu
+        if A is not None and n_buckets is None:
+            if n_seq != 1:
+                raise ValueError("n_buckets is needed with a packed A")
+            n_buckets = A.shape[1]
+        if n_buckets is None:
+            raise ValueError("n_buckets or A must be given")
+        Cs = _per_seq(n_buckets, n_seq, "n_buckets")
+        Zs = _per_seq(bucket_size, n_seq, "bucket_size")
+        # segments tile the flat [H * N_total] key rows: segment (h, s) starts at h * N_total + cu[s]
+        seg_kb = [h * N_total + cu[s] for h in range(H) for s in range(n_seq)] + [H * N_total]
+        seg_cb, seg_z, table_off, bucket_len = [0], [], [0], []
+        for h in range(H):
+            for s in range(n_seq):
+                zc = min(Zs[s], cu[s + 1] - cu[s])
+                seg_cb.append(seg_cb[-1] + Cs[s])
+                seg_z.append(Zs[s])
+                bucket_len += [zc] * Cs[s]
+                table_off.append(table_off[-1] + Cs[s] * zc)
+        self.seg_kb, self.seg_cb, self.seg_z, self.table_off = seg_kb, seg_cb, seg_z, table_off
+        self.seq_buckets = Cs
+        total_c = seg_cb[-1]
+        c_per_head = total_c // H
+        n_seg = H * n_seq
+        kf = self.k.reshape(H * N_total, d)
+
+        if A is None:
+            if kmeans_init is None:
+                init = torch.cat([kf[seg_kb[i]: seg_kb[i] + (seg_cb[i + 1] - seg_cb[i])] for i in range(n_seg)], 0)
+                if init.shape[0] != total_c:
+                    raise ValueError("a segment has fewer keys than buckets: pass kmeans_init")
+            else:
+                init = kmeans_init
+                if init.dim() == 3:
+                    if n_seq == 1:
+                        init = init[:, :c_per_head]
+                    init = init.reshape(-1, d)
+                if init.shape[0] != total_c:
+                    raise ValueError(f"kmeans_init must provide {total_c} rows, got {init.shape[0]}")
+            A2, self.centroids_f32 = kmeans_projection(kf, init, kmeans_iters, seg_kb, seg_cb)
+        else:
+            if A.dtype != k.dtype:
+                raise TypeError(f"A ({A.dtype}) must be in the key dtype ({k.dtype})")
+            A2 = A.reshape(-1, d).contiguous()
+            if A2.shape[0] != total_c:
+                raise ValueError(f"A must have {total_c} rows in total, got {A2.shape[0]}")
+            self.centroids_f32 = None
+        self.A = A2
+
+        table = torch.empty(max(table_off[-1], 1), dtype=torch.int32, device=dev)
+        kb, cb, zz, to = L.host_i64(seg_kb), L.host_i64(seg_cb), L.host_i64(seg_z), L.host_i64(table_off[:-1])
+        need = L.lib().fm_index_build_workspace_bytes(n_seg, kb, cb, zz, d, L.dtype_id(k.dtype))
+        ws = ops._ws.get("build", need, dev)
+        L.check(L.lib().fm_index_build(L.ptr(kf), L.ptr(A2), L.dtype_id(k.dtype), d, n_seg, kb, cb, zz, to,
+                                       L.ptr(table), L.ptr(ws), ws.numel(), L.stream_ptr(dev)), "fm_index_build")
+        self.table = table
+        blen = torch.tensor(bucket_len, dtype=torch.int64)
+        bucket_off = torch.zeros(total_c + 1, dtype=torch.int64)
+        torch.cumsum(blen, 0, out=bucket_off[1:])
+        self.bucket_off = bucket_off.to(dev)
+        self.max_bucket_len = max(bucket_len) if bucket_len else 0
+        self._seg_cb_dev = torch.tensor(seg_cb, dtype=torch.int32, device=dev)
+        if key_range is not None:
+            self._apply_key_range(key_range)
+        return self
+
+    def _apply_key_range(self, key_range):
+        """Keep table entries whose per-head key index is in [lo, hi) (compaction like tk:283-286)."""
+        if self.n_seq != 1:
+            raise ValueError("key_range applies to uniform memories only")
+        lo, hi = key_range
+        N = self.k.shape[1]
+        C = self.seq_buckets[0]
+        z = min(self.seg_z[0], N)
+        t = self.table.reshape(self.n_heads, C, z)
+        local = t - (torch.arange(self.n_heads, device=t.device, dtype=torch.int32) * N)[:, None, None]
+        m = torch.logical_and(local >= lo, local < hi)
+        counts = m.sum(-1).reshape(-1).to(torch.int64)
+        self.table = t[m].contiguous()
+        if self.table.numel() == 0:
+            self.table = torch.zeros(1, dtype=torch.int32, device=t.device)
+        off = torch.zeros(counts.numel() + 1, dtype=torch.int64, device=t.device)
+        torch.cumsum(counts, 0, out=off[1:])
+        self.bucket_off = off
+
+    # ---- views -------------------------------------------------------------------------------------
+    @property
+    def total_buckets(self) -> int:
+        return self.seg_cb[-1]
+
+    def table_of(self, head: int, seq: int = 0) -> torch.Tensor:
+        """``[C, min(Z, N)]`` int32 table of one segment as indices LOCAL to the segment's keys."""
+        s = head * self.n_seq + seq
+        C = self.seg_cb[s + 1] - self.seg_cb[s]
+        t = self.table[self.table_off[s]: self.table_off[s + 1]].reshape(C, -1)
+        return t - self.seg_kb[s]
+
+    def projection_of(self, head: int, seq: int = 0) -> torch.Tensor:
+        s = head * self.n_seq + seq
+        return self.A[self.seg_cb[s]: self.seg_cb[s + 1]]
+
+    # ---- query -------------------------------------------------------------------------------------
+    def _query_segments(self, Hq: int, S_total: int, cu_q: Optional[Sequence[int]], dev):
+        key = (Hq, S_total, None if cu_q is None else tuple(cu_q))
+        hit = self._q_seg_cache.get(key)
+        if hit is None:
+            G = Hq // self.n_heads
+            if cu_q is None:
+                if self.n_seq != 1:
+                    raise ValueError("a packed memory needs cu_seqlens_q")
+                xb = [h * G * S_total for h in range(self.n_heads + 1)]
+                max_rows = G * S_total
+            else:
+                cu = [int(x) for x in cu_q]
+                if len(cu) != self.n_seq + 1 or cu[0] != 0 or cu[-1] != S_total:
+                    raise ValueError("cu_seqlens_q must have one entry per sequence plus one and end at the query count")
+                if G != 1:
+                    raise ValueError("packed queries with grouped heads are not supported: fold the group first")
+                xb = [h * S_total + cu[s] for h in range(self.n_heads) for s in range(self.n_seq)] + [Hq * S_total]
+                max_rows = max(b - a for a, b in zip(cu, cu[1:]))
+            hit = (torch.tensor(xb, dtype=torch.int32, device=dev), max_rows)
+            self._q_seg_cache[key] = hit
+        return hit
+
+    def hash_queries(self, q: torch.Tensor, cu_seqlens_q: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """int32 LOCAL bucket of every query, shaped like ``q`` without its last dim (README.md:29)."""
+        Hq, S, d = q.shape
+        seg_xb, max_rows = self._query_segments(Hq, S, cu_seqlens_q, q.device)
+        h = ops.hash_rows(q.reshape(Hq * S, d), self.A, seg_xb, self._seg_cb_dev, max_rows)
+        return h.reshape(Hq, S)
+
+    def query(self, q: torch.Tensor, sm_scale: float, cu_seqlens_q: Optional[Sequence[int]] = None,
+              q_hashes: Optional[torch.Tensor] = None, key_chunk: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+        """q ``[Hq, S, d]`` -> (o ``[Hq, S, d]`` in q's dtype, lse ``[Hq, S]`` fp32 natural log; ``-inf``
+        and o = 0 where the query's bucket is empty)."""
+        dev = L.require_cuda(q)
+        if q.dim() != 3 or q.shape[2] != self.d or q.shape[0] % self.n_heads:
+            raise ValueError(f"q must be [Hq, S, {self.d}] with Hq a multiple of {self.n_heads}, got {tuple(q.shape)}")
+        if q.dtype != self.k.dtype:
+            raise TypeError(f"q ({q.dtype}) must be in the memory's dtype ({self.k.dtype})")
+        q = q.contiguous()
+        Hq, S, d = q.shape
+        seg_xb, max_rows = self._query_segments(Hq, S, cu_seqlens_q, dev)
+        qf = q.reshape(Hq * S, d)
+        if q_hashes is None:
+            hashes = ops.hash_rows(qf, self.A, seg_xb, self._seg_cb_dev, max_rows)
+        else:
+            hashes = q_hashes.reshape(-1).to(torch.int32).contiguous()
+        group_off, perm = ops.group_rows(hashes, self.total_buckets, seg_xb, self._seg_cb_dev)
+        o, lse = ops.hashed_attention(qf, self.k.reshape(-1, d), self.v.reshape(-1, d), self.table, self.bucket_off,
+                                      group_off, perm, sm_scale, self.max_bucket_len, key_chunk=key_chunk)
+        return o.reshape(Hq, S, d), lse.reshape(Hq, S)
+
+    # ---- persistence ---------------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        return dict(A=self.A, table=self.table, bucket_off=self.bucket_off, seg_kb=self.seg_kb, seg_cb=self.seg_cb,
+                    seg_z=self.seg_z, table_off=self.table_off, n_heads=self.n_heads, n_seq=self.n_seq, d=self.d,
+                    max_bucket_len=self.max_bucket_len, seq_buckets=self.seq_buckets,
+                    cu_seqlens_k=self.cu_seqlens_k)
+
+    @classmethod
+    def from_state_dict(cls, state: dict, k: torch.Tensor, v: torch.Tensor) -> "Memory":
+        self = cls()
+        for name, val in state.items():
+            setattr(self, name, val)
+        self.k, self.v = k.contiguous(), v.contiguous()
+        self.centroids_f32 = None
+        self._seg_cb_dev = torch.tensor(self.seg_cb, dtype=torch.int32, device=k.device)
+        return self
+
+
+def merge(o1: torch.Tensor, lse1: torch.Tensor, o2: torch.Tensor, lse2: torch.Tensor
+          ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """LSE-merge two partial attention results over disjoint key sets (mem:54-71): returns fp32
+    ``(out, lse)``; ``o*`` are ``[..., d]``, ``lse*`` are ``[...]``."""
+    out = o1.to(torch.float32).contiguous().clone() if o1.dtype == torch.float32 else o1.to(torch.float32).contiguous()
+    lse = lse1.to(torch.float32).contiguous().clone() if lse1.dtype == torch.float32 else lse1.to(torch.float32).contiguous()
+    ops.lse_merge(out, lse, o2.contiguous(), lse2.contiguous())
+    return out, lse

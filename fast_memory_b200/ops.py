@@ -1,0 +1,292 @@
+"""Operators of the LSH attention-memory path, with the reference's names, arguments and error behaviour.
+
+Drop-in functions (reference interface in brackets; tk = triton_kernel.py, mem = memory.py):
+
+  * :func:`attention_hash_varlen`   [tk:51-119]
+  * :func:`attention_hash`          [tk:275-286]
+  * :func:`update_out_and_lse`      [mem:54-71]
+  * :func:`ring_attention_masked_forward` [mem:106-163]
+
+plus the thin tensor-level wrappers of the C entry points they are built from (``hash_rows``,
+``group_rows``, ``hashed_attention``, ``lse_merge``, ``project``, ``topz_select``, ``unit_rows``).
+Everything runs in the CUDA library; tensors must live on a CUDA device.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+
+class _Workspace:
+    """Per-device scratch buffers that grow on demand and are reused between calls."""
+
+    def __init__(self):
+        self._bufs = {}
+
+    def get(self, key: str, nbytes: int, device) -> torch.Tensor:
+        k = (key, device)
+        buf = self._bufs.get(k)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+            self._bufs[k] = buf
+        return buf
+
+
+_ws = _Workspace()
+
+
+# ---------------------------------------------------------------------------------------------------
+# tensor-level wrappers of the C entry points
+# ---------------------------------------------------------------------------------------------------
+def hash_rows(x: torch.Tensor, A: torch.Tensor, seg_xb: Optional[torch.Tensor] = None,
+              seg_cb: Optional[torch.Tensor] = None, max_seg_rows: int = 0) -> torch.Tensor:
+    """x ``[rows, d]``, A ``[buckets, d]`` (same dtype) -> int32 ``[rows]`` local bucket of each row."""
+    dev = L.require_cuda(x, A, seg_xb, seg_cb)
+    if x.dtype != A.dtype:
+        raise TypeError(f"x ({x.dtype}) and A ({A.dtype}) must share a dtype")
+    assert x.dim() == 2 and A.dim() == 2 and x.shape[1] == A.shape[1]
+    assert x.is_contiguous() and A.is_contiguous()
+    out = torch.empty(x.shape[0], dtype=torch.int32, device=dev)
+    n_seg = 1 if seg_xb is None else seg_xb.numel() - 1
+    L.check(L.lib().fm_hash_rows(L.ptr(x), L.ptr(A), L.dtype_id(x.dtype), x.shape[0], A.shape[0], x.shape[1], n_seg,
+                                 L.ptr(seg_xb), L.ptr(seg_cb), int(max_seg_rows), L.ptr(out), L.stream_ptr(dev)),
+            "fm_hash_rows")
+    return out
+
+
+def group_rows(hashes: torch.Tensor, total_buckets: int, seg_xb: Optional[torch.Tensor] = None,
+               seg_cb: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Counting sort of rows by global bucket -> (group_off int32 ``[buckets+1]``, perm int32 ``[rows]``)."""
+    dev = L.require_cuda(hashes, seg_xb, seg_cb)
+    assert hashes.dtype == torch.int32 and hashes.is_contiguous()
+    n = hashes.numel()
+    group_off = torch.empty(total_buckets + 1, dtype=torch.int32, device=dev)
+    perm = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    need = L.lib().fm_group_rows_workspace_bytes(n, total_buckets)
+    ws = _ws.get("group", need, dev)
+    n_seg = 1 if seg_xb is None else seg_xb.numel() - 1
+    L.check(L.lib().fm_group_rows(L.ptr(hashes), n, total_buckets, n_seg, L.ptr(seg_xb), L.ptr(seg_cb),
+                                  L.ptr(group_off), L.ptr(perm), L.ptr(ws), ws.numel(), L.stream_ptr(dev)),
+            "fm_group_rows")
+    return group_off, perm[:n]
+
+
+def hashed_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: torch.Tensor,
+                     bucket_off: torch.Tensor, group_off: torch.Tensor, perm: torch.Tensor, sm_scale: float,
+                     max_bucket_len: int, bucket_kbase: Optional[torch.Tensor] = None, key_chunk: int = 0,
+                     out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None
+                     ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q ``[n_q, d]``, k/v ``[n_k, d]``; flat ``table`` (int32 or int64) cut by ``bucket_off`` (int64
+    ``[buckets+1]``); queries grouped by ``group_off`` / ``perm``.  Returns o (q's dtype) and fp32
+    natural-log LSE (``-inf`` where the bucket is empty)."""
+    dev = L.require_cuda(q, k, v, table, bucket_off, group_off, perm, bucket_kbase)
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("q, k and v must share a dtype")
+    assert q.dim() == 2 and k.dim() == 2 and v.shape == k.shape and q.shape[1] == k.shape[1]
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and table.is_contiguous()
+    assert table.dtype in (torch.int32, torch.int64) and bucket_off.dtype == torch.int64
+    assert group_off.dtype == torch.int32 and perm.dtype == torch.int32
+    n_q, d = q.shape
+    total_buckets = bucket_off.numel() - 1
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None:
+        lse = torch.empty(n_q, dtype=torch.float32, device=dev)
+    need = L.lib().fm_hashed_attn_workspace_bytes(n_q, total_buckets, int(max_bucket_len), d, int(key_chunk))
+    ws = _ws.get("attn", need, dev)
+    L.check(L.lib().fm_hashed_attn_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.dtype_id(q.dtype), d, n_q, k.shape[0],
+                                       total_buckets, L.ptr(table), table.element_size(), L.ptr(bucket_off),
+                                       L.ptr(bucket_kbase), int(max_bucket_len), L.ptr(group_off), L.ptr(perm),
+                                       float(sm_scale), L.ptr(out), L.ptr(lse), int(key_chunk), L.ptr(ws), ws.numel(),
+                                       L.stream_ptr(dev)), "fm_hashed_attn_fwd")
+    return out, lse
+
+
+def lse_merge(out: torch.Tensor, lse: torch.Tensor, block_out: torch.Tensor, block_lse: torch.Tensor) -> None:
+    """In place on fp32 ``out`` ``[rows, d]`` / ``lse`` ``[rows]``."""
+    dev = L.require_cuda(out, lse, block_out, block_lse)
+    if out.dtype != torch.float32 or lse.dtype != torch.float32:
+        raise TypeError("the merge accumulators must be float32")
+    assert out.is_contiguous() and lse.is_contiguous() and block_out.is_contiguous() and block_lse.is_contiguous()
+    d = out.shape[-1]
+    rows = out.numel() // d
+    assert block_out.numel() == out.numel() and lse.numel() == rows and block_lse.numel() == rows
+    L.check(L.lib().fm_lse_merge(L.ptr(out), L.ptr(lse), L.ptr(block_out), L.dtype_id(block_out.dtype),
+                                 L.ptr(block_lse), L.dtype_id(block_lse.dtype), rows, d, L.stream_ptr(dev)),
+            "fm_lse_merge")
+
+
+def project(A: torch.Tensor, K: torch.Tensor) -> torch.Tensor:
+    """fp32 ``Y[c, j] = A[c] . K[j]`` in the library's fixed summation order."""
+    dev = L.require_cuda(A, K)
+    assert A.dtype == K.dtype and A.is_contiguous() and K.is_contiguous() and A.shape[1] == K.shape[1]
+    Y = torch.empty(A.shape[0], K.shape[0], dtype=torch.float32, device=dev)
+    L.check(L.lib().fm_project(L.ptr(A), L.ptr(K), L.dtype_id(A.dtype), A.shape[0], K.shape[0], A.shape[1], L.ptr(Y),
+                               K.shape[0], L.stream_ptr(dev)), "fm_project")
+    return Y
+
+
+def topz_select(Y: torch.Tensor, Z: int, index_base: int = 0) -> torch.Tensor:
+    """Rows of fp32 ``Y`` -> int32 ``[rows, Z]`` indices of the Z largest (lower index wins ties), ascending."""
+    dev = L.require_cuda(Y)
+    assert Y.dtype == torch.float32 and Y.dim() == 2 and Y.is_contiguous()
+    Z = min(int(Z), Y.shape[1])
+    out = torch.empty(Y.shape[0], Z, dtype=torch.int32, device=dev)
+    L.check(L.lib().fm_topz_select(L.ptr(Y), Y.shape[0], Y.shape[1], Y.shape[1], Z, int(index_base), L.ptr(out), Z,
+                                   L.stream_ptr(dev)), "fm_topz_select")
+    return out
+
+
+def unit_rows(X: torch.Tensor) -> torch.Tensor:
+    dev = L.require_cuda(X)
+    X2 = X.reshape(-1, X.shape[-1]).contiguous()
+    U = torch.empty(X2.shape, dtype=torch.float32, device=dev)
+    L.check(L.lib().fm_unit_rows(L.ptr(X2), L.dtype_id(X.dtype), X2.shape[0], X2.shape[1], L.ptr(U), L.stream_ptr(dev)),
+            "fm_unit_rows")
+    return U.reshape(X.shape)
+
+
+# ---------------------------------------------------------------------------------------------------
+# drop-in operators
+# ---------------------------------------------------------------------------------------------------
+_kbase_cache = {}
+
+
+def _uniform_kbase(B: int, C: int, N: int, device) -> torch.Tensor:
+    key = (B, C, N, device)
+    t = _kbase_cache.get(key)
+    if t is None:
+        t = (torch.arange(B * C, device=device, dtype=torch.int64) // C * N).to(torch.int32)
+        _kbase_cache[key] = t
+    return t
+
+
+@torch.library.custom_op("fast_memory_b200::attention_hash_varlen", mutates_args=())
+def _attention_hash_varlen_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_hashes: torch.Tensor,
+                              k_hash_counts: torch.Tensor, q_hashes: torch.Tensor, sm_scale: float,
+                              max_bucket_len: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Registered operator behind :func:`attention_hash_varlen` (the reference registers
+    ``notbad::attention_hash_varlen``, tk:16).  Returns o ``[B, S, d]`` and fp32 natural-log LSE ``[B, S]``."""
+    B, S, d = q.shape
+    N = k.shape[1]
+    C = k_hash_counts.shape[1]
+    dev = q.device
+    bucket_off = torch.zeros(B * C + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(k_hash_counts.reshape(-1), 0, out=bucket_off[1:])
+    hashes = q_hashes.reshape(-1).to(torch.int32)
+    seg_xb = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+    seg_cb = torch.arange(0, (B + 1) * C, C, dtype=torch.int32, device=dev)
+    group_off, perm = group_rows(hashes, B * C, seg_xb, seg_cb)
+    table = k_hashes if k_hashes.dtype in (torch.int32, torch.int64) else k_hashes.to(torch.int64)
+    o, lse = hashed_attention(q.reshape(B * S, d), k.reshape(B * N, d), v.reshape(B * N, d), table.contiguous(),
+                              bucket_off, group_off, perm, sm_scale, max_bucket_len,
+                              bucket_kbase=_uniform_kbase(B, C, N, dev))
+    return o.reshape(B, S, d), lse.reshape(B, S)
+
+
+@_attention_hash_varlen_op.register_fake
+def _(q, k, v, k_hashes, k_hash_counts, q_hashes, sm_scale, max_bucket_len):
+    return torch.empty_like(q), q.new_empty(q.shape[:-1], dtype=torch.float32)
+
+
+def attention_hash_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                          k_hashes: torch.Tensor, k_hash_counts: torch.Tensor,
+                          q_hashes: torch.Tensor,
+                          sm_scale: float, *, return_fp32_lse: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Hashed attention forward (drop-in for tk:51-119).
+
+    :param q: ``[batch_size, q_seq_len, d_head]``
+    :param k: ``[batch_size, kv_seq_len, d_head]``
+    :param v: ``[batch_size, kv_seq_len, d_head]``
+    :param k_hashes: flat key indices, ``[sum(k_hash_counts)]``, ordered (batch, bucket, slot)
+    :param k_hash_counts: ``[batch_size, C]``
+    :param q_hashes: ``[batch_size, q_seq_len]`` bucket of every query
+    :param sm_scale: softmax scale
+
+    Returns ``(o, lse)`` with o in q's dtype.  As in the reference, lse is returned in q's dtype after
+    ``nan_to_num`` (empty bucket -> ``finfo.min``; tk:111-117); ``return_fp32_lse=True`` returns the
+    un-rounded fp32 natural-log LSE with ``-inf`` for empty buckets instead.
+    """
+    batch_size, q_seq_len, d_head = q.shape
+    _, kv_seq_len, _ = k.shape
+    _, n_buckets = k_hash_counts.shape
+    assert k.shape[0] == batch_size
+    assert k_hash_counts.shape[0] == batch_size
+    assert q_hashes.shape[0] == batch_size
+    assert q_hashes.shape[1] == q_seq_len, f'{q_hashes.shape} != {q_seq_len}'
+    assert d_head == k.shape[-1] == v.shape[-1]
+    assert q.is_contiguous()
+    assert k.is_contiguous()
+    assert v.is_contiguous()
+    assert k.stride() == v.stride()
+    L.require_cuda(q, k, v, k_hashes, k_hash_counts, q_hashes)
+    # the longest bucket sizes the work split; like the reference wrapper (unique_consecutive, tk:81)
+    # this reads one number back from the device
+    max_len = int(k_hash_counts.max().item()) if k_hash_counts.numel() else 0
+    o, lse = _attention_hash_varlen_op(q, k, v, k_hashes, k_hash_counts, q_hashes, float(sm_scale), max_len)
+    if return_fp32_lse:
+        return o, lse
+    lse = (lse * (1.0 / math.log(2))).to(q.dtype) * math.log(2)
+    lse = torch.nan_to_num(lse, nan=0.0, posinf=torch.finfo(lse.dtype).max, neginf=torch.finfo(lse.dtype).min)
+    return o, lse
+
+
+def attention_hash(q, k, v, centroids, bucket_size, sm_scale, key_range: Optional[Tuple[int, int]] = None):
+    """Single-device build + hash + attend (drop-in for tk:275-286).
+
+    q ``[B, S, d]``, k/v ``[B, N, d]``, centroids ``[B, C, d]``.  The reference hard-codes a key-index
+    filter ``[8192, 65536)`` (tk:283); here it is the optional ``key_range``.
+    """
+    from .memory import Memory
+    mem = Memory.build(k, v, A=centroids, bucket_size=bucket_size, key_range=key_range)
+    o, lse = mem.query(q, sm_scale)
+    lse = (lse * (1.0 / math.log(2))).to(q.dtype) * math.log(2)
+    lse = torch.nan_to_num(lse, nan=0.0, posinf=torch.finfo(lse.dtype).max, neginf=torch.finfo(lse.dtype).min)
+    return o, lse
+
+
+def update_out_and_lse(out: Optional[torch.Tensor], lse: Optional[torch.Tensor],
+                       block_out: torch.Tensor, block_lse: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Merge a block's (out, lse) into fp32 accumulators (drop-in for mem:54-71).
+
+    First call (``out is None``): returns ``block_out`` in fp32 and ``block_lse`` with a trailing
+    singleton dimension.  Unlike the reference the lse accumulator is always fp32 (the reference keeps
+    the dtype of the first block's lse).  Later calls update ``out`` / ``lse`` in place and return them.
+    """
+    if out is None:
+        return block_out.to(torch.float32).contiguous(), block_lse.to(torch.float32).unsqueeze(dim=-1).contiguous()
+    assert lse is not None and lse.shape[-1] == 1
+    lse_merge(out, lse, block_out.contiguous(), block_lse.contiguous())
+    return out, lse
+
+
+def ring_attention_masked_forward(k_hashes, q_hashes, q, k, v, sm_scale, rank):
+    """Attention of all queries against ONE key shard of a globally indexed memory (drop-in for
+    mem:106-163).
+
+    :param k_hashes: ``[n_buckets, k_heads, bucket_size]`` GLOBAL key indices
+    :param q_hashes: ``[k_heads, n_groups, seq_len]``
+    :param q: ``[1, n_heads, seq_len, d]``;  k, v: ``[1, k_heads, context_len, d]`` (the visiting shard)
+    :param rank: which shard is visiting: only table entries in ``[rank*ctx, (rank+1)*ctx)`` take part
+    Returns ``(out [1, n_heads, seq_len, d], lse [1, n_heads, seq_len])`` in q's dtype.
+    """
+    batch_size, n_heads, seq_len, d_head = q.shape
+    _, k_heads, context_len, _ = k.shape
+    assert batch_size == 1
+    assert k_hashes.shape[1] == k_heads
+    assert q_hashes.shape[0] == k_heads
+    assert q_hashes.shape[1] == n_heads // k_heads
+    assert q_hashes.shape[2] == seq_len
+    k_hashes = k_hashes.permute(1, 0, 2)
+    q_hashes = q_hashes.reshape(k_heads, -1)
+    mask = torch.logical_and(rank * context_len <= k_hashes, k_hashes < (rank + 1) * context_len)
+    counts = mask.to(torch.long).sum(-1)
+    assert k_hashes.numel() > 0, k_hashes.shape
+    flat = k_hashes[mask] - rank * context_len
+    out, lse = attention_hash_varlen(q.reshape(k_heads, -1, d_head), k.reshape(k_heads, -1, d_head),
+                                     v.reshape(k_heads, -1, d_head), flat, counts, q_hashes, sm_scale)
+    return out.reshape(batch_size, n_heads, seq_len, d_head), lse.reshape(batch_size, n_heads, seq_len)

@@ -1,0 +1,157 @@
+/*
+ * fastmem_b200 - C ABI of the B200 (sm_100a) LSH attention-memory kernels.
+ *
+ * Every entry point takes plain pointers and sizes, runs asynchronously on the CUDA stream it is
+ * given, writes only into caller-provided buffers and returns FM_OK or a negative status.  Unless a
+ * declaration says otherwise nothing is allocated inside: scratch memory is a caller-provided
+ * workspace whose size comes from the matching *_workspace_bytes function.
+ *
+ * Vocabulary.  A memory is made of SEGMENTS (one per KV head, or per (head, sequence) for packed
+ * variable-length memories).  Segment s owns key rows [seg_kb[s], seg_kb[s+1]) of the flat K / V
+ * arrays [rows, d], buckets [seg_cb[s], seg_cb[s+1]) of the flat bucket space, the matching rows of
+ * the packed projection matrix A [total_buckets, d], and query rows [seg_qb[s], seg_qb[s+1]).
+ * The bucket table is a flat list of key rows ordered (bucket, slot); bucket b owns
+ * table[bucket_off[b] .. bucket_off[b+1]).
+ *
+ * Each declaration cites the reference interface it stands in for
+ * (tk = triton_kernel.py, mem = memory.py of notbadai/fast_memory).
+ */
+#ifndef FASTMEM_B200_H
+#define FASTMEM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FM_ABI_VERSION 1
+
+/* element types of q / k / v / A */
+#define FM_F32 0
+#define FM_BF16 1
+#define FM_F16 2
+
+/* status codes */
+#define FM_OK 0
+#define FM_ERR_BAD_ARG (-1)       /* null pointer, negative size, misaligned buffer              */
+#define FM_ERR_UNSUPPORTED (-2)   /* head dim / dtype / size outside what the kernels were built for */
+#define FM_ERR_WORKSPACE (-3)     /* workspace smaller than *_workspace_bytes                     */
+#define FM_ERR_CUDA (-4)          /* a CUDA runtime call or launch failed (see fm_last_error)     */
+#define FM_ERR_DEVICE (-5)        /* a kernel reported an anomaly through the status word         */
+
+typedef void *fm_stream_t; /* a cudaStream_t */
+
+int fm_abi_version(void);
+const char *fm_status_string(int status);
+/* Thread-local text describing the last non-OK status returned on this thread. */
+const char *fm_last_error(void);
+/* Number of kernels this library has launched in the calling process (for launch accounting). */
+int64_t fm_launch_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Query hashing: hash[r] = argmax_c  A[c, :] . x[r, :]  over the buckets of r's segment, as a LOCAL
+ * bucket number; first maximum wins; fp32 sequential-FMA projection.
+ * Replaces: einsum + argmax at mem:281-283 and tk:280-281 (README.md:29).
+ * x [n_rows, d] and A [total_buckets, d] share `dtype`.  seg_xb / seg_cb: DEVICE int32 prefix
+ * arrays of n_seg+1 entries (pass NULL, NULL and n_seg = 1 for one segment covering everything).
+ * max_seg_rows: largest number of rows in one segment (sizes the grid).
+ * ------------------------------------------------------------------------------------------- */
+int fm_hash_rows(const void *x, const void *A, int dtype, int64_t n_rows, int64_t total_buckets, int d,
+                 int n_seg, const int32_t *seg_xb, const int32_t *seg_cb, int64_t max_seg_rows,
+                 int32_t *hash_out, fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Grouping: counting sort of rows by global bucket (segment bucket base + local hash).
+ * Replaces: the stable sort / unique_consecutive / cumsum block of the reference wrapper, tk:75-88.
+ * Out: group_off [total_buckets+1] int32 exclusive prefix of rows per bucket; perm [n_rows] int32,
+ * perm[group_off[b] .. group_off[b+1]) = the rows hashed to bucket b (order inside a bucket is
+ * unspecified; the attention result does not depend on it).
+ * ------------------------------------------------------------------------------------------- */
+size_t fm_group_rows_workspace_bytes(int64_t n_rows, int64_t total_buckets);
+int fm_group_rows(const int32_t *hash, int64_t n_rows, int64_t total_buckets, int n_seg,
+                  const int32_t *seg_xb, const int32_t *seg_cb, int32_t *group_off, int32_t *perm,
+                  void *workspace, size_t workspace_bytes, fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Hashed attention forward: every query attends to the keys listed in its bucket.
+ * Replaces: torch op notbad::attention_hash_varlen and its Triton kernel, tk:16-41, 135-272 (the
+ * gathers through the table, base-2 online softmax, P rounded to the q dtype before P.V), without
+ * the q / o permutation copies of tk:77, 109: queries are read and outputs written through `perm`.
+ *   q, o      [n_q_rows, d] in `dtype`;  k, v [n_k_rows, d] in `dtype`
+ *   table     key rows, int32 (idx_bytes = 4) or int64 (idx_bytes = 8)
+ *   bucket_off [total_buckets+1] int64, DEVICE
+ *   bucket_kbase [total_buckets] int32 DEVICE or NULL: added to every table entry of the bucket
+ *              (lets a table hold per-head indices as the reference's does)
+ *   group_off, perm: from fm_group_rows
+ *   lse       [n_q_rows] fp32 natural-log LSE; -inf (and o = 0) where the bucket is empty
+ *   key_chunk  keys per work item; 0 lets the library choose.  Buckets longer than one chunk are
+ *              split over CTAs and combined by a second kernel (needs the workspace).
+ * ------------------------------------------------------------------------------------------- */
+size_t fm_hashed_attn_workspace_bytes(int64_t n_q_rows, int64_t total_buckets, int64_t max_bucket_len, int d,
+                                      int64_t key_chunk);
+int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, int dtype, int d, int64_t n_q_rows,
+                       int64_t n_k_rows, int64_t total_buckets, const void *table, int idx_bytes,
+                       const int64_t *bucket_off, const int32_t *bucket_kbase, int64_t max_bucket_len,
+                       const int32_t *group_off, const int32_t *perm, float sm_scale, void *o, float *lse,
+                       int64_t key_chunk, void *workspace, size_t workspace_bytes, fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * LSE merge, in place on fp32 accumulators:
+ *   lse <- log(e^lse + e^blk_lse);  out <- out - sigmoid(blk_lse - lse) (out - blk_out)
+ * Replaces: update_out_and_lse, mem:54-71 (the branch with existing accumulators, mem:67-69).
+ * blk_out is in `blk_dtype`; blk_lse in `lse_dtype`.  A side whose LSE is -inf has weight 0.
+ * ------------------------------------------------------------------------------------------- */
+int fm_lse_merge(float *out, float *lse, const void *blk_out, int blk_dtype, const void *blk_lse, int lse_dtype,
+                 int64_t n_rows, int d, fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Projection Y[c, j] = A[c, :] . K[j, :] in fp32 (sequential FMA over the head dim), row stride ldy.
+ * Replaces: the einsum at mem:261 / tk:277 (README.md:25).  Stand-alone form, for tests and for
+ * callers that want the scores themselves.
+ * ------------------------------------------------------------------------------------------- */
+int fm_project(const void *A, const void *K, int dtype, int64_t C, int64_t N, int d, float *Y, int64_t ldy,
+               fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Exact top-Z of every row of Y [n_rows, N] (row stride ldy): the Z largest values, lower index wins
+ * ties, indices written in ascending order plus `index_base`.
+ * Replaces: torch.topk at mem:273 / tk:278 (README.md:27).  Z <= N.
+ * ------------------------------------------------------------------------------------------- */
+int fm_topz_select(const float *Y, int64_t n_rows, int64_t N, int64_t ldy, int64_t Z, int32_t index_base,
+                   int32_t *table, int64_t ld_table, fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Index build for a whole memory: for every segment, table rows of its buckets = top-min(Z_s, N_s)
+ * keys by projection, as ABSOLUTE key rows in ascending order.
+ * Replaces: einsum + topk, mem:261 + 273 and tk:277-278.
+ * seg_kb, seg_cb [n_seg+1] and seg_z [n_seg] are HOST arrays.  Bucket b of segment s is written at
+ * table + table_off[s] + (b - seg_cb[s]) * min(seg_z[s], N_s)  (table_off: HOST, n_seg entries).
+ * ------------------------------------------------------------------------------------------- */
+size_t fm_index_build_workspace_bytes(int n_seg, const int64_t *seg_kb, const int64_t *seg_cb, const int64_t *seg_z,
+                                      int d, int dtype);
+int fm_index_build(const void *K, const void *A, int dtype, int d, int n_seg, const int64_t *seg_kb,
+                   const int64_t *seg_cb, const int64_t *seg_z, const int64_t *table_off, int32_t *table,
+                   void *workspace, size_t workspace_bytes, fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Projection matrix by spherical k-means (distance 1 - c.x, README.md:37-45): `iters` rounds of
+ * assignment (fm_hash_rows on the raw rows) and centroid update (exact integer sums of the unit rows
+ * in units of 2^-40, normalised in fp64).  The reference's code has no k-means (mem:209-231 is a
+ * different construction); this follows its README.
+ * X [rows, d] in `dtype`; cent_f32 [total_buckets, d] fp32 in/out: initial centroids (unit rows) on
+ * entry, final centroids on exit; A_out [total_buckets, d] in `dtype` = the final centroids rounded
+ * to the key dtype (the form the index build and the query hash use).  seg_* are HOST arrays.
+ * ------------------------------------------------------------------------------------------- */
+size_t fm_kmeans_workspace_bytes(int n_seg, const int64_t *seg_xb, const int64_t *seg_cb, int d);
+int fm_kmeans(const void *X, int dtype, int d, int n_seg, const int64_t *seg_xb, const int64_t *seg_cb, int iters,
+              float *cent_f32, void *A_out, void *workspace, size_t workspace_bytes, fm_stream_t stream);
+
+/* U[r, :] = X[r, :] / max(||X[r, :]||, 1e-6) in fp32 (unit-sphere projection, README.md:39; mem:215-217). */
+int fm_unit_rows(const void *X, int dtype, int64_t n_rows, int d, float *U, fm_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTMEM_B200_H */

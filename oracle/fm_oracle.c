@@ -80,18 +80,32 @@ void fmo_project_fast(const float *A, const float *K, int64_t C, int64_t N, int6
  * README.md:29, memory.py:281-283, triton_kernel.py:280-281. */
 void fmo_argmax_hash(const float *A, const float *X, int64_t C, int64_t R, int64_t d, int32_t *h)
 {
-#pragma omp parallel for schedule(static)
-    for (int64_t r = 0; r < R; ++r) {
-        const float *x = X + r * d;
-        float best = -INFINITY;
-        int32_t arg = 0;
-        for (int64_t c = 0; c < C; ++c) {
-            const float *a = A + c * d;
-            float y = 0.0f;
-            for (int64_t i = 0; i < d; ++i) y = fmaf(a[i], x[i], y);
-            if (y > best || c == 0) { best = y; arg = (int32_t)c; }
+    /* rows are processed in tiles, transposed once, so that the FMA chain of every (row, bucket) pair
+     * keeps its sequential order over i while the compiler vectorises across the rows of the tile */
+#pragma omp parallel
+    {
+        float *xt = (float *)malloc((size_t)d * FMO_TILE * sizeof(float));
+        float acc[FMO_TILE], best[FMO_TILE];
+        int32_t arg[FMO_TILE];
+#pragma omp for schedule(static)
+        for (int64_t r0 = 0; r0 < R; r0 += FMO_TILE) {
+            int64_t rn = (R - r0 < FMO_TILE) ? (R - r0) : FMO_TILE;
+            for (int64_t j = 0; j < rn; ++j)
+                for (int64_t i = 0; i < d; ++i) xt[i * FMO_TILE + j] = X[(r0 + j) * d + i];
+            for (int64_t c = 0; c < C; ++c) {
+                const float *a = A + c * d;
+                for (int64_t j = 0; j < rn; ++j) acc[j] = 0.0f;
+                for (int64_t i = 0; i < d; ++i) {
+                    float ai = a[i];
+                    const float *xr = xt + i * FMO_TILE;
+                    for (int64_t j = 0; j < rn; ++j) acc[j] = fmaf(ai, xr[j], acc[j]);
+                }
+                for (int64_t j = 0; j < rn; ++j)
+                    if (c == 0 || acc[j] > best[j]) { best[j] = acc[j]; arg[j] = (int32_t)c; }
+            }
+            for (int64_t j = 0; j < rn; ++j) h[r0 + j] = arg[j];
         }
-        h[r] = arg;
+        free(xt);
     }
 }
 

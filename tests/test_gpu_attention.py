@@ -1,0 +1,145 @@
+"""GPU parity of the hashed-attention path (through the C ABI) against the CPU oracle and the golden vectors."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import fast_memory_b200 as fm
+from oracle import oracle as O
+from tests.util import TOL_LSE, TOL_O, assert_attn_close, random_case
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DT = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+
+
+def _run_dropin(q, k, v, kh, cnt, qh, sm, **kw):
+    return fm.attention_hash_varlen(q.to(DEV), k.to(DEV), v.to(DEV), kh.to(DEV), cnt.to(DEV), qh.to(DEV), sm, **kw)
+
+
+@pytest.mark.parametrize("name", ["attn_f32_tiny", "attn_f32_ragged", "attn_f16_ragged", "attn_f32_d128",
+                                  "attn_f32_empty_buckets"])
+def test_matches_reference_golden(golden_dir, name):
+    """Outputs of the reference's own kernel (tk:51-272) on the same inputs."""
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    dt = DT[str(z["dtype"])]
+    t = lambda a: torch.from_numpy(np.asarray(a))
+    q, k, v = t(z["q"]).to(dt), t(z["k"]).to(dt), t(z["v"]).to(dt)
+    o, lse = _run_dropin(q, k, v, t(z["k_hashes"]), t(z["k_hash_counts"]), t(z["q_hashes"]), float(z["sm_scale"]))
+    assert o.dtype == dt and lse.dtype == dt                         # reference returns LSE in q's dtype
+    tol_o = 1e-4 if dt == torch.float32 else 2e-2
+    assert (o.float().cpu() - t(z["o"])).abs().max() <= tol_o
+    ref_lse = t(z["lse"])
+    fin = ref_lse > torch.finfo(dt).min
+    assert torch.equal(lse.float().cpu()[~fin], ref_lse[~fin])       # empty bucket -> finfo.min (tk:114-117)
+    tol_l = 1e-3 if dt == torch.float32 else 8e-3                    # fp16 LSE carries its own rounding (tk:111)
+    assert (lse.float().cpu()[fin] - ref_lse[fin]).abs().max() <= tol_l
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [16, 32, 64, 128, 256])
+def test_random_ragged_vs_oracle(dtype, d):
+    B, S, N, C, Z = 2, 150, 700, 12, 90
+    q, k, v, kh, cnt, qh = random_case(B, S, N, C, Z, d, dtype, seed=100 + d)
+    o, lse = _run_dropin(q, k, v, kh, cnt, qh, d ** -0.5, return_fp32_lse=True)
+    o_ref, lse_ref = O.hashed_attention(q, k, v, kh, cnt, qh, d ** -0.5)
+    assert_attn_close(o, lse, o_ref, lse_ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reference_self_test_shape(dtype):
+    """The reference's own large correctness shape, cut to 2 heads (tk:502): S=4*2040, N=61380, C=512, Z=1024, d=128."""
+    B, S, N, C, Z, d = 2, 4 * 2040, 1023 * 60, 512, 1024, 128
+    q, k, v, kh, cnt, qh = random_case(B, S, N, C, Z, d, dtype, seed=20)
+    o, lse = _run_dropin(q, k, v, kh, cnt, qh, d ** -0.5, return_fp32_lse=True)
+    # oracle on a sample of queries (the full dense check is minutes of CPU)
+    g = torch.Generator().manual_seed(1)
+    pick = torch.randperm(S, generator=g)[:96]
+    for b in range(B):
+        o_ref, lse_ref = O.hashed_attention(q[b:b + 1, pick], k[b:b + 1], v[b:b + 1],
+                                            kh[cnt[:b].sum():cnt[:b + 1].sum()], cnt[b:b + 1], qh[b:b + 1, pick], d ** -0.5)
+        assert_attn_close(o[b:b + 1, pick], lse[b:b + 1, pick], o_ref, lse_ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("key_chunk", [64, 128, 1000])
+def test_split_buckets_match_unsplit(dtype, key_chunk):
+    """Few queries, long buckets: buckets are cut into key chunks and the partials combined."""
+    B, S, N, C, Z, d = 1, 9, 3000, 4, 1000, 64
+    q, k, v, kh, cnt, qh = random_case(B, S, N, C, Z, d, dtype, seed=7)
+    dev = lambda t: t.to(DEV)
+    bucket_off = torch.zeros(B * C + 1, dtype=torch.int64)
+    bucket_off[1:] = torch.cumsum(cnt.reshape(-1), 0)
+    group_off, perm = fm.group_rows(dev(qh.reshape(-1).int()), B * C)
+    o, lse = fm.hashed_attention(dev(q[0]), dev(k[0]), dev(v[0]), dev(kh), dev(bucket_off), group_off, perm,
+                                 d ** -0.5, int(cnt.max()), key_chunk=key_chunk)
+    o_ref, lse_ref = O.hashed_attention(q, k, v, kh, cnt, qh, d ** -0.5)
+    assert_attn_close(o[None], lse[None], o_ref, lse_ref, dtype)
+
+
+def test_edge_cases():
+    d = 32
+    # one query, one key; a bucket with no key; a query block boundary (17 queries in one bucket); int32 table
+    q, k, v, kh, cnt, qh = random_case(1, 17, 64, 3, 5, d, torch.float32, seed=3)
+    qh[:] = 1
+    o, lse = _run_dropin(q, k, v, kh.int(), cnt, qh, 0.3, return_fp32_lse=True)
+    o_ref, lse_ref = O.hashed_attention(q, k, v, kh, cnt, qh, 0.3)
+    assert_attn_close(o, lse, o_ref, lse_ref, torch.float32)
+    cnt0 = cnt.clone()
+    cnt0[0, 1] = 0                                                   # the queried bucket becomes empty
+    kh0 = torch.cat([kh[:cnt[0, 0]], kh[cnt[0, :2].sum():]])
+    o, lse = _run_dropin(q, k, v, kh0, cnt0, qh, 0.3, return_fp32_lse=True)
+    assert (o == 0).all() and torch.isinf(lse).all() and (lse < 0).all()
+    o, lse = _run_dropin(q, k, v, kh0, cnt0, qh, 0.3)               # drop-in form: finfo.min (tk:114-117)
+    assert (lse == torch.finfo(torch.float32).min).all()
+    # no queries at all
+    o, lse = _run_dropin(q[:, :0], k, v, kh, cnt, qh[:, :0], 0.3)
+    assert o.shape == (1, 0, d) and lse.shape == (1, 0)
+
+
+def test_deterministic():
+    q, k, v, kh, cnt, qh = random_case(2, 300, 2000, 16, 300, 128, torch.bfloat16, seed=5)
+    a = _run_dropin(q, k, v, kh, cnt, qh, 0.1, return_fp32_lse=True)
+    b = _run_dropin(q, k, v, kh, cnt, qh, 0.1, return_fp32_lse=True)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_ring_attention_masked_forward_matches_reference_dense(golden_dir):
+    """mem:106-163 drop-in against the reference's dense statement (mem:74-103) on two key shards + merge."""
+    z = np.load(os.path.join(golden_dir, "dense_ref_two_shards.npz"))
+    t = lambda a: torch.from_numpy(np.asarray(a)).to(DEV)
+    q, k, v = t(z["q"]), t(z["k"]), t(z["v"])
+    out, lse = None, None
+    for r in range(k.shape[0]):
+        bo, bl = fm.ring_attention_masked_forward(t(z["k_hashes"]), t(z["q_hashes"]), q, k[r], v[r], float(z["sm_scale"]), r)
+        assert (bo.cpu() - torch.from_numpy(z[f"out_rank{r}"])).abs().max() <= 1e-4
+        out, lse = fm.update_out_and_lse(out, lse, bo, bl)
+    assert (out.cpu() - torch.from_numpy(z["out_merged"])).abs().max() <= 1e-4
+    assert (lse.cpu() - torch.from_numpy(z["lse_merged"])).abs().max() <= 1e-3
+
+
+def test_merge_matches_reference(golden_dir):
+    z = np.load(os.path.join(golden_dir, "merge_chain.npz"))
+    out, lse = None, None
+    for i in range(3):
+        bo = torch.from_numpy(z[f"block_out{i}"]).to(DEV)
+        if i == 1:
+            bo = bo.to(torch.bfloat16)
+        out, lse = fm.update_out_and_lse(out, lse, bo, torch.from_numpy(z[f"block_lse{i}"]).to(DEV))
+        assert (out.cpu() - torch.from_numpy(z[f"out{i}"])).abs().max() <= 2e-6
+        assert (lse.cpu() - torch.from_numpy(z[f"lse{i}"])).abs().max() <= 2e-6
+
+
+def test_merge_handles_empty_sides():
+    o1 = torch.randn(6, 16, device=DEV)
+    o2 = torch.randn(6, 16, device=DEV).bfloat16()
+    l1 = torch.tensor([0.5, -math.inf, 1.0, -math.inf, 3.0, -2.0], device=DEV)
+    l2 = torch.tensor([-math.inf, 0.25, 2.0, -math.inf, -1.0, -2.0], device=DEV)
+    out, lse = fm.merge(o1, l1, o2, l2)
+    ro, rl = O.merge_exact(o1.cpu(), l1.cpu(), o2.cpu(), l2.cpu())
+    keep = torch.isfinite(rl)
+    assert torch.allclose(out.cpu()[keep], ro[keep], atol=1e-6)
+    assert torch.equal(torch.isinf(lse.cpu()), torch.isinf(rl)) and torch.allclose(lse.cpu()[keep], rl[keep], atol=1e-6)
+    assert torch.equal(o1, o1) and out.data_ptr() != o1.data_ptr()      # merge() leaves its inputs alone

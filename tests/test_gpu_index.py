@@ -1,0 +1,188 @@
+"""GPU parity of index build, query hashing, k-means and the Memory object against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+import fast_memory_b200 as fm
+from fast_memory_b200 import synth
+from oracle import oracle as O
+from tests.util import assert_attn_close, oracle_for_sampled_queries, tables_equal_as_sets
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [16, 64, 128, 256])
+def test_projection_is_bit_exact(dtype, d):
+    g = torch.Generator().manual_seed(d)
+    A = torch.randn(70, d, generator=g).to(dtype)
+    K = torch.randn(333, d, generator=g).to(dtype)
+    Y = fm.project(A.to(DEV), K.to(DEV)).cpu().numpy()
+    assert np.array_equal(Y, O.project(A, K))
+
+
+@pytest.mark.parametrize("N,Z", [(1, 1), (100, 100), (1000, 1), (5000, 257), (70000, 2048), (4096, 4095)])
+def test_topz_select_is_bit_exact(N, Z):
+    g = torch.Generator().manual_seed(N + Z)
+    Y = torch.randn(9, N, generator=g)
+    got = fm.topz_select(Y.to(DEV), Z).cpu().numpy()
+    assert np.array_equal(got, O.topz(Y, Z))
+    # heavy ties (values on a coarse grid, signed zeros): lower index wins
+    Yt = (torch.round(Y * 2) / 2) * torch.where(torch.rand(9, N, generator=g) < 0.5, -1.0, 1.0)
+    got = fm.topz_select(Yt.to(DEV), Z, index_base=7).cpu().numpy()
+    assert np.array_equal(got, O.topz(Yt, Z) + 7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_hash_rows_bit_exact_multi_segment(dtype):
+    g = torch.Generator().manual_seed(11)
+    d = 64
+    Cs, Ss = [5, 64, 130], [70, 1, 200]
+    A = torch.randn(sum(Cs), d, generator=g).to(dtype)
+    X = torch.randn(sum(Ss), d, generator=g).to(dtype)
+    xb = torch.tensor([0, 70, 71, 271], dtype=torch.int32)
+    cb = torch.tensor([0, 5, 69, 199], dtype=torch.int32)
+    h = fm.hash_rows(X.to(DEV), A.to(DEV), xb.to(DEV), cb.to(DEV), max(Ss)).cpu().numpy()
+    for s in range(3):
+        ref = O.query_hash(A[cb[s]:cb[s + 1]][None], X[xb[s]:xb[s + 1]][None])[0]
+        assert np.array_equal(h[xb[s]:xb[s + 1]], ref)
+    # duplicated centroids: the first maximum wins
+    A2 = torch.cat([A[:5], A[:5]], 0)
+    h2 = fm.hash_rows(X[:70].to(DEV), A2.to(DEV)).cpu().numpy()
+    assert (h2 < 5).all()
+
+
+def test_group_rows_is_a_valid_counting_sort():
+    g = torch.Generator().manual_seed(2)
+    C, n = 37, 5000
+    h = torch.randint(C, (n,), generator=g).int()
+    off, perm = fm.group_rows(h.to(DEV), C)
+    off, perm = off.cpu(), perm.cpu().long()
+    assert off[0] == 0 and off[-1] == n and torch.equal(off[1:] - off[:-1], torch.bincount(h.long(), minlength=C).int())
+    assert torch.equal(torch.sort(perm).values, torch.arange(n))
+    for c in range(C):
+        assert (h[perm[off[c]:off[c + 1]]] == c).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kmeans_bit_exact(dtype):
+    g = torch.Generator().manual_seed(9)
+    d, C, n = 64, 16, 3000
+    cent = torch.nn.functional.normalize(torch.randn(C, d, generator=g), dim=-1)
+    X = (cent[torch.randint(C, (n,), generator=g)] + 0.3 * torch.randn(n, d, generator=g)).to(dtype)
+    for iters in (0, 1, 3):
+        A, c32 = fm.kmeans_projection(X.to(DEV), X[:C].to(DEV), iters, [0, n], [0, C])
+        ref = O.spherical_kmeans(X, X[:C], iters)
+        assert torch.equal(A.cpu(), ref), f"iters={iters}: {(A.cpu().float() - ref.float()).abs().max()}"
+    assert np.array_equal(fm.unit_rows(X.to(DEV)).cpu().numpy(), O.unit_rows(X))
+
+
+def _check_memory_tables(mem, A_cpu, k_cpu, Z):
+    for h in range(mem.n_heads):
+        ref = O.topz(O.project(A_cpu[h], k_cpu[h]), Z)
+        ok, why = tables_equal_as_sets(mem.table_of(h).cpu().numpy(), ref)
+        assert ok, f"head {h}: {why}"
+
+
+def test_cfg1_end_to_end():
+    """BASELINE config 1 in full: k-means A, index, hash, attention; every stage against the oracle."""
+    cfg = synth.config("cfg1")
+    q, k, v = synth.make(cfg, seed=0)
+    sm = cfg.d ** -0.5
+    mem = fm.Memory.build(k.to(DEV), v.to(DEV), n_buckets=cfg.n_buckets, bucket_size=cfg.bucket_size,
+                          kmeans_iters=cfg.kmeans_iters, kmeans_init=q.to(DEV))
+    A_ref = O.spherical_kmeans(k[0], q[0, :cfg.n_buckets], cfg.kmeans_iters)
+    assert torch.equal(mem.A.cpu(), A_ref)
+    _check_memory_tables(mem, A_ref[None], k, cfg.bucket_size)
+    hashes = mem.hash_queries(q.to(DEV)).cpu()
+    assert np.array_equal(hashes.numpy(), O.query_hash(A_ref[None], q))
+    o, lse = mem.query(q.to(DEV), sm)
+    table = torch.from_numpy(O.build_table(A_ref[None], k, cfg.bucket_size)).long()
+    counts = torch.full((1, cfg.n_buckets), table.shape[-1])
+    o_ref, lse_ref = O.hashed_attention_dense(q, k, v, table, counts, hashes.long(), sm)
+    assert_attn_close(o, lse, o_ref, lse_ref, torch.float32)
+    o_g, lse_g = O.hashed_attention(q, k, v, table.reshape(-1), counts, hashes.long(), sm)
+    assert_attn_close(o, lse, o_g, lse_g, torch.float32)
+
+
+@pytest.mark.parametrize("name,H,N,S", [("cfg2", 2, 16384, 1024), ("cfg3", 2, 32768, 16), ("cfg5", 1, 65536, 512)])
+def test_cut_down_configs(name, H, N, S):
+    """The bf16 configurations at reduced key counts / heads, same distributions, C and Z scaled with N."""
+    cfg = synth.config(name)
+    scale = N / (cfg.n_keys // cfg.shards)
+    C, Z = max(16, int(cfg.n_buckets * scale ** 0.5) // 16 * 16), max(32, int(cfg.bucket_size * scale))
+    q, k, v = synth.make(cfg, seed=3, kv_heads=H, n_keys=N, n_queries=S)
+    sm = cfg.d ** -0.5
+    mem = fm.Memory.build(k.to(DEV), v.to(DEV), n_buckets=C, bucket_size=Z, kmeans_iters=2)
+    A = mem.A.reshape(H, C, cfg.d).cpu()
+    for h in range(H):
+        assert torch.equal(A[h], O.spherical_kmeans(k[h], k[h, :C], 2))
+    _check_memory_tables(mem, A, k, Z)
+    qd = q.to(DEV)
+    hashes = mem.hash_queries(qd).cpu()
+    G = cfg.q_groups
+    ref_h = O.query_hash(A, q.reshape(H, G * S, cfg.d)).reshape(H * G, S)
+    assert np.array_equal(hashes.numpy(), ref_h)
+    o, lse = mem.query(qd, sm)
+    table = torch.stack([mem.table_of(h) for h in range(H)]).cpu().long()
+    counts = torch.full((H, C), table.shape[-1])
+    o_ref, lse_ref = O.hashed_attention(q.reshape(H, G * S, cfg.d), k, v, table.reshape(-1), counts,
+                                        hashes.reshape(H, G * S).long(), sm)
+    assert_attn_close(o.reshape(H, G * S, -1), lse.reshape(H, G * S), o_ref, lse_ref, cfg.dtype)
+
+
+def test_varlen_memory_matches_per_sequence_calls():
+    """cfg4 layout cut down: packed keys/queries with cu_seqlens equal independent per-sequence memories."""
+    cfg = synth.config("cfg4")
+    seq = [3000, 700, 5000]
+    H, S = 2, 64
+    q, k, v, cu_q, cu_k = synth.make_varlen(cfg, seed=5, kv_heads=H, seq_keys=seq, n_queries=S)
+    Cs = [synth.varlen_buckets(n) for n in seq]
+    Zs = [synth.varlen_bucket_size(n) for n in seq]
+    sm = cfg.d ** -0.5
+    mem = fm.Memory.build(k.to(DEV), v.to(DEV), n_buckets=Cs, bucket_size=Zs, kmeans_iters=1, cu_seqlens_k=cu_k)
+    o, lse = mem.query(q.to(DEV), sm, cu_seqlens_q=cu_q)
+    for s, n in enumerate(seq):
+        ks, vs = k[:, cu_k[s]:cu_k[s + 1]].contiguous(), v[:, cu_k[s]:cu_k[s + 1]].contiguous()
+        qs = q[:, cu_q[s]:cu_q[s + 1]].contiguous()
+        A = torch.stack([O.spherical_kmeans(ks[h], ks[h, :Cs[s]], 1) for h in range(H)])
+        for h in range(H):
+            assert torch.equal(mem.projection_of(h, s).cpu(), A[h])
+            ok, why = tables_equal_as_sets(mem.table_of(h, s).cpu().numpy(), O.topz(O.project(A[h], ks[h]), Zs[s]))
+            assert ok, why
+        table = torch.from_numpy(O.build_table(A, ks, Zs[s])).long()
+        hashes = torch.from_numpy(O.query_hash(A, qs)).long()
+        o_ref, lse_ref = O.hashed_attention(qs, ks, vs, table.reshape(-1), torch.full((H, Cs[s]), table.shape[-1]), hashes, sm)
+        assert_attn_close(o[:, cu_q[s]:cu_q[s + 1]], lse[:, cu_q[s]:cu_q[s + 1]], o_ref, lse_ref, cfg.dtype)
+    # and the same through the single-sequence API of the drop-in
+    m0 = fm.Memory.build(k[:, :seq[0]].contiguous().to(DEV), v[:, :seq[0]].contiguous().to(DEV), n_buckets=Cs[0],
+                         bucket_size=Zs[0], kmeans_iters=1)
+    o0, l0 = m0.query(q[:, :S].contiguous().to(DEV), sm)
+    assert torch.equal(o0, o[:, :S]) and torch.equal(l0, lse[:, :S])
+
+
+def test_attention_hash_dropin_with_key_range():
+    """tk:275-286 with its key-range filter as an argument."""
+    g = torch.Generator().manual_seed(8)
+    B, S, N, C, Z, d = 2, 200, 4096, 16, 256, 64
+    q = torch.randn(B, S, d, generator=g).bfloat16()
+    k = torch.randn(B, N, d, generator=g).bfloat16()
+    v = torch.randn(B, N, d, generator=g).bfloat16()
+    cent = torch.randn(B, C, d, generator=g).bfloat16()
+    o, lse = fm.attention_hash(q.to(DEV), k.to(DEV), v.to(DEV), cent.to(DEV), Z, 0.1, key_range=(1024, 3072))
+    table = torch.from_numpy(O.build_table(cent, k, Z)).long()
+    m = (table >= 1024) & (table < 3072)
+    hashes = torch.from_numpy(O.query_hash(cent, q)).long()
+    o_ref, lse_ref = O.hashed_attention(q, k, v, table[m], m.sum(-1), hashes, 0.1)
+    assert (o.float().cpu() - o_ref.float()).abs().max() <= 2e-2
+    assert (lse.float().cpu() - O.dropin_lse(lse_ref, torch.bfloat16).float()).abs().max() <= 4e-2   # bf16 LSE (tk:111)
+
+
+def test_state_dict_round_trip():
+    cfg = synth.config("cfg1")
+    q, k, v = synth.make(cfg, seed=2)
+    mem = fm.Memory.build(k.to(DEV), v.to(DEV), n_buckets=32, bucket_size=100, kmeans_iters=1)
+    m2 = fm.Memory.from_state_dict(mem.state_dict(), k.to(DEV), v.to(DEV))
+    a, b = mem.query(q.to(DEV), 0.2), m2.query(q.to(DEV), 0.2)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
