@@ -224,6 +224,9 @@ def attention_hash_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     assert v.is_contiguous()
     assert k.stride() == v.stride()
     L.require_cuda(q, k, v, k_hashes, k_hash_counts, q_hashes)
+    if q.numel() == 0:
+        lse_dtype = torch.float32 if return_fp32_lse else q.dtype
+        return torch.empty_like(q), q.new_empty(q.shape[:-1], dtype=lse_dtype)
     # the longest bucket sizes the work split; like the reference wrapper (unique_consecutive, tk:81)
     # this reads one number back from the device
     max_len = int(k_hash_counts.max().item()) if k_hash_counts.numel() else 0
