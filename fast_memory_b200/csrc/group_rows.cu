@@ -3,6 +3,8 @@
 // (triton_kernel.py:75-88); empty buckets simply get an empty range.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace fm {
 
 __device__ __forceinline__ int global_bucket(const int32_t *__restrict__ hash, int r, int n_seg,
@@ -78,6 +80,35 @@ __global__ void bucket_scatter_kernel(const int32_t *__restrict__ hash, int n_ro
     }
 }
 
+// ---- scratch that lives in the library image, for callers that must not allocate ---------------------
+// Counts and cursors of fm_group_rows_static.  Every GPU that loads the library carries these 512 KiB
+// until the process exits.
+constexpr int kStaticMaxBuckets = 65536;
+static __device__ __align__(256) int32_t g_static_group_scratch[2 * kStaticMaxBuckets];
+
+// Device address of g_static_group_scratch on the current device.  In host code the symbol's name is
+// only a handle for the runtime, never a pointer a kernel may be given, so the address is asked for
+// once per device (with that device current) and remembered.
+static int static_group_scratch(int32_t **out)
+{
+    static std::mutex mu;
+    static int32_t *cached[64];
+    int dev = -1;
+    FM_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_error("fm_group_rows_static: device ordinal %d out of range", dev);
+        return FM_ERR_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void *p = nullptr;
+        FM_CUDA_OK(cudaGetSymbolAddress(&p, g_static_group_scratch));
+        cached[dev] = static_cast<int32_t *>(p);
+    }
+    *out = cached[dev];
+    return FM_OK;
+}
+
 }  // namespace fm
 
 extern "C" size_t fm_group_rows_workspace_bytes(int64_t n_rows, int64_t total_buckets)
@@ -102,6 +133,45 @@ extern "C" int fm_group_rows(const int32_t *hash, int64_t n_rows, int64_t total_
     cudaStream_t st = (cudaStream_t)stream;
     int32_t *counts = (int32_t *)workspace;
     int32_t *cursor = (int32_t *)((char *)workspace + align_up(size_t(total_buckets) * 4, 256));
+    FM_CUDA_OK(cudaMemsetAsync(counts, 0, size_t(total_buckets) * 4, st));
+    int blocks = (int)std::min<int64_t>(std::max<int64_t>(ceil_div(n_rows, 256), 1), 4 * sm_count());
+    if (n_rows > 0) {
+        bucket_histogram_kernel<<<blocks, 256, 0, st>>>(hash, (int)n_rows, (int)total_buckets, n_seg, seg_xb, seg_cb, counts);
+        FM_LAUNCHED("bucket_histogram_kernel");
+    }
+    exclusive_scan_kernel<<<1, 1024, 0, st>>>(counts, (int)total_buckets, group_off, cursor);
+    FM_LAUNCHED("exclusive_scan_kernel");
+    if (n_rows > 0) {
+        bucket_scatter_kernel<<<blocks, 256, 0, st>>>(hash, (int)n_rows, (int)total_buckets, n_seg, seg_xb, seg_cb, cursor, perm);
+        FM_LAUNCHED("bucket_scatter_kernel");
+    }
+    return FM_OK;
+}
+
+extern "C" int64_t fm_group_rows_static_max_buckets(void) { return fm::kStaticMaxBuckets; }
+
+extern "C" int fm_group_rows_static(const int32_t *hash, int64_t n_rows, int64_t total_buckets, int n_seg,
+                                    const int32_t *seg_xb, const int32_t *seg_cb, int32_t *group_off, int32_t *perm,
+                                    fm_stream_t stream)
+{
+    using namespace fm;
+    FM_REQUIRE(group_off && (n_rows == 0 || (hash && perm)), "fm_group_rows_static: null pointer");
+    FM_REQUIRE(n_rows >= 0 && total_buckets > 0 && n_seg >= 1, "fm_group_rows_static: bad sizes");
+    FM_REQUIRE(n_rows < (int64_t(1) << 31), "fm_group_rows_static: sizes exceed int32");
+    FM_REQUIRE((seg_xb == nullptr) == (seg_cb == nullptr), "fm_group_rows_static: pass both segment arrays or neither");
+    if (total_buckets > kStaticMaxBuckets) {
+        set_error("fm_group_rows_static: %lld buckets exceed the built-in scratch (%d buckets); use fm_group_rows "
+                  "with a caller-provided workspace", (long long)total_buckets, kStaticMaxBuckets);
+        return FM_ERR_UNSUPPORTED;
+    }
+    int32_t *scratch = nullptr;
+    int rc = static_group_scratch(&scratch);
+    if (rc != FM_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    int32_t *counts = scratch;
+    int32_t *cursor = scratch + kStaticMaxBuckets;
+    // the array keeps whatever the previous call left: the counts must start at zero (the cursors are
+    // overwritten by the scan)
     FM_CUDA_OK(cudaMemsetAsync(counts, 0, size_t(total_buckets) * 4, st));
     int blocks = (int)std::min<int64_t>(std::max<int64_t>(ceil_div(n_rows, 256), 1), 4 * sm_count());
     if (n_rows > 0) {

@@ -75,6 +75,28 @@ int fm_group_rows(const int32_t *hash, int64_t n_rows, int64_t total_buckets, in
                   void *workspace, size_t workspace_bytes, fm_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * fm_group_rows for callers that cannot allocate device memory.  This entry point has no counterpart
+ * in the reference: it exists for hosts that get their buffers handed to them and may not call
+ * cudaMalloc themselves - code running inside a fixed memory plan or arena, a serving process whose
+ * memory budget is pinned at start-up, a plugin that runs while the owning framework forbids new
+ * allocations.  Inputs and outputs are as for fm_group_rows, but there is no workspace argument:
+ * the per-bucket counts and cursors live in an array that is part of the library image
+ * (2 x 65536 x 4 bytes = 512 KiB, held by every GPU that loads the library until the process exits).
+ *   - total_buckets above fm_group_rows_static_max_buckets() (65536) is refused with
+ *     FM_ERR_UNSUPPORTED; use fm_group_rows there.
+ *   - Nothing is allocated or freed, here or in any routine it calls.
+ *   - The first call on each device looks up the array's device address (a one-time, per-device
+ *     set-up inside the call); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents (the call
+ *     clears what it needs).  Two calls that overlap on the GPU - different streams, or threads -
+ *     race on it; serialise them.
+ * ------------------------------------------------------------------------------------------- */
+int64_t fm_group_rows_static_max_buckets(void);
+int fm_group_rows_static(const int32_t *hash, int64_t n_rows, int64_t total_buckets, int n_seg,
+                         const int32_t *seg_xb, const int32_t *seg_cb, int32_t *group_off, int32_t *perm,
+                         fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Hashed attention forward: every query attends to the keys listed in its bucket.
  * Replaces: torch op notbad::attention_hash_varlen and its Triton kernel, tk:16-41, 135-272 (the
  * gathers through the table, base-2 online softmax, P rounded to the q dtype before P.V), without
