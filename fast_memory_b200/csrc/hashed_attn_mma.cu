@@ -1,20 +1,357 @@
-// Tensor-core hashed attention for 16-bit inputs (placeholder dispatch until the kernel lands).
+// Tensor-core hashed attention for 16-bit inputs (bf16 / fp16, head dim 64 or 128).
+//
+// The path is HBM-bound (arithmetic intensity ~ queries per bucket, far below the ridge), so the kernel
+// is built around the gather: each CTA streams the K and V rows of its bucket chunk through a 3-stage
+// cp.async pipeline of 64-key tiles (16-byte pieces, XOR-swizzled rows), keeping ~64 KB of row fetches in
+// flight, and the math rides along on mma.sync m16n8k16:
+//   * a work item holds <= 16 queries = one MMA row tile; the 4 warps split every key tile four ways
+//     (16 keys each), so all warps do equal work however few queries the bucket has;
+//   * S = Q K^T from ldmatrix'd K rows, base-2 online softmax per warp in registers, P rounded to the
+//     input dtype and fed straight back as the A operand of P V (V through ldmatrix.trans);
+//   * at the end of the item the four (m, l, acc) states are folded through shared memory and written out
+//     through the grouping permutation (or as a partial when the bucket is split over CTAs).
+// Rounding points follow the reference kernel (triton_kernel.py:248-263).
 #include "attn_common.cuh"
 
 namespace fm {
 
-bool attn_mma_supported(int dtype, int d)
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kTK = 64;                     // keys per tile
+constexpr int kStages = 3;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid)
 {
-    (void)dtype;
-    (void)d;
-    return false;
+    int sz = valid ? 16 : 0;                 // src-size 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <typename T> __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi)
+{
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+template <int D> struct MmaCfg {
+    static constexpr int CPR = D / 8;                           // 16-byte chunks per row
+    static constexpr int ROWS_PER_PASS = kThreads / CPR;        // rows covered by one sweep of the CTA
+    static constexpr int PASSES = kTK / ROWS_PER_PASS;          // copies per thread per matrix per tile
+    static constexpr int TILE_BYTES = kTK * D * 2;              // one K (or V) tile
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int ACC_LD = D + 4;                        // combine buffer row stride (floats)
+    static constexpr size_t smem = size_t(kStages) * STAGE_BYTES + kStages * kTK;   // tiles + validity flags
+    static_assert(4 * kQB * ACC_LD * 4 + 4 * kQB * 8 <= kStages * STAGE_BYTES, "combine buffer must fit in the tile stages");
+};
+
+// byte offset of 16-byte chunk `c` of row `j` inside a swizzled tile
+template <int D> __device__ __forceinline__ uint32_t swz(int j, int c) { return uint32_t(j * (D * 2) + ((c ^ (j & 7)) << 4)); }
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads, 2)
+attn_mma_kernel(AttnParams p)
+{
+    using C = MmaCfg<D>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char *flags = smem + kStages * C::STAGE_BYTES;     // [kStages][kTK] 1 = key row is live
+    __shared__ int s_item;
+
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int g = lane >> 2, tq = lane & 3;
+    const T *qg = reinterpret_cast<const T *>(p.q);
+    const char *kg = reinterpret_cast<const char *>(p.k);
+    const char *vg = reinterpret_cast<const char *>(p.v);
+    const int n_items = min(p.counters[0], p.max_items);
+    const uint32_t smem_base = smem_u32(smem);
+    const int my_c = t % C::CPR;                                 // chunk column this thread copies
+    const int my_r = t / C::CPR;                                 // first row this thread copies
+
+    for (;;) {
+        __syncthreads();
+        if (t == 0) s_item = atomicAdd(&p.counters[1], 1);
+        __syncthreads();
+        const int item = s_item;
+        if (item >= n_items) break;
+        const int4 it = p.items[item];
+        const int gb = it.x, q_begin = it.y, kc = it.z, nkc = it.w;
+        const int nq = min(kQB, p.group_off[gb + 1] - q_begin);
+        const int64_t kb = p.bucket_off[gb];
+        const int64_t len = p.bucket_off[gb + 1] - kb;
+        const int64_t k0 = int64_t(kc) * p.key_chunk;
+        const int chunk_len = int(min(len - k0, int64_t(p.key_chunk)));
+        const int n_tiles = chunk_len > 0 ? (chunk_len + kTK - 1) / kTK : 0;
+        const int64_t kbase = p.bucket_kbase ? p.bucket_kbase[gb] : 0;
+        const int64_t tbl0 = kb + k0;
+
+        // ---- Q fragments (A operand), straight from global through the permutation ---------------------
+        uint32_t qf[D / 16][4];
+        {
+            const int r0 = g, r1 = g + 8;
+            const T *q0 = r0 < nq ? qg + size_t(p.perm[q_begin + r0]) * D : nullptr;
+            const T *q1 = r1 < nq ? qg + size_t(p.perm[q_begin + r1]) * D : nullptr;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const int c = ks * 16 + tq * 2;
+                qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + c) : 0u;
+                qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + c) : 0u;
+                qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + c + 8) : 0u;
+                qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + c + 8) : 0u;
+            }
+        }
+
+        // ---- gather pipeline -----------------------------------------------------------------------------
+        int64_t rows[C::PASSES];                                // key rows this thread copies for the next tile to issue
+        auto load_rows = [&](int tile) {
+#pragma unroll
+            for (int i = 0; i < C::PASSES; ++i) {
+                const int j = tile * kTK + my_r + i * C::ROWS_PER_PASS;
+                int64_t row = -1;
+                if (tile < n_tiles && j < chunk_len) {
+                    row = load_index(p.table, p.idx_bytes, tbl0 + j) + kbase;
+                    if (row < 0 || row >= p.n_k_rows) row = -1;
+                }
+                rows[i] = row;
+            }
+        };
+        auto issue = [&](int tile) {
+            if (tile < n_tiles) {
+                const int st = tile % kStages;
+                const uint32_t kdst = smem_base + st * C::STAGE_BYTES;
+                const uint32_t vdst = kdst + C::TILE_BYTES;
+#pragma unroll
+                for (int i = 0; i < C::PASSES; ++i) {
+                    const int j = my_r + i * C::ROWS_PER_PASS;
+                    const bool ok = rows[i] >= 0;
+                    const size_t off = ok ? size_t(rows[i]) * (D * 2) + my_c * 16 : 0;
+                    cp_async16(kdst + swz<D>(j, my_c), kg + off, ok);
+                    cp_async16(vdst + swz<D>(j, my_c), vg + off, ok);
+                    if (my_c == 0) flags[st * kTK + j] = ok ? 1 : 0;
+                }
+            }
+            cp_async_commit();
+        };
+        load_rows(0);
+#pragma unroll
+        for (int s = 0; s < kStages - 1; ++s) {
+            issue(s);
+            load_rows(s + 1);
+        }
+
+        float m_run[2] = {-INFINITY, -INFINITY};
+        float l_run[2] = {1.f, 1.f};
+        float acc[D / 8][4];
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+
+        for (int tile = 0; tile < n_tiles; ++tile) {
+            cp_async_wait<kStages - 2>();
+            __syncthreads();                                     // tile landed; the stage refilled below is free
+            issue(tile + kStages - 1);
+            load_rows(tile + kStages);
+            const int st = tile % kStages;
+            const uint32_t ks_base = smem_base + st * C::STAGE_BYTES;
+            const uint32_t vs_base = ks_base + C::TILE_BYTES;
+            const int wk = warp * 16;                            // this warp's 16 keys of the tile
+
+            // S = Q K^T for 16 queries x 16 keys
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+                const int j = wk + (lane & 7) + ((lane >> 4) << 3);
+                const int c = ks * 2 + ((lane >> 3) & 1);
+                uint32_t b[4];
+                ldmatrix_x4(b, ks_base + swz<D>(j, c));
+                mma16816<T>(s[0], qf[ks], b[0], b[1]);
+                mma16816<T>(s[1], qf[ks], b[2], b[3]);
+            }
+            // scale, mask, online softmax (rows g and g + 8; this thread's keys: wk + 8 n + 2 tq + {0, 1})
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int jk = wk + n * 8 + tq * 2;
+                const bool ok0 = flags[st * kTK + jk] != 0, ok1 = flags[st * kTK + jk + 1] != 0;
+                s[n][0] = ok0 ? s[n][0] * p.scale2 : -INFINITY;
+                s[n][1] = ok1 ? s[n][1] * p.scale2 : -INFINITY;
+                s[n][2] = ok0 ? s[n][2] * p.scale2 : -INFINITY;
+                s[n][3] = ok1 ? s[n][3] * p.scale2 : -INFINITY;
+                mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
+            }
+            uint32_t pa[4];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                float alpha = 1.f, p00 = 0.f, p01 = 0.f, p10 = 0.f, p11 = 0.f;
+                if (m_new > -INFINITY) {
+                    alpha = exp2f(m_run[r] - m_new);
+                    p00 = exp2f(s[0][2 * r] - m_new);
+                    p01 = exp2f(s[0][2 * r + 1] - m_new);
+                    p10 = exp2f(s[1][2 * r] - m_new);
+                    p11 = exp2f(s[1][2 * r + 1] - m_new);
+                }
+                float sum = (p00 + p01) + (p10 + p11);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                l_run[r] = l_run[r] * alpha + sum;
+                m_run[r] = m_new;
+                pa[r] = pack2<T>(p00, p01);                      // keys 0-7 of the warp's slice
+                pa[2 + r] = pack2<T>(p10, p11);                  // keys 8-15
+#pragma unroll
+                for (int n = 0; n < D / 8; ++n) {
+                    acc[n][2 * r] *= alpha;
+                    acc[n][2 * r + 1] *= alpha;
+                }
+            }
+            // acc += P V  (k = the warp's 16 keys, n = head dim)
+#pragma unroll
+            for (int n2 = 0; n2 < D / 16; ++n2) {
+                // matrices: (keys 0-7, d n2*16 + 0-7), (keys 8-15, same d), (keys 0-7, d + 8), (keys 8-15, d + 8)
+                const int j = wk + (lane & 7) + (((lane >> 3) & 1) << 3);
+                const int c = n2 * 2 + (lane >> 4);
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vs_base + swz<D>(j, c));
+                mma16816<T>(acc[2 * n2], pa, b[0], b[1]);
+                mma16816<T>(acc[2 * n2 + 1], pa, b[2], b[3]);
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();                                         // all tiles consumed: the stages become the combine buffer
+
+        // ---- fold the four warps' states ---------------------------------------------------------------------
+        float *acc_s = reinterpret_cast<float *>(smem);          // [4][kQB][ACC_LD]
+        float *ml_s = acc_s + 4 * kQB * C::ACC_LD;                // [4][kQB][2]
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            float *a0 = acc_s + (warp * kQB + g) * C::ACC_LD + n * 8 + tq * 2;
+            *reinterpret_cast<float2 *>(a0) = make_float2(acc[n][0], acc[n][1]);
+            *reinterpret_cast<float2 *>(a0 + 8 * C::ACC_LD) = make_float2(acc[n][2], acc[n][3]);
+        }
+        if (tq == 0) {
+            ml_s[(warp * kQB + g) * 2] = m_run[0];
+            ml_s[(warp * kQB + g) * 2 + 1] = l_run[0];
+            ml_s[(warp * kQB + g + 8) * 2] = m_run[1];
+            ml_s[(warp * kQB + g + 8) * 2 + 1] = l_run[1];
+        }
+        __syncthreads();
+        {
+            constexpr int TPQ = kThreads / kQB;                  // threads per query (8)
+            constexpr int CPT = D / TPQ;                         // columns per thread (16 or 8)
+            const int qi = t / TPQ, c0 = (t % TPQ) * CPT;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, ml_s[(w * kQB + qi) * 2]);
+            float wgt[4], Lsum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float mw = ml_s[(w * kQB + qi) * 2];
+                wgt[w] = mw > -INFINITY ? exp2f(mw - M) : 0.f;
+                // a warp that saw no key still carries its initial l = 1 with m = -inf: weight 0 drops it
+                Lsum += wgt[w] * ml_s[(w * kQB + qi) * 2 + 1];
+            }
+            if (M == -INFINITY) Lsum = 1.f;                       // empty bucket: o = 0, lse = -inf
+            float o[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) o[c] = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float *src = acc_s + (w * kQB + qi) * C::ACC_LD + c0;
+#pragma unroll
+                for (int c = 0; c < CPT; c += 4) {
+                    float4 v4 = *reinterpret_cast<const float4 *>(src + c);
+                    o[c] += wgt[w] * v4.x;
+                    o[c + 1] += wgt[w] * v4.y;
+                    o[c + 2] += wgt[w] * v4.z;
+                    o[c + 3] += wgt[w] * v4.w;
+                }
+            }
+            if (qi < nq) {
+                if (nkc == 1) {
+                    const size_t row = p.perm[q_begin + qi];
+                    T *orow = reinterpret_cast<T *>(p.o) + row * D + c0;
+                    const float inv = 1.f / Lsum;
+#pragma unroll
+                    for (int c = 0; c < CPT; c += 8) {
+                        uint4 pk;
+                        pk.x = pack2<T>(o[c] * inv, o[c + 1] * inv);
+                        pk.y = pack2<T>(o[c + 2] * inv, o[c + 3] * inv);
+                        pk.z = pack2<T>(o[c + 4] * inv, o[c + 5] * inv);
+                        pk.w = pack2<T>(o[c + 6] * inv, o[c + 7] * inv);
+                        *reinterpret_cast<uint4 *>(orow + c) = pk;
+                    }
+                    if ((t % TPQ) == 0) p.lse[row] = (M + log2f(Lsum)) * 0.6931471805599453f;
+                } else {
+                    float *dst = p.partials + (size_t(q_begin + qi) * p.nkc_max + kc) * (D + 2);
+#pragma unroll
+                    for (int c = 0; c < CPT; c += 2) *reinterpret_cast<float2 *>(dst + c0 + c) = make_float2(o[c], o[c + 1]);
+                    if ((t % TPQ) == 0) {
+                        dst[D] = M;
+                        dst[D + 1] = Lsum;
+                        if (kc == 0) p.qparts[q_begin + qi] = nkc;
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int D>
+int launch_mma(const AttnParams &p, int grid, cudaStream_t st)
+{
+    const size_t smem = MmaCfg<D>::smem;
+    FM_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attn_mma_kernel<T, D><<<grid, kThreads, smem, st>>>(p);
+    FM_LAUNCHED("attn_mma_kernel");
+    return FM_OK;
+}
+
+}  // namespace
+
+bool attn_mma_supported(int dtype, int d) { return (dtype == FM_BF16 || dtype == FM_F16) && (d == 64 || d == 128); }
 
 int launch_attn_mma(const AttnParams &p, int dtype, int d, int grid, cudaStream_t st)
 {
-    (void)p; (void)dtype; (void)d; (void)grid; (void)st;
-    set_error("tensor-core attention kernel not built for this shape");
-    return FM_ERR_UNSUPPORTED;
+    if (dtype == FM_BF16) return d == 128 ? launch_mma<__nv_bfloat16, 128>(p, grid, st) : launch_mma<__nv_bfloat16, 64>(p, grid, st);
+    return d == 128 ? launch_mma<__half, 128>(p, grid, st) : launch_mma<__half, 64>(p, grid, st);
 }
 
 }  // namespace fm
