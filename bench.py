@@ -132,6 +132,8 @@ def run_ours(args, rank, world):
     cfg = synth.config(args.workload)
     sm_scale = cfg.d ** -0.5
     esize = 2 if cfg.dtype != torch.float32 else 4
+    if args.kv_heads:                      # cut-down copy of the workload (fewer heads) for profiler captures
+        cfg.kv_heads = args.kv_heads
     q, k, v = synth.make(cfg, seed=args.seed + rank, device=dev)
     Hq, S, d = q.shape
     n_queries = Hq * S
@@ -254,7 +256,7 @@ def run_ours(args, rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if cfg.dtype == torch.bfloat16 else str(cfg.dtype).replace("torch.", ""),
         "data": "synthetic",
-        "config": {"workload": f"{cfg.name}: {H} KV heads x {cfg.q_groups} groups, d={d}, N={N} keys/head, C={cfg.n_buckets}, "
+        "config": {"workload": ("CUT-DOWN " if args.kv_heads else "") + f"{cfg.name}: {H} KV heads x {cfg.q_groups} groups, d={d}, N={N} keys/head, C={cfg.n_buckets}, "
                                f"Z={cfg.bucket_size}, {S} queries/head" + (f", merged with a causal local window of {cfg.local_window}" if cfg.local_window else ""),
                    "parallelism": f"independent memories per GPU x{world}" if world > 1 else "single GPU",
                    "l2": f"inputs larger than L2 ({attn_bytes / 1e9:.2f} GB gathered per step)",
@@ -361,8 +363,12 @@ def main():
     ap.add_argument("--build-steps", type=int, default=2)
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kv-heads", type=int, default=0,
+                    help="run a cut-down workload with this many KV heads (small case for profiler captures; "
+                         "not a benchmark number)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "ours" and not args.kv_heads:
+        args.warmup = max(args.warmup, 3)
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":

@@ -109,8 +109,9 @@ attn_simt_kernel(AttnParams p)
             if (t < kSimtTK) {
                 int64_t row = -1;
                 if (t < nk) {
+                    // entries outside [0, n_k_rows) are clamped: a malformed table never reads out of bounds
                     row = load_index(p.table, p.idx_bytes, kb + t0 + t) + kbase;
-                    if (row < 0 || row >= p.n_k_rows) row = -1;  // out-of-range entries contribute nothing
+                    row = min(max(row, int64_t(0)), p.n_k_rows - 1);
                 }
                 idx_s[t] = row;
             }
@@ -352,7 +353,8 @@ extern "C" int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, i
     FM_LAUNCHED("attn_plan_kernel");
 
     int rc;
-    const bool use_mma = attn_mma_supported(dtype, d);
+    // the tensor-core kernel tracks the row maximum before scaling, which needs a positive scale
+    const bool use_mma = attn_mma_supported(dtype, d) && sm_scale > 0.f;
     int grid = (int)std::min<int64_t>(L.max_items, int64_t(sms) * (use_mma ? 2 : 4));
     if (use_mma) rc = launch_attn_mma(p, dtype, d, grid, st);
     else if (dtype == FM_F32) rc = dispatch_simt<float>(p, d, grid, st);

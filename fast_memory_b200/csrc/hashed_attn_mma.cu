@@ -56,6 +56,14 @@ template <> __device__ __forceinline__ void mma16816<__half>(float (&c)[4], cons
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 2^x on the special-function unit (2 ulp; ex2(-inf) = 0)
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi)
 {
@@ -75,7 +83,7 @@ template <int D> struct MmaCfg {
     static constexpr int TILE_BYTES = kTK * D * 2;              // one K (or V) tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int ACC_LD = D + 4;                        // combine buffer row stride (floats)
-    static constexpr size_t smem = size_t(kStages) * STAGE_BYTES + kStages * kTK;   // tiles + validity flags
+    static constexpr size_t smem = size_t(kStages) * STAGE_BYTES;
     static_assert(4 * kQB * ACC_LD * 4 + 4 * kQB * 8 <= kStages * STAGE_BYTES, "combine buffer must fit in the tile stages");
 };
 
@@ -88,7 +96,6 @@ attn_mma_kernel(AttnParams p)
 {
     using C = MmaCfg<D>;
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char *flags = smem + kStages * C::STAGE_BYTES;     // [kStages][kTK] 1 = key row is live
     __shared__ int s_item;
 
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -135,17 +142,16 @@ attn_mma_kernel(AttnParams p)
         }
 
         // ---- gather pipeline -----------------------------------------------------------------------------
-        int64_t rows[C::PASSES];                                // key rows this thread copies for the next tile to issue
+        // Table entries are fetched one tile ahead and only looked at when their copies are issued, so the
+        // index load never stalls the warp.  Entries outside [0, n_k_rows) are clamped into range: a malformed
+        // table gives a meaningless result but never an out-of-bounds access.
+        int32_t rows[C::PASSES];
+        const int32_t row_max = int32_t(min(p.n_k_rows - 1, int64_t(0x7fffffff)));
         auto load_rows = [&](int tile) {
 #pragma unroll
             for (int i = 0; i < C::PASSES; ++i) {
                 const int j = tile * kTK + my_r + i * C::ROWS_PER_PASS;
-                int64_t row = -1;
-                if (tile < n_tiles && j < chunk_len) {
-                    row = load_index(p.table, p.idx_bytes, tbl0 + j) + kbase;
-                    if (row < 0 || row >= p.n_k_rows) row = -1;
-                }
-                rows[i] = row;
+                rows[i] = (tile < n_tiles && j < chunk_len) ? int32_t(load_index(p.table, p.idx_bytes, tbl0 + j)) : -1;
             }
         };
         auto issue = [&](int tile) {
@@ -153,14 +159,15 @@ attn_mma_kernel(AttnParams p)
                 const int st = tile % kStages;
                 const uint32_t kdst = smem_base + st * C::STAGE_BYTES;
                 const uint32_t vdst = kdst + C::TILE_BYTES;
+                const int live = chunk_len - tile * kTK;             // rows of this tile that exist
 #pragma unroll
                 for (int i = 0; i < C::PASSES; ++i) {
                     const int j = my_r + i * C::ROWS_PER_PASS;
-                    const bool ok = rows[i] >= 0;
-                    const size_t off = ok ? size_t(rows[i]) * (D * 2) + my_c * 16 : 0;
+                    const bool ok = j < live;
+                    const int32_t row = min(max(rows[i] + int32_t(kbase), 0), row_max);
+                    const size_t off = size_t(row) * (D * 2) + my_c * 16;
                     cp_async16(kdst + swz<D>(j, my_c), kg + off, ok);
                     cp_async16(vdst + swz<D>(j, my_c), vg + off, ok);
-                    if (my_c == 0) flags[st * kTK + j] = ok ? 1 : 0;
                 }
             }
             cp_async_commit();
@@ -202,44 +209,49 @@ attn_mma_kernel(AttnParams p)
                 mma16816<T>(s[0], qf[ks], b[0], b[1]);
                 mma16816<T>(s[1], qf[ks], b[2], b[3]);
             }
-            // scale, mask, online softmax (rows g and g + 8; this thread's keys: wk + 8 n + 2 tq + {0, 1})
-            float mx[2] = {-INFINITY, -INFINITY};
+            // mask (only the last tile can be partial), online softmax in the scaled base-2 domain
+            // (rows g and g + 8; this thread's keys: wk + 8 n + 2 tq + {0, 1})
+            if (tile == n_tiles - 1) {
+                const int live = chunk_len - tile * kTK;
 #pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const int jk = wk + n * 8 + tq * 2;
-                const bool ok0 = flags[st * kTK + jk] != 0, ok1 = flags[st * kTK + jk + 1] != 0;
-                s[n][0] = ok0 ? s[n][0] * p.scale2 : -INFINITY;
-                s[n][1] = ok1 ? s[n][1] * p.scale2 : -INFINITY;
-                s[n][2] = ok0 ? s[n][2] * p.scale2 : -INFINITY;
-                s[n][3] = ok1 ? s[n][3] * p.scale2 : -INFINITY;
-                mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
-                mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
+                for (int n = 0; n < 2; ++n) {
+                    const int jk = wk + n * 8 + tq * 2;
+                    if (jk >= live) { s[n][0] = -INFINITY; s[n][2] = -INFINITY; }
+                    if (jk + 1 >= live) { s[n][1] = -INFINITY; s[n][3] = -INFINITY; }
+                }
             }
+            float mx[2];
+            mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+            mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
             uint32_t pa[4];
+            float alpha[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                const float m_new = fmaxf(m_run[r], mx[r]);
-                float alpha = 1.f, p00 = 0.f, p01 = 0.f, p10 = 0.f, p11 = 0.f;
-                if (m_new > -INFINITY) {
-                    alpha = exp2f(m_run[r] - m_new);
-                    p00 = exp2f(s[0][2 * r] - m_new);
-                    p01 = exp2f(s[0][2 * r + 1] - m_new);
-                    p10 = exp2f(s[1][2 * r] - m_new);
-                    p11 = exp2f(s[1][2 * r + 1] - m_new);
-                }
+                const float m_new = fmaxf(m_run[r], mx[r] * p.scale2);          // scale2 > 0 keeps the order
+                const float m_sub = m_new > -INFINITY ? m_new : 0.f;            // nothing live yet: p = 2^-inf = 0
+                alpha[r] = fast_exp2(m_run[r] - m_sub);
+                const float p00 = fast_exp2(fmaf(s[0][2 * r], p.scale2, -m_sub));
+                const float p01 = fast_exp2(fmaf(s[0][2 * r + 1], p.scale2, -m_sub));
+                const float p10 = fast_exp2(fmaf(s[1][2 * r], p.scale2, -m_sub));
+                const float p11 = fast_exp2(fmaf(s[1][2 * r + 1], p.scale2, -m_sub));
                 float sum = (p00 + p01) + (p10 + p11);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                l_run[r] = l_run[r] * alpha + sum;
+                l_run[r] = l_run[r] * alpha[r] + sum;
                 m_run[r] = m_new;
                 pa[r] = pack2<T>(p00, p01);                      // keys 0-7 of the warp's slice
                 pa[2 + r] = pack2<T>(p10, p11);                  // keys 8-15
+            }
+            // the running maxima settle after a few tiles; rescale the accumulators only when one moved
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
                 for (int n = 0; n < D / 8; ++n) {
-                    acc[n][2 * r] *= alpha;
-                    acc[n][2 * r + 1] *= alpha;
+                    acc[n][0] *= alpha[0];
+                    acc[n][1] *= alpha[0];
+                    acc[n][2] *= alpha[1];
+                    acc[n][3] *= alpha[1];
                 }
             }
             // acc += P V  (k = the warp's 16 keys, n = head dim)
