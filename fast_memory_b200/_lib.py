@@ -34,8 +34,9 @@ _SIGNATURES = {
     "fm_status_string": (c_char_p, [c_int]),
     "fm_last_error": (c_char_p, []),
     "fm_launch_count": (c_int64, []),
+    "fm_hash_rows_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "fm_hash_rows": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64,
-                             c_void_p, c_void_p]),
+                             c_void_p, c_void_p, c_size_t, c_void_p]),
     "fm_group_rows_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "fm_group_rows": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_size_t, c_void_p]),

@@ -1,5 +1,6 @@
 // Query / key hashing: hash[r] = argmax_c A[c, :] . x[r, :] over the buckets of r's segment.
 // Stands in for the einsum + argmax of the reference (memory.py:281-283, triton_kernel.py:280-281).
+#include "mma_utils.cuh"
 #include "simt_tile.cuh"
 
 namespace fm {
@@ -67,6 +68,239 @@ hash_rows_kernel(const T *__restrict__ x, const T *__restrict__ A, int d, int n_
     }
 }
 
+// ---- tensor-core path for 16-bit inputs ------------------------------------------------------------------
+// The scores are computed with mma.sync (fp32 accumulate, unspecified summation order), which is only a
+// FILTER: per row the kernel keeps the best and second-best score; when they are closer than a bound on
+// the accumulation error the row goes on a re-check list and a second kernel decides it with the canonical
+// fp32 chain.  A row whose gap exceeds the bound has the same argmax under both orders, so the result is
+// bit-identical to the all-fp32 kernel above.
+//
+// Error bound: each value is within 2^-16 M of the exact dot product and the canonical chain within
+// 2^-17 M (d <= 256), M = ||x|| max_c ||a_c|| >= sum_i |a_ci x_i|; two scores can therefore swap order
+// only if their tensor-core gap is below 3 * 2^-16 M.  The test uses 2^-12 M.
+constexpr float kHashEps = 1.0f / 4096.0f;
+constexpr int kHashThreads = 128;
+
+__device__ __forceinline__ void top2_push(float v, int c, float &best, int &arg, float &second)
+{
+    if (v > best) { second = best; best = v; arg = c; }
+    else if (v > second) second = v;
+}
+
+// amax[s] = max row norm of the A rows of segment s (as the bits of a non-negative float, via atomicMax)
+template <typename T>
+__global__ void a_norm_max_kernel(const T *__restrict__ A, int total_buckets, int d, int n_seg,
+                                  const int32_t *__restrict__ seg_cb, unsigned *__restrict__ amax)
+{
+    const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (c >= total_buckets) return;
+    const int lane = threadIdx.x & 31;
+    float n2 = 0.f;
+    for (int i = lane; i < d; i += 32) {
+        float v = Elem<T>::to_f32(A[size_t(c) * d + i]);
+        n2 = fmaf(v, v, n2);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, off);
+    if (lane == 0) {
+        const int s = seg_cb ? find_segment(seg_cb, n_seg, c) : 0;
+        atomicMax(&amax[s], __float_as_uint(sqrtf(n2) * 1.0001f));
+    }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kHashThreads)
+hash_rows_mma_kernel(const T *__restrict__ x, const T *__restrict__ A, int n_rows, int total_buckets,
+                     const int32_t *__restrict__ seg_xb, const int32_t *__restrict__ seg_cb,
+                     const unsigned *__restrict__ amax, int32_t *__restrict__ hash_out,
+                     int32_t *__restrict__ recheck, int *__restrict__ n_recheck)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int CPR = D / 8;                                   // 16-byte chunks per row
+    constexpr int TILE_BYTES = kTile * D * 2;
+    const int s = blockIdx.y;
+    const int row0 = seg_xb ? seg_xb[s] : 0;
+    const int row1 = seg_xb ? seg_xb[s + 1] : n_rows;
+    const int cb0 = seg_cb ? seg_cb[s] : 0;
+    const int C = (seg_cb ? seg_cb[s + 1] : total_buckets) - cb0;
+    const int r0 = row0 + blockIdx.x * kTile;
+    if (r0 >= row1) return;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, g = lane >> 2, tq = lane & 3;
+    const uint32_t smem_base = smem_u32(smem_raw);
+    const char *Ab = reinterpret_cast<const char *>(A + size_t(cb0) * D);
+
+    auto issue = [&](int ta) {
+        const int c0 = ta * kTile;
+        if (c0 < C) {
+            const uint32_t dst = smem_base + (ta & 1) * TILE_BYTES;
+            for (int e = t; e < kTile * CPR; e += kHashThreads) {
+                const int j = e / CPR, c = e - j * CPR;
+                const bool ok = c0 + j < C;
+                cp_async16(dst + swz<D>(j, c), Ab + (ok ? size_t(c0 + j) * (D * 2) + c * 16 : 0), ok);
+            }
+        }
+        cp_async_commit();
+    };
+    issue(0);
+
+    // this warp's 16 rows as A-operand fragments, and their norms
+    uint32_t qf[D / 16][4];
+    float xn2[2] = {0.f, 0.f};
+    {
+        const int ra = r0 + warp * 16 + g, rb = ra + 8;
+        const T *q0 = ra < row1 ? x + size_t(ra) * D : nullptr;
+        const T *q1 = rb < row1 ? x + size_t(rb) * D : nullptr;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            const int c = ks * 16 + tq * 2;
+            qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + c) : 0u;
+            qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + c) : 0u;
+            qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + c + 8) : 0u;
+            qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + c + 8) : 0u;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const T *h = reinterpret_cast<const T *>(&qf[ks][e]);
+                const float a = Elem<T>::to_f32(h[0]), b = Elem<T>::to_f32(h[1]);
+                xn2[e & 1] += a * a + b * b;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            xn2[r] += __shfl_xor_sync(0xffffffffu, xn2[r], 1);
+            xn2[r] += __shfl_xor_sync(0xffffffffu, xn2[r], 2);
+        }
+    }
+
+    float best[2] = {-INFINITY, -INFINITY}, second[2] = {-INFINITY, -INFINITY};
+    int arg[2] = {0, 0};
+    const int n_at = (C + kTile - 1) / kTile;
+    for (int ta = 0; ta < n_at; ++ta) {
+        issue(ta + 1);
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t a_base = smem_base + (ta & 1) * TILE_BYTES;
+        const int c0 = ta * kTile;
+#pragma unroll
+        for (int nt2 = 0; nt2 < kTile / 16; ++nt2) {
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const int j = nt2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+                const int c = ks * 2 + ((lane >> 3) & 1);
+                uint32_t b[4];
+                ldmatrix_x4(b, a_base + swz<D>(j, c));
+                mma16816<T>(s0, qf[ks], b[0], b[1]);
+                mma16816<T>(s1, qf[ks], b[2], b[3]);
+            }
+            const int ca = c0 + nt2 * 16 + tq * 2;             // bucket of s0[0] / s0[2]; s1 is 8 further
+            if (ca < C) { top2_push(s0[0], ca, best[0], arg[0], second[0]); top2_push(s0[2], ca, best[1], arg[1], second[1]); }
+            if (ca + 1 < C) { top2_push(s0[1], ca + 1, best[0], arg[0], second[0]); top2_push(s0[3], ca + 1, best[1], arg[1], second[1]); }
+            if (ca + 8 < C) { top2_push(s1[0], ca + 8, best[0], arg[0], second[0]); top2_push(s1[2], ca + 8, best[1], arg[1], second[1]); }
+            if (ca + 9 < C) { top2_push(s1[1], ca + 9, best[0], arg[0], second[0]); top2_push(s1[3], ca + 9, best[1], arg[1], second[1]); }
+        }
+        __syncthreads();                                         // tile consumed before its buffer is refilled
+    }
+    cp_async_wait<0>();
+
+    const float a_max = __uint_as_float(amax[s]);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+#pragma unroll
+        for (int off = 1; off <= 2; off <<= 1) {                 // fold the 4 lanes of the quad that share a row
+            const float ob = __shfl_xor_sync(0xffffffffu, best[r], off);
+            const float os = __shfl_xor_sync(0xffffffffu, second[r], off);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg[r], off);
+            if (ob > best[r]) { second[r] = fmaxf(best[r], os); best[r] = ob; arg[r] = oa; }
+            else second[r] = fmaxf(second[r], ob);               // includes ob == best: a tie is always re-checked
+        }
+        const int row = r0 + warp * 16 + g + 8 * r;
+        if (tq == 0 && row < row1) {
+            hash_out[row] = arg[r];
+            const float eps = kHashEps * sqrtf(xn2[r]) * a_max;
+            if (!(best[r] - second[r] > eps)) recheck[atomicAdd(n_recheck, 1)] = row;
+        }
+    }
+}
+
+// One warp per listed row: canonical argmax (fp32 FMA chain per bucket, first maximum wins).
+template <typename T>
+__global__ void __launch_bounds__(128)
+hash_recheck_kernel(const T *__restrict__ x, const T *__restrict__ A, int d, int n_rows, int total_buckets, int n_seg,
+                    const int32_t *__restrict__ seg_xb, const int32_t *__restrict__ seg_cb,
+                    const int32_t *__restrict__ recheck, const int *__restrict__ n_recheck,
+                    int32_t *__restrict__ hash_out)
+{
+    __shared__ float xs[4][256];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = min(*n_recheck, n_rows);
+    for (int i = blockIdx.x * 4 + warp; i < n; i += gridDim.x * 4) {
+        const int row = recheck[i];
+        const int s = seg_xb ? find_segment(seg_xb, n_seg, row) : 0;
+        const int cb0 = seg_cb ? seg_cb[s] : 0;
+        const int C = (seg_cb ? seg_cb[s + 1] : total_buckets) - cb0;
+        __syncwarp();
+        for (int e = lane; e < d; e += 32) xs[warp][e] = Elem<T>::to_f32(x[size_t(row) * d + e]);
+        __syncwarp();
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int c = lane; c < C; c += 32) {
+            const T *a = A + size_t(cb0 + c) * d;
+            float y = 0.f;
+            for (int e = 0; e < d; e += 8) {
+                uint4 raw = *reinterpret_cast<const uint4 *>(a + e);
+                float f[8];
+                widen8(raw, f, T());
+#pragma unroll
+                for (int u = 0; u < 8; ++u) y = fmaf(f[u], xs[warp][e + u], y);
+            }
+            if (y > best || arg == 0x7fffffff) { best = y; arg = c; }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
+            if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+        }
+        if (lane == 0) hash_out[row] = arg == 0x7fffffff ? 0 : arg;
+    }
+}
+
+struct HashLayout { size_t off_amax, off_count, off_list, total; };
+static HashLayout hash_layout(int64_t n_rows, int n_seg)
+{
+    HashLayout L;
+    L.off_amax = 0;
+    L.off_count = align_up(size_t(n_seg) * 4, 256);
+    L.off_list = L.off_count + 256;
+    L.total = L.off_list + align_up(size_t(std::max<int64_t>(n_rows, 1)) * 4, 256);
+    return L;
+}
+
+template <typename T, int D>
+static int launch_hash_mma(const void *x, const void *A, int64_t n_rows, int64_t total_buckets, int n_seg,
+                           const int32_t *seg_xb, const int32_t *seg_cb, int64_t max_seg_rows, int32_t *hash_out,
+                           char *ws, cudaStream_t st)
+{
+    HashLayout L = hash_layout(n_rows, n_seg);
+    unsigned *amax = (unsigned *)(ws + L.off_amax);
+    int *count = (int *)(ws + L.off_count);
+    int32_t *list = (int32_t *)(ws + L.off_list);
+    FM_CUDA_OK(cudaMemsetAsync(ws, 0, L.off_list, st));
+    a_norm_max_kernel<T><<<(unsigned)ceil_div(total_buckets, 4), 128, 0, st>>>((const T *)A, (int)total_buckets, D, n_seg, seg_cb, amax);
+    FM_LAUNCHED("a_norm_max_kernel");
+    const size_t smem = 2 * size_t(kTile) * D * 2;
+    FM_CUDA_OK(cudaFuncSetAttribute(hash_rows_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)ceil_div(max_seg_rows, kTile), (unsigned)n_seg);
+    hash_rows_mma_kernel<T, D><<<grid, kHashThreads, smem, st>>>((const T *)x, (const T *)A, (int)n_rows, (int)total_buckets,
+                                                               seg_xb, seg_cb, amax, hash_out, list, count);
+    FM_LAUNCHED("hash_rows_mma_kernel");
+    const int blocks = (int)std::min<int64_t>(ceil_div(n_rows, 4), int64_t(sm_count()) * 4);
+    hash_recheck_kernel<T><<<blocks, 128, 0, st>>>((const T *)x, (const T *)A, D, (int)n_rows, (int)total_buckets, n_seg,
+                                                  seg_xb, seg_cb, list, count, hash_out);
+    FM_LAUNCHED("hash_recheck_kernel");
+    return FM_OK;
+}
+
 template <typename T>
 static int launch_hash(const void *x, const void *A, int64_t n_rows, int64_t total_buckets, int d, int n_seg,
                        const int32_t *seg_xb, const int32_t *seg_cb, int64_t max_seg_rows, int32_t *hash_out,
@@ -83,12 +317,17 @@ static int launch_hash(const void *x, const void *A, int64_t n_rows, int64_t tot
 
 }  // namespace fm
 
+extern "C" size_t fm_hash_rows_workspace_bytes(int64_t n_rows, int n_seg)
+{
+    return fm::hash_layout(n_rows, std::max(n_seg, 1)).total;
+}
+
 extern "C" int fm_hash_rows(const void *x, const void *A, int dtype, int64_t n_rows, int64_t total_buckets, int d,
                             int n_seg, const int32_t *seg_xb, const int32_t *seg_cb, int64_t max_seg_rows,
-                            int32_t *hash_out, fm_stream_t stream)
+                            int32_t *hash_out, void *workspace, size_t workspace_bytes, fm_stream_t stream)
 {
     using namespace fm;
-    FM_REQUIRE(x && A && hash_out, "fm_hash_rows: null pointer");
+    FM_REQUIRE(x && A && hash_out && workspace, "fm_hash_rows: null pointer");
     FM_REQUIRE(n_rows >= 0 && total_buckets > 0 && n_seg >= 1, "fm_hash_rows: bad sizes");
     FM_REQUIRE(n_rows < (int64_t(1) << 31) && total_buckets < (int64_t(1) << 31), "fm_hash_rows: sizes exceed int32");
     FM_REQUIRE((seg_xb == nullptr) == (seg_cb == nullptr), "fm_hash_rows: pass both segment arrays or neither");
@@ -97,9 +336,19 @@ extern "C" int fm_hash_rows(const void *x, const void *A, int dtype, int64_t n_r
         set_error("fm_hash_rows: head dim %d not supported (multiple of 16 in [16, 256])", d);
         return FM_ERR_UNSUPPORTED;
     }
+    if (workspace_bytes < fm_hash_rows_workspace_bytes(n_rows, n_seg)) {
+        set_error("fm_hash_rows: workspace %zu < %zu", workspace_bytes, fm_hash_rows_workspace_bytes(n_rows, n_seg));
+        return FM_ERR_WORKSPACE;
+    }
     if (n_rows == 0) return FM_OK;
     if (max_seg_rows <= 0) max_seg_rows = n_rows;
     cudaStream_t st = (cudaStream_t)stream;
+    char *ws = (char *)workspace;
+    const bool aligned = ((uintptr_t)x | (uintptr_t)A) % 16 == 0;
+    if (dtype == FM_BF16 && aligned && d == 128) return launch_hash_mma<__nv_bfloat16, 128>(x, A, n_rows, total_buckets, n_seg, seg_xb, seg_cb, max_seg_rows, hash_out, ws, st);
+    if (dtype == FM_BF16 && aligned && d == 64) return launch_hash_mma<__nv_bfloat16, 64>(x, A, n_rows, total_buckets, n_seg, seg_xb, seg_cb, max_seg_rows, hash_out, ws, st);
+    if (dtype == FM_F16 && aligned && d == 128) return launch_hash_mma<__half, 128>(x, A, n_rows, total_buckets, n_seg, seg_xb, seg_cb, max_seg_rows, hash_out, ws, st);
+    if (dtype == FM_F16 && aligned && d == 64) return launch_hash_mma<__half, 64>(x, A, n_rows, total_buckets, n_seg, seg_xb, seg_cb, max_seg_rows, hash_out, ws, st);
     switch (dtype) {
     case FM_F32: return launch_hash<float>(x, A, n_rows, total_buckets, d, n_seg, seg_xb, seg_cb, max_seg_rows, hash_out, st);
     case FM_BF16: return launch_hash<__nv_bfloat16>(x, A, n_rows, total_buckets, d, n_seg, seg_xb, seg_cb, max_seg_rows, hash_out, st);

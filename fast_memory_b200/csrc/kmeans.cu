@@ -81,7 +81,7 @@ __global__ void cast_rows_kernel(const float *__restrict__ src, T *__restrict__ 
     if (i < n) dst[i] = Elem<T>::from_f32(src[i]);
 }
 
-struct KmLayout { size_t off_nrm, off_hash, off_goff, off_perm, off_group, total; };
+struct KmLayout { size_t off_nrm, off_hash, off_goff, off_perm, off_group, off_hws, total; };
 
 static KmLayout km_layout(int n_seg, const int64_t *seg_xb, const int64_t *seg_cb)
 {
@@ -97,6 +97,7 @@ static KmLayout km_layout(int n_seg, const int64_t *seg_xb, const int64_t *seg_c
     L.off_goff = off; off += align_up(size_t(max_c + 1) * 4, 256);
     L.off_perm = off; off += align_up(size_t(max_rows) * 4, 256);
     L.off_group = off; off += fm_group_rows_workspace_bytes(max_rows, std::max<int64_t>(max_c, 1));
+    L.off_hws = off; off += fm_hash_rows_workspace_bytes(max_rows, 1);
     L.total = off;
     return L;
 }
@@ -125,7 +126,8 @@ static int kmeans_impl(const void *Xv, int d, int n_seg, const int64_t *seg_xb, 
         for (int s = 0; s < n_seg; ++s) {
             const int64_t r0 = seg_xb[s], n = seg_xb[s + 1] - r0, c0 = seg_cb[s], C = seg_cb[s + 1] - c0;
             if (C <= 0) continue;
-            int rc = fm_hash_rows(X + r0 * d, A + c0 * d, Elem<T>::id, n, C, d, 1, nullptr, nullptr, n, hash, st);
+            int rc = fm_hash_rows(X + r0 * d, A + c0 * d, Elem<T>::id, n, C, d, 1, nullptr, nullptr, n, hash,
+                                  ws + L.off_hws, fm_hash_rows_workspace_bytes(n, 1), st);
             if (rc != FM_OK) return rc;
             rc = fm_group_rows(hash, n, C, 1, nullptr, nullptr, goff, perm, gws,
                                fm_group_rows_workspace_bytes(n, C), st);

@@ -52,9 +52,10 @@ def hash_rows(x: torch.Tensor, A: torch.Tensor, seg_xb: Optional[torch.Tensor] =
     assert x.is_contiguous() and A.is_contiguous()
     out = torch.empty(x.shape[0], dtype=torch.int32, device=dev)
     n_seg = 1 if seg_xb is None else seg_xb.numel() - 1
+    ws = _ws.get("hash", L.lib().fm_hash_rows_workspace_bytes(x.shape[0], n_seg), dev)
     L.check(L.lib().fm_hash_rows(L.ptr(x), L.ptr(A), L.dtype_id(x.dtype), x.shape[0], A.shape[0], x.shape[1], n_seg,
-                                 L.ptr(seg_xb), L.ptr(seg_cb), int(max_seg_rows), L.ptr(out), L.stream_ptr(dev)),
-            "fm_hash_rows")
+                                 L.ptr(seg_xb), L.ptr(seg_cb), int(max_seg_rows), L.ptr(out), L.ptr(ws), ws.numel(),
+                                 L.stream_ptr(dev)), "fm_hash_rows")
     return out
 
 

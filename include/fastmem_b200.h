@@ -57,10 +57,14 @@ int64_t fm_launch_count(void);
  * x [n_rows, d] and A [total_buckets, d] share `dtype`.  seg_xb / seg_cb: DEVICE int32 prefix
  * arrays of n_seg+1 entries (pass NULL, NULL and n_seg = 1 for one segment covering everything).
  * max_seg_rows: largest number of rows in one segment (sizes the grid).
+ * 16-bit inputs with d = 64 or 128 run on the tensor cores as a filter: rows whose two best scores are
+ * closer than a bound on the accumulation error are re-decided with the fp32 chain, so the result is
+ * the same bits as the all-fp32 path.
  * ------------------------------------------------------------------------------------------- */
+size_t fm_hash_rows_workspace_bytes(int64_t n_rows, int n_seg);
 int fm_hash_rows(const void *x, const void *A, int dtype, int64_t n_rows, int64_t total_buckets, int d,
                  int n_seg, const int32_t *seg_xb, const int32_t *seg_cb, int64_t max_seg_rows,
-                 int32_t *hash_out, fm_stream_t stream);
+                 int32_t *hash_out, void *workspace, size_t workspace_bytes, fm_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Grouping: counting sort of rows by global bucket (segment bucket base + local hash).

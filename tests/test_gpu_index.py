@@ -53,6 +53,24 @@ def test_hash_rows_bit_exact_multi_segment(dtype):
     assert (h2 < 5).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [64, 128])
+def test_hash_rows_near_ties_are_decided_by_the_fp32_chain(dtype, d):
+    """Tensor-core filter + exact re-check: centroids that differ by one ulp in one coordinate give score gaps
+    far below any accumulation error, and exact ties; the result must still equal the oracle bit for bit."""
+    g = torch.Generator().manual_seed(d)
+    base = torch.nn.functional.normalize(torch.randn(40, d, generator=g), dim=-1)
+    A = base.repeat(8, 1)                                   # 320 buckets: every centroid 8 times ...
+    A = A.to(dtype)
+    bump = A.view(torch.int16).clone()
+    sel = torch.arange(40, 320)
+    bump[sel, sel % d] += ((sel // 40) % 3 - 1).to(torch.int16)      # ... some copies off by +-1 ulp in one place
+    A = bump.view(dtype)
+    X = (base[torch.randint(40, (3000,), generator=g)] + 0.2 * torch.randn(3000, d, generator=g)).to(dtype)
+    h = fm.hash_rows(X.to(DEV), A.to(DEV)).cpu().numpy()
+    assert np.array_equal(h, O.query_hash(A[None], X[None])[0])
+
+
 def test_group_rows_is_a_valid_counting_sort():
     g = torch.Generator().manual_seed(2)
     C, n = 37, 5000

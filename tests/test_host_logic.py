@@ -27,7 +27,7 @@ def test_status_plumbing_without_a_gpu():
     assert L.fm_status_string(0) == b"ok"
     assert b"workspace" in L.fm_status_string(-3)
     # argument validation happens before any CUDA call
-    rc = L.fm_hash_rows(None, None, 0, 10, 4, 64, 1, None, None, 10, None, None)
+    rc = L.fm_hash_rows(None, None, 0, 10, 4, 64, 1, None, None, 10, None, None, 0, None)
     assert rc == -1 and b"null pointer" in L.fm_last_error()
     rc = L.fm_topz_select(None, 1, 1, 1, 1, 0, None, 1, None)
     assert rc == -1
