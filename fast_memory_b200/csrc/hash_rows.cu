@@ -243,17 +243,26 @@ hash_recheck_kernel(const T *__restrict__ x, const T *__restrict__ A, int d, int
         __syncwarp();
         float best = -INFINITY;
         int arg = 0x7fffffff;
-        for (int c = lane; c < C; c += 32) {
-            const T *a = A + size_t(cb0 + c) * d;
-            float y = 0.f;
-            for (int e = 0; e < d; e += 8) {
-                uint4 raw = *reinterpret_cast<const uint4 *>(a + e);
-                float f[8];
-                widen8(raw, f, T());
+        // four buckets per lane at a time: the chains are independent, which hides the FMA latency
+        for (int c = lane; c < C; c += 128) {
+            float y[4] = {0.f, 0.f, 0.f, 0.f};
+            const T *a[4];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) y = fmaf(f[u], xs[warp][e + u], y);
+            for (int u = 0; u < 4; ++u) a[u] = A + size_t(cb0 + min(c + 32 * u, C - 1)) * d;
+            for (int e = 0; e < d; e += 8) {
+                float f[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) widen8(*reinterpret_cast<const uint4 *>(a[u] + e), f[u], T());
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    const float xv = xs[warp][e + v];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) y[u] = fmaf(f[u][v], xv, y[u]);
+                }
             }
-            if (y > best || arg == 0x7fffffff) { best = y; arg = c; }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (c + 32 * u < C && (y[u] > best || arg == 0x7fffffff)) { best = y[u]; arg = c + 32 * u; }
         }
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) {

@@ -1,0 +1,320 @@
+// Projection Y = A K^T on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operands staged
+// by TMA), with the epilogue that makes the index build a single pass over the keys: instead of writing
+// Y (C x N fp32, several GB) each epilogue thread owns one bucket row, compares its scores with the bucket's
+// threshold and appends the survivors (score, key) to the bucket's candidate list.  A dense-store epilogue of
+// the same kernel produces the small score matrix of the key sample from which the thresholds are estimated.
+//
+// CTA = 192 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and TMEM owner,
+// warps 2-5 = epilogue (TMEM lane quarter = warp % 4).  Work unit = (segment, 128-bucket tile, key range).
+// Per 256-key tile: K tile -> shared memory (3-stage ring, 64 KB per stage at d = 128), 8 UMMAs
+// (M = 128, N = 256, K = 16) into one of two 256-column accumulators, so the MMAs of tile t + 1 overlap the
+// epilogue of tile t.  Every mbarrier wait is bounded; on a give-up the CTA records a status and unwinds.
+#include "tc_utils.cuh"
+
+#include <mutex>
+
+namespace fm {
+
+namespace {
+
+constexpr int kBM = 128;                    // bucket rows per tile (UMMA M)
+constexpr int kBN = 256;                    // keys per tile (UMMA N)
+constexpr int kStagesTc = 3;
+constexpr int kTcThreads = 192;
+
+}  // namespace
+
+struct TcSeg {
+    int a_row0;        // first row of A of this segment (tensor-map row)
+    int n_buckets;
+    int k_row0;        // first key row of this segment in the key tensor map's row coordinate
+    int n_keys;        // columns of this segment's projection (keys, or sampled keys)
+    int mtile0;        // index of the segment's first bucket tile in the global list
+};
+
+struct TcParams {
+    const TcSeg *segs;
+    int n_seg;
+    int n_ranges;          // key ranges per bucket tile
+    // dense epilogue
+    float *Y;
+    int64_t ldy;
+    // candidate epilogue
+    const float *tau;      // [total buckets] threshold of every bucket
+    uint2 *cand;           // [total buckets][cap] (score bits, key index local to the segment)
+    int cap;
+    int *cand_count;       // [total buckets][n_ranges]
+    int *status;           // set non-zero when a wait gave up
+};
+
+template <int D, bool DENSE>
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmK, TcParams p, uint32_t idesc)
+{
+    constexpr int KB = D / 64;                               // 64-element (128-byte) k-blocks
+    constexpr uint32_t A_BYTES = KB * kBM * 128;
+    constexpr uint32_t STAGE_BYTES = KB * kBN * 128;
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t bars[2 * kStagesTc + 1 + 4];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (tc::smem_addr(smem_dyn) + 1023u) & ~1023u;          // 1024-byte aligned tiles
+    const uint32_t a_smem = base, k_smem = base + A_BYTES;
+    const uint32_t bar0 = tc::smem_addr(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStagesTc + s); };
+    const uint32_t a_bar = bar0 + 8u * (2 * kStagesTc);
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kStagesTc + 1 + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kStagesTc + 3 + a); };
+
+    // ---- which unit -----------------------------------------------------------------------------------------
+    const int unit = blockIdx.x;
+    const int range = unit % p.n_ranges;
+    const int mt_global = unit / p.n_ranges;
+    int seg = 0;
+    {
+        int lo = 0, hi = p.n_seg;                            // largest seg with mtile0 <= mt_global
+        while (hi - lo > 1) {
+            int mid = (lo + hi) >> 1;
+            if (p.segs[mid].mtile0 <= mt_global) lo = mid; else hi = mid;
+        }
+        seg = lo;
+    }
+    const TcSeg sg = p.segs[seg];
+    const int m0 = (mt_global - sg.mtile0) * kBM;            // first bucket of the tile inside the segment
+    const int n_tiles_seg = (sg.n_keys + kBN - 1) / kBN;
+    const int per_range = (n_tiles_seg + p.n_ranges - 1) / p.n_ranges;
+    const int t_begin = min(range * per_range, n_tiles_seg), t_end = min(t_begin + per_range, n_tiles_seg);
+    const int n_tiles = t_end - t_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStagesTc; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
+        tc::mbar_init(a_bar, 1);
+        for (int a = 0; a < 2; ++a) { tc::mbar_init(tfull_bar(a), 1); tc::mbar_init(tempty_bar(a), 4); }
+        tc::mbar_fence_init();
+        s_abort = 0;
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_addr(&tmem_slot), 512);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer ---------------------------------------------------------------------------------
+        if (lane == 0 && n_tiles > 0) {
+            tc::prefetch_tensormap(&tmA);
+            tc::prefetch_tensormap(&tmK);
+            tc::mbar_arrive_expect_tx(a_bar, A_BYTES);
+            for (int kb = 0; kb < KB; ++kb) tc::tma_load_2d(a_smem + kb * (kBM * 128), &tmA, kb * 64, sg.a_row0 + m0, a_bar);
+            for (int t = 0; t < n_tiles; ++t) {
+                const int s = t % kStagesTc;
+                if (!tc::mbar_wait(empty_bar(s), ((t / kStagesTc) & 1) ^ 1)) { atomicExch(p.status, 1); s_abort = 1; break; }
+                if (*(volatile int *)&s_abort) break;
+                tc::mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
+                const int key_row = sg.k_row0 + (t_begin + t) * kBN;
+                for (int kb = 0; kb < KB; ++kb)
+                    tc::tma_load_2d(k_smem + s * STAGE_BYTES + kb * (kBN * 128), &tmK, kb * 64, key_row, full_bar(s));
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -------------------------------------------------------------------------------------
+        if (lane == 0 && n_tiles > 0) {
+            bool ok = tc::mbar_wait(a_bar, 0);
+            for (int t = 0; ok && t < n_tiles; ++t) {
+                const int s = t % kStagesTc, acc = t & 1;
+                ok = tc::mbar_wait(tempty_bar(acc), ((t >> 1) & 1) ^ 1) && tc::mbar_wait(full_bar(s), (t / kStagesTc) & 1);
+                if (!ok || *(volatile int *)&s_abort) { ok = false; break; }
+                tc::fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kBN;
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t da = tc::smem_desc_sw128(a_smem + kb * (kBM * 128) + k * 32);
+                        const uint64_t db = tc::smem_desc_sw128(k_smem + s * STAGE_BYTES + kb * (kBN * 128) + k * 32);
+                        tc::umma_f16(d_tmem, da, db, idesc, (kb | k) != 0);
+                    }
+                }
+                tc::umma_commit(empty_bar(s));               // the stage may be refilled once these MMAs have read it
+                tc::umma_commit(tfull_bar(acc));             // the accumulator is complete
+            }
+            if (!ok) { atomicExch(p.status, 2); s_abort = 1; }
+        }
+    } else {
+        // ---- epilogue: one bucket row per thread --------------------------------------------------------------
+        const int q = warp & 3;                              // TMEM lane quarter this warp may read
+        const int m = q * 32 + lane;                         // row of the tile
+        const bool row_ok = m0 + m < sg.n_buckets;
+        const int grow = sg.a_row0 + m0 + m;                 // global bucket
+        float tau = 0.f;
+        uint2 *list = nullptr;
+        int cursor = 0, dir = 1, sub_cap = 0;
+        if constexpr (!DENSE) {
+            if (row_ok) {
+                tau = p.tau[grow];
+                const int nb = max(1, p.n_ranges / 2);       // buffers per row; two ranges share one, growing toward each other
+                sub_cap = p.cap / nb;
+                list = p.cand + size_t(grow) * p.cap + size_t(range / 2) * sub_cap;
+                if (p.n_ranges > 1 && (range & 1)) { dir = -1; list += sub_cap - 1; }
+            }
+        }
+        bool ok = true;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int acc = t & 1;
+            ok = tc::mbar_wait(tfull_bar(acc), (t >> 1) & 1) && !*(volatile int *)&s_abort;
+            ok = __all_sync(0xffffffffu, ok);                // the TMEM loads below need the whole warp
+            if (!ok) break;
+            tc::fence_after_sync();
+            const int col0 = (t_begin + t) * kBN;
+#pragma unroll 1
+            for (int b = 0; b < kBN / 32; ++b) {
+                uint32_t v[32];
+                tc::tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * kBN + b * 32, v);
+                tc::tmem_ld_wait();
+                const int c0 = col0 + b * 32;
+                if constexpr (DENSE) {
+                    if (row_ok) {
+                        float *dst = p.Y + size_t(grow) * p.ldy + c0;
+                        if (c0 + 32 <= sg.n_keys && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+                            for (int e = 0; e < 32; e += 4)
+                                *reinterpret_cast<uint4 *>(dst + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e)
+                                if (c0 + e < sg.n_keys) dst[e] = __uint_as_float(v[e]);
+                        }
+                    }
+                } else {
+                    if (row_ok) {
+                        const int live = sg.n_keys - c0;     // columns of this batch that exist
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            if (__uint_as_float(v[e]) >= tau && e < live) {
+                                if (cursor < sub_cap) list[cursor * dir] = make_uint2(v[e], uint32_t(c0 + e));
+                                ++cursor;                    // keeps counting past the capacity: the overflow is detected later
+                            }
+                        }
+                    }
+                }
+            }
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tempty_bar(acc));
+        }
+        if (!ok && lane == 0) { atomicExch(p.status, 3); s_abort = 1; }
+        if constexpr (!DENSE) {
+            if (row_ok) p.cand_count[size_t(grow) * p.n_ranges + range] = cursor;
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tc::tmem_dealloc(tmem_base, 512);
+}
+
+// ---- host ----------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static std::mutex mu;
+    static EncodeTiledFn fn = nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+int make_tensor_map_2d(CUtensorMap *map, const void *base_ptr, int dtype, uint64_t rows, uint64_t d, uint64_t row_stride_bytes,
+                       uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return FM_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {d, rows};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dtype == FM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                    const_cast<void *>(base_ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with %d (rows %llu, d %llu, stride %llu)", (int)r, (unsigned long long)rows,
+                  (unsigned long long)d, (unsigned long long)row_stride_bytes);
+        return FM_ERR_CUDA;
+    }
+    return FM_OK;
+}
+
+template <int D, bool DENSE>
+static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmK, const TcParams &p, int units, bool bf16, cudaStream_t st)
+{
+    constexpr size_t smem = size_t(D / 64) * (kBM * 128 + kStagesTc * kBN * 128) + 1024;
+    FM_CUDA_OK(cudaFuncSetAttribute(tc_project_kernel<D, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tc_project_kernel<D, DENSE><<<units, kTcThreads, smem, st>>>(tmA, tmK, p, tc::instr_desc_f16(bf16, kBM, kBN));
+    FM_LAUNCHED("tc_project_kernel");
+    return FM_OK;
+}
+
+int tc_project_launch(const CUtensorMap &tmA, const CUtensorMap &tmK, const TcParams &p, int units, int d, bool dense, bool bf16,
+                      cudaStream_t st)
+{
+    if (d == 128) return dense ? launch_tc<128, true>(tmA, tmK, p, units, bf16, st) : launch_tc<128, false>(tmA, tmK, p, units, bf16, st);
+    if (d == 64) return dense ? launch_tc<64, true>(tmA, tmK, p, units, bf16, st) : launch_tc<64, false>(tmA, tmK, p, units, bf16, st);
+    set_error("tensor-core projection supports head dim 64 and 128, got %d", d);
+    return FM_ERR_UNSUPPORTED;
+}
+
+}  // namespace fm
+
+// Dense tensor-core projection of ONE segment: Y[c, j] ~= A[c] . K[j * key_step] for j < n_cols, fp32
+// accumulation in the tensor cores' own order (NOT the canonical chain: for scores that feed an index use
+// fm_project).  workspace: 256 bytes.
+extern "C" int fm_project_tc(const void *A, const void *K, int dtype, int64_t C, int64_t n_key_rows, int d, int64_t key_step,
+                             float *Y, int64_t ldy, void *workspace, size_t workspace_bytes, fm_stream_t stream)
+{
+    using namespace fm;
+    FM_REQUIRE(A && K && Y && workspace, "fm_project_tc: null pointer");
+    FM_REQUIRE(C > 0 && n_key_rows > 0 && key_step >= 1, "fm_project_tc: bad sizes");
+    FM_REQUIRE(workspace_bytes >= 256, "fm_project_tc: workspace must be at least 256 bytes");
+    FM_REQUIRE(((uintptr_t)A | (uintptr_t)K) % 16 == 0, "fm_project_tc: A and K must be 16-byte aligned");
+    if ((dtype != FM_BF16 && dtype != FM_F16) || (d != 64 && d != 128)) {
+        set_error("fm_project_tc: needs bf16/fp16 and head dim 64 or 128");
+        return FM_ERR_UNSUPPORTED;
+    }
+    const int64_t n_cols = (n_key_rows + key_step - 1) / key_step;
+    FM_REQUIRE(ldy >= n_cols, "fm_project_tc: ldy too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    CUtensorMap tmA, tmK;
+    int rc = make_tensor_map_2d(&tmA, A, dtype, (uint64_t)C, (uint64_t)d, (uint64_t)d * 2, kBM);
+    if (rc != FM_OK) return rc;
+    rc = make_tensor_map_2d(&tmK, K, dtype, (uint64_t)n_cols, (uint64_t)d, (uint64_t)d * 2 * key_step, kBN);
+    if (rc != FM_OK) return rc;
+    TcSeg seg = {0, (int)C, 0, (int)n_cols, 0};
+    char *ws = (char *)workspace;
+    FM_CUDA_OK(cudaMemsetAsync(ws, 0, 256, st));
+    FM_CUDA_OK(cudaMemcpyAsync(ws + 64, &seg, sizeof(seg), cudaMemcpyHostToDevice, st));
+    TcParams p = {};
+    p.segs = (const TcSeg *)(ws + 64);
+    p.n_seg = 1;
+    const int m_tiles = (int)ceil_div(C, kBM);
+    const int n_tiles = (int)ceil_div(n_cols, kBN);
+    p.n_ranges = (int)std::max<int64_t>(1, std::min<int64_t>(n_tiles, ceil_div(2 * sm_count(), m_tiles)));
+    p.Y = Y;
+    p.ldy = ldy;
+    p.status = (int *)ws;
+    return tc_project_launch(tmA, tmK, p, m_tiles * p.n_ranges, d, true, dtype == FM_BF16, st);
+}

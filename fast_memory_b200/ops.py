@@ -131,6 +131,22 @@ def project(A: torch.Tensor, K: torch.Tensor) -> torch.Tensor:
     return Y
 
 
+def project_tc(A: torch.Tensor, K: torch.Tensor, key_step: int = 1) -> torch.Tensor:
+    """Tensor-core (tcgen05) projection of every ``key_step``-th row of K: approximate fp32 scores."""
+    dev = L.require_cuda(A, K)
+    assert A.dtype == K.dtype and A.is_contiguous() and K.is_contiguous() and A.shape[1] == K.shape[1]
+    n_cols = (K.shape[0] + key_step - 1) // key_step
+    Y = torch.empty(A.shape[0], n_cols, dtype=torch.float32, device=dev)
+    ws = _ws.get("project_tc", 256, dev)
+    L.check(L.lib().fm_project_tc(L.ptr(A), L.ptr(K), L.dtype_id(A.dtype), A.shape[0], K.shape[0], A.shape[1],
+                                  int(key_step), L.ptr(Y), n_cols, L.ptr(ws), ws.numel(), L.stream_ptr(dev)),
+            "fm_project_tc")
+    status = int(ws[:4].view(torch.int32).item())
+    if status:
+        raise L.FastMemError(f"fm_project_tc: a pipeline wait gave up (status {status})")
+    return Y
+
+
 def topz_select(Y: torch.Tensor, Z: int, index_base: int = 0) -> torch.Tensor:
     """Rows of fp32 ``Y`` -> int32 ``[rows, Z]`` indices of the Z largest (lower index wins ties), ascending."""
     dev = L.require_cuda(Y)

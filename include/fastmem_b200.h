@@ -141,6 +141,16 @@ int fm_project(const void *A, const void *K, int dtype, int64_t C, int64_t N, in
                fm_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * The same projection on the tcgen05 tensor cores (TMA-fed, accumulators in TMEM) for bf16 / fp16 and
+ * d = 64 or 128, optionally over every key_step-th key row: Y[c, j] ~ A[c, :] . K[j * key_step, :]
+ * for j < ceil(n_key_rows / key_step).  The summation order is the hardware's, so these scores are
+ * approximate (about 1e-6 relative): they drive threshold estimates, never an index decision.
+ * Same reference lines as fm_project.  workspace: at least 256 bytes.
+ * ------------------------------------------------------------------------------------------- */
+int fm_project_tc(const void *A, const void *K, int dtype, int64_t C, int64_t n_key_rows, int d, int64_t key_step,
+                  float *Y, int64_t ldy, void *workspace, size_t workspace_bytes, fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Exact top-Z of every row of Y [n_rows, N] (row stride ldy): the Z largest values, lower index wins
  * ties, indices written in ascending order plus `index_base`.
  * Replaces: torch.topk at mem:273 / tk:278 (README.md:27).  Z <= N.

@@ -22,6 +22,20 @@ def test_projection_is_bit_exact(dtype, d):
     assert np.array_equal(Y, O.project(A, K))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("C,N,d,step", [(128, 256, 128, 1), (130, 1000, 128, 1), (512, 5000, 128, 16), (70, 777, 64, 3),
+                                        (1024, 40000, 128, 1)])
+def test_tensor_core_projection_close_to_canonical(dtype, C, N, d, step):
+    """tcgen05 / TMEM / TMA projection: same contraction as the canonical one up to summation order."""
+    g = torch.Generator().manual_seed(C + N)
+    A = torch.randn(C, d, generator=g).to(dtype)
+    K = torch.randn(N, d, generator=g).to(dtype)
+    Y = fm.ops.project_tc(A.to(DEV), K.to(DEV), key_step=step).cpu()
+    ref = torch.from_numpy(O.project(A, K[::step].contiguous()))
+    assert Y.shape == ref.shape
+    assert (Y - ref).abs().max() <= 2e-5 * (A.float().norm(dim=-1).max() * K.float().norm(dim=-1).max())
+
+
 @pytest.mark.parametrize("N,Z", [(1, 1), (100, 100), (1000, 1), (5000, 257), (70000, 2048), (4096, 4095)])
 def test_topz_select_is_bit_exact(N, Z):
     g = torch.Generator().manual_seed(N + Z)
