@@ -52,9 +52,9 @@ _SIGNATURES = {
     "fm_project_tc": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_void_p, c_int64, c_void_p,
                               c_size_t, c_void_p]),
     "fm_topz_select": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int32, c_void_p, c_int64, c_void_p]),
-    "fm_index_build_workspace_bytes": (c_size_t, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "fm_index_build_workspace_bytes": (c_size_t, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
     "fm_index_build": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_void_p, c_void_p, c_size_t, c_void_p]),
+                               c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "fm_kmeans_workspace_bytes": (c_size_t, [c_int, c_void_p, c_void_p, c_int]),
     "fm_kmeans": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                           c_size_t, c_void_p]),

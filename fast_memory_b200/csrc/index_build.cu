@@ -1,7 +1,11 @@
 // Index build: projection Y = A K^T in the canonical fp32 order, exact top-Z selection per bucket, and
 // the per-segment driver.  Stands in for einsum + topk of the reference (memory.py:261, 273;
 // triton_kernel.py:277-278; README.md:25-27).
+#include "index_fused.cuh"
 #include "simt_tile.cuh"
+#include "topz_row.cuh"
+
+#include <vector>
 
 namespace fm {
 
@@ -38,83 +42,12 @@ project_kernel(const T *__restrict__ A, const T *__restrict__ K, int C, int64_t 
     }
 }
 
-// ---- exact top-Z of a row ------------------------------------------------------------------------------
-// One CTA per row.  Four 8-bit radix passes over the order-preserving keys find the Z-th largest key
-// theta and how many entries equal to theta belong to the result; an ordered compaction then writes
-// the selected indices in ascending order (entries > theta, and the first `want` entries == theta).
-constexpr int kSelThreads = 1024;
-
+// ---- exact top-Z of a row: see topz_row.cuh ---------------------------------------------------------------
 __global__ void __launch_bounds__(kSelThreads)
 topz_select_kernel(const float *__restrict__ Y, int64_t N, int64_t ldy, int Z, int32_t index_base,
                    int32_t *__restrict__ table, int64_t ld_table)
 {
-    __shared__ int hist[256];
-    __shared__ uint32_t s_prefix;
-    __shared__ int s_want;
-    __shared__ int warp_gt[32], warp_eq[32];
-    const float *y = Y + size_t(blockIdx.x) * ldy;
-    int32_t *out = table + size_t(blockIdx.x) * ld_table;
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-
-    if (t == 0) { s_prefix = 0; s_want = Z; }
-    uint32_t mask = 0;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        if (t < 256) hist[t] = 0;
-        __syncthreads();
-        const uint32_t prefix = s_prefix;
-        for (int64_t j = t; j < N; j += kSelThreads) {
-            uint32_t key = float_key(y[j]);
-            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
-        }
-        __syncthreads();
-        if (t == 0) {
-            int want = s_want, b = 255;
-            for (; b > 0; --b) {
-                if (hist[b] >= want) break;
-                want -= hist[b];
-            }
-            s_prefix = prefix | (uint32_t(b) << shift);
-            s_want = want;
-        }
-        mask |= 255u << shift;
-        __syncthreads();
-    }
-    const uint32_t theta = s_prefix;
-    const int want = s_want;
-    int gt_base = 0, eq_base = 0;
-    for (int64_t j0 = 0; j0 < N; j0 += kSelThreads) {
-        const int64_t j = j0 + t;
-        uint32_t key = j < N ? float_key(y[j]) : 0u;
-        const bool gt = j < N && key > theta;
-        const bool eq = j < N && key == theta;
-        const unsigned bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
-        const unsigned lt_mask = (1u << lane) - 1u;
-        int gt_ex = __popc(bg & lt_mask), eq_ex = __popc(be & lt_mask);
-        if (lane == 0) { warp_gt[warp] = __popc(bg); warp_eq[warp] = __popc(be); }
-        __syncthreads();
-        if (warp == 0) {
-            int g = warp_gt[lane], e = warp_eq[lane];
-            int gi = g, ei = e;
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                int tg = __shfl_up_sync(0xffffffffu, gi, off), te = __shfl_up_sync(0xffffffffu, ei, off);
-                if (lane >= off) { gi += tg; ei += te; }
-            }
-            warp_gt[lane] = gi - g;
-            warp_eq[lane] = ei - e;
-            if (lane == 31) { hist[0] = gi; hist[1] = ei; }          // chunk totals
-        }
-        __syncthreads();
-        gt_ex += gt_base + warp_gt[warp];
-        eq_ex += eq_base + warp_eq[warp];
-        if (gt || (eq && eq_ex < want)) {
-            int pos = gt_ex + min(eq_ex, want);
-            if (pos < Z) out[pos] = int32_t(j) + index_base;
-        }
-        gt_base += hist[0];
-        eq_base += hist[1];
-        __syncthreads();
-    }
+    topz_row(Y + size_t(blockIdx.x) * ldy, N, Z, index_base, table + size_t(blockIdx.x) * ld_table);
 }
 
 template <typename T>
@@ -176,35 +109,74 @@ extern "C" int fm_topz_select(const float *Y, int64_t n_rows, int64_t N, int64_t
     return FM_OK;
 }
 
-extern "C" size_t fm_index_build_workspace_bytes(int n_seg, const int64_t *seg_kb, const int64_t *seg_cb,
-                                                 const int64_t *seg_z, int d, int dtype)
+namespace fm {
+// segments that take the tensor-core path, as parallel arrays
+struct FusedList {
+    std::vector<int64_t> kb, nk, cb, nbk, zc, toff;
+    std::vector<int> seg;
+};
+static FusedList fused_segments(int n_seg, const int64_t *seg_kb, const int64_t *seg_cb, const int64_t *seg_z,
+                                const int64_t *table_off, int d, int dtype, int flags)
 {
-    (void)seg_z; (void)d; (void)dtype;
-    size_t need = 256;
+    FusedList F;
+    if (flags & FM_BUILD_EXACT_ONLY) return F;
     for (int s = 0; s < n_seg; ++s) {
+        const int64_t N = seg_kb[s + 1] - seg_kb[s], C = seg_cb[s + 1] - seg_cb[s];
+        if (N <= 0 || C <= 0 || seg_z[s] <= 0) continue;
+        const int64_t zc = std::min(seg_z[s], N);
+        if (!fused_eligible(dtype, d, N, zc)) continue;
+        F.kb.push_back(seg_kb[s]); F.nk.push_back(N); F.cb.push_back(seg_cb[s]); F.nbk.push_back(C); F.zc.push_back(zc);
+        F.toff.push_back(table_off ? table_off[s] : 0);
+        F.seg.push_back(s);
+    }
+    return F;
+}
+}  // namespace fm
+
+extern "C" size_t fm_index_build_workspace_bytes(int n_seg, const int64_t *seg_kb, const int64_t *seg_cb,
+                                                 const int64_t *seg_z, int d, int dtype, int flags)
+{
+    using namespace fm;
+    size_t need = 256;
+    FusedList F = fused_segments(n_seg, seg_kb, seg_cb, seg_z, nullptr, d, dtype, flags);
+    size_t fi = 0;
+    for (int s = 0; s < n_seg; ++s) {
+        if (fi < F.seg.size() && F.seg[fi] == s) { ++fi; continue; }
         int64_t N = seg_kb[s + 1] - seg_kb[s], C = seg_cb[s + 1] - seg_cb[s];
         if (N <= 0 || C <= 0) continue;
-        need = std::max(need, size_t(fm::rows_per_pass(C, N)) * size_t(N) * 4);
+        need = std::max(need, 256 + size_t(rows_per_pass(C, N)) * size_t(N) * 4);
     }
-    return fm::align_up(need, 256);
+    if (!F.seg.empty()) need = std::max(need, fused_plan((int)F.seg.size(), F.nk.data(), F.nbk.data(), F.zc.data()).total);
+    return align_up(need, 256);
 }
 
 extern "C" int fm_index_build(const void *K, const void *A, int dtype, int d, int n_seg, const int64_t *seg_kb,
                               const int64_t *seg_cb, const int64_t *seg_z, const int64_t *table_off, int32_t *table,
-                              void *workspace, size_t workspace_bytes, fm_stream_t stream)
+                              int flags, void *workspace, size_t workspace_bytes, fm_stream_t stream)
 {
     using namespace fm;
     FM_REQUIRE(K && A && seg_kb && seg_cb && seg_z && table_off && table && workspace, "fm_index_build: null pointer");
     FM_REQUIRE(n_seg >= 1, "fm_index_build: bad segment count");
     int rc = check_dim("fm_index_build", d);
     if (rc != FM_OK) return rc;
-    if (workspace_bytes < fm_index_build_workspace_bytes(n_seg, seg_kb, seg_cb, seg_z, d, dtype)) {
+    if (workspace_bytes < fm_index_build_workspace_bytes(n_seg, seg_kb, seg_cb, seg_z, d, dtype, flags)) {
         set_error("fm_index_build: workspace %zu too small", workspace_bytes);
         return FM_ERR_WORKSPACE;
     }
+    cudaStream_t st = (cudaStream_t)stream;
     const size_t eb = elem_bytes(dtype);
-    float *Y = (float *)workspace;
+    FM_CUDA_OK(cudaMemsetAsync(workspace, 0, 256, st));              // status word
+    FusedList F = fused_segments(n_seg, seg_kb, seg_cb, seg_z, table_off, d, dtype, flags);
+    if (!F.seg.empty()) {
+        FM_REQUIRE(((uintptr_t)K | (uintptr_t)A) % 16 == 0, "fm_index_build: K and A must be 16-byte aligned");
+        rc = fused_index_build(K, A, dtype, d, seg_kb[n_seg], seg_cb[n_seg], (int)F.seg.size(), F.kb.data(), F.nk.data(),
+                               F.cb.data(), F.nbk.data(), F.zc.data(), F.toff.data(), table, workspace, st);
+        if (rc != FM_OK) return rc;
+    }
+    float *Y = (float *)((char *)workspace + 256);
+    size_t fi = 0;
     for (int s = 0; s < n_seg; ++s) {
+        if (fi < F.seg.size() && F.seg[fi] == s) { ++fi; continue; }
         const int64_t N = seg_kb[s + 1] - seg_kb[s], C = seg_cb[s + 1] - seg_cb[s];
         if (N <= 0 || C <= 0) continue;
         FM_REQUIRE(seg_z[s] > 0, "fm_index_build: bucket size of segment %d must be positive", s);

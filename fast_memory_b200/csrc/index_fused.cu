@@ -1,0 +1,467 @@
+// Fused index build for 16-bit keys (d = 64 / 128): projection on the tcgen05 tensor cores, selection without
+// ever writing Y.  Stands in for einsum + topk of the reference (memory.py:261, 273; triton_kernel.py:277-278).
+//
+//   1. key_norm_max:   kmax_s = max_j ||k_j|| per segment (bounds the accumulation error of a score).
+//   2. sample scores:  tensor-core projection of every `step`-th key (dense epilogue, small).
+//   3. thresholds:     tau_b = the r-th largest sample score of bucket b, r chosen so that about
+//                      (r / z) Z keys pass and fewer than Z pass with probability ~1e-9 (z = Z / step).
+//   4. candidates:     tensor-core projection of ALL keys; the epilogue appends (score, key) for score >= tau_b
+//                      to the bucket's candidate list, in key order.
+//   5. selection:      per bucket, theta = Z-th largest candidate score.  Scores come from the tensor cores
+//                      (hardware summation order), so only candidates whose score is outside
+//                      [theta - eps, theta + eps] are decided by them; the band in between is re-scored
+//                      with the canonical fp32 chain and ranked exactly (lower index wins ties).  The table row
+//                      (ascending key rows) is therefore bit-identical to the all-fp32 build.
+//   6. fallback:       a bucket whose list overflowed, or whose threshold was too high to prove completeness,
+//                      is rebuilt from canonical scores of all its segment's keys.
+#include "index_fused.cuh"
+#include "simt_tile.cuh"
+#include "tc_project.cuh"
+#include "topz_row.cuh"
+
+#include <cmath>
+#include <vector>
+
+namespace fm {
+
+// eps = kBandEps * ||a_b|| * kmax.  A tensor-core score is within 2^-16 M of the exact dot product and the
+// canonical chain within 2^-17 M (M = ||a|| ||k|| >= sum |a_i k_i|, d <= 128), so two keys can compare
+// differently under the two orders only if their tensor-core scores differ by less than 3 * 2^-16 M.
+constexpr float kBandEps = 1.0f / 4096.0f;
+constexpr int kMaxBand = 2048;              // largest band re-scored exactly; beyond it the bucket goes to the fallback
+constexpr int kMaxFail = 64;                // buckets the fallback can take per group of segments
+constexpr int kSelCThreads = 512;
+constexpr int kMaxSample = 49152;           // sample scores of one bucket held in shared memory (192 KB)
+
+struct FusedSeg {
+    int kb, n_keys;            // first key row (absolute), key count
+    int cb, n_buckets;         // first bucket (global), bucket count
+    int zc;                    // min(Z, N)
+    int rank;                  // which sample order statistic is the threshold (1 = largest)
+    int ns0, ns;               // first sampled row in units of `step`, number of sampled rows
+    int out_row0;              // first bucket of the segment inside the group's arrays
+    unsigned kmax_bits;        // max key norm, as float bits (atomicMax)
+    long long table_off;       // where the segment's table starts
+};
+
+// ---- 1. max key norm per segment ---------------------------------------------------------------------------
+template <typename T>
+__global__ void key_norm_max_kernel(const T *__restrict__ K, int d, FusedSeg *__restrict__ segs)
+{
+    FusedSeg &sg = segs[blockIdx.y];
+    const int lanes_per_row = d / 8;                         // 16-byte pieces per row
+    const int rows_per_warp = 32 / lanes_per_row;
+    const int lane = threadIdx.x & 31, sub = lane % lanes_per_row, rsel = lane / lanes_per_row;
+    const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int n_warps = gridDim.x * (blockDim.x >> 5);
+    float best = 0.f;
+    for (int r = warp_global * rows_per_warp + rsel; r < sg.n_keys; r += n_warps * rows_per_warp) {
+        uint4 raw = *reinterpret_cast<const uint4 *>(K + size_t(sg.kb + r) * d + sub * 8);
+        float f[8];
+        widen8(raw, f, T());
+        float n2 = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) n2 = fmaf(f[e], f[e], n2);
+        for (int off = 1; off < lanes_per_row; off <<= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, off);
+        best = fmaxf(best, n2);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, off));
+    if (lane == 0 && best > 0.f) atomicMax(&sg.kmax_bits, __float_as_uint(sqrtf(best) * 1.0001f));
+}
+
+__device__ __forceinline__ int seg_of_out_row(const FusedSeg *__restrict__ segs, int n_seg, int row)
+{
+    int lo = 0, hi = n_seg;
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (segs[mid].out_row0 <= row) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float key_to_float(uint32_t key)
+{
+    return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
+}
+
+// r-th largest of n keys held in shared memory (all threads of the CTA call; result in every thread).
+// Returns the key and, through `take_equal`, how many entries equal to it lie within the top r.
+__device__ __forceinline__ uint32_t smem_radix_select(const uint32_t *__restrict__ keys, int n, int r, int *hist, int *s_scratch,
+                                                      int &take_equal)
+{
+    uint32_t prefix = 0, mask = 0;
+    int want = r;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const uint32_t key = keys[i];
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int b = 255, w = want;
+            for (; b > 0; --b) {
+                if (hist[b] >= w) break;
+                w -= hist[b];
+            }
+            s_scratch[0] = b;
+            s_scratch[1] = w;
+        }
+        __syncthreads();
+        prefix |= uint32_t(s_scratch[0]) << shift;
+        want = s_scratch[1];
+        mask |= 255u << shift;
+        __syncthreads();
+    }
+    take_equal = want;
+    return prefix;
+}
+
+// ---- 3. thresholds from the sample scores -----------------------------------------------------------------------
+__global__ void __launch_bounds__(kSelCThreads)
+sample_tau_kernel(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg, float *__restrict__ tau)
+{
+    extern __shared__ uint32_t keys[];
+    __shared__ int hist[256];
+    __shared__ int scratch[2];
+    const int row = blockIdx.x;
+    const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
+    const float *y = Ys + size_t(row) * ldy;
+    for (int i = threadIdx.x; i < sg.ns; i += blockDim.x) keys[i] = float_key(y[i]);
+    __syncthreads();
+    int take;
+    const uint32_t k = smem_radix_select(keys, sg.ns, min(sg.rank, sg.ns), hist, scratch, take);
+    if (threadIdx.x == 0) tau[row] = key_to_float(k);
+}
+
+// ---- 5. exact selection among the candidates ---------------------------------------------------------------------
+struct SelParams {
+    const FusedSeg *segs;
+    int n_seg;
+    int n_ranges, cap;
+    const uint2 *cand;
+    const int *cand_count;
+    const float *tau;
+    const void *A, *K;
+    int d;
+    int32_t *table;
+    int *fail_count;           // buckets handed to the fallback
+    int *fail_list;            // their rows inside the group
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kSelCThreads)
+candidate_select_kernel(SelParams p)
+{
+    extern __shared__ __align__(16) unsigned char sel_smem[];
+    uint32_t *keys = reinterpret_cast<uint32_t *>(sel_smem);           // [cap] score keys, later the selection flags
+    int32_t *idxs = reinterpret_cast<int32_t *>(keys + p.cap);         // [cap] key index inside the segment
+    int32_t *band = idxs + p.cap;                                       // [kMaxBand] candidate positions of the band
+    float *band_y = reinterpret_cast<float *>(band + kMaxBand);        // [kMaxBand] their canonical scores
+    __shared__ int hist[256];
+    __shared__ int scratch[2];
+    __shared__ int s_n, s_fail, s_nin, s_nband;
+    __shared__ int warp_sel[kSelCThreads / 32];
+    __shared__ float s_anorm;
+
+    const int row = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const FusedSeg sg = p.segs[seg_of_out_row(p.segs, p.n_seg, row)];
+    const int bucket = sg.cb + (row - sg.out_row0);
+    const int Z = sg.zc;
+    const T *a_row = reinterpret_cast<const T *>(p.A) + size_t(bucket) * p.d;
+
+    // candidate counts per range; two ranges share a buffer and must not have met in the middle
+    if (t == 0) {
+        const int nb = max(1, p.n_ranges / 2), sub_cap = p.cap / nb;
+        int n = 0, fail = 0;
+        for (int b = 0; b < nb; ++b) {
+            const int c0 = p.cand_count[size_t(row) * p.n_ranges + 2 * b];
+            const int c1 = p.n_ranges > 1 ? p.cand_count[size_t(row) * p.n_ranges + 2 * b + 1] : 0;
+            if (c0 + c1 > sub_cap) fail = 1;
+            n += c0 + c1;
+        }
+        if (n < Z) fail = 1;
+        s_n = n;
+        s_fail = fail;
+        s_nin = 0;
+        s_nband = 0;
+    }
+    if (warp == 1) {                                         // ||a_b||
+        float n2 = 0.f;
+        for (int i = lane; i < p.d; i += 32) {
+            const float v = Elem<T>::to_f32(a_row[i]);
+            n2 = fmaf(v, v, n2);
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, off);
+        if (lane == 0) s_anorm = sqrtf(n2) * 1.0001f;
+    }
+    __syncthreads();
+    const int n = s_n;
+    if (!s_fail) {
+        // gather the lists in key order: range 0 upward, range 1 downward from the end of the shared buffer, ...
+        const int nb = max(1, p.n_ranges / 2), sub_cap = p.cap / nb;
+        int base = 0;
+        for (int r = 0; r < p.n_ranges; ++r) {
+            const int cnt = p.cand_count[size_t(row) * p.n_ranges + r];
+            const uint2 *buf = p.cand + size_t(row) * p.cap + size_t(r / 2) * sub_cap;
+            for (int i = t; i < cnt; i += kSelCThreads) {
+                const uint2 e = (r & 1) ? buf[sub_cap - 1 - i] : buf[i];
+                keys[base + i] = float_key(__uint_as_float(e.x));
+                idxs[base + i] = int32_t(e.y);
+            }
+            base += cnt;
+        }
+        __syncthreads();
+        int take;
+        const uint32_t theta_key = smem_radix_select(keys, n, Z, hist, scratch, take);
+        const float theta = key_to_float(theta_key);
+        const float eps = kBandEps * s_anorm * __uint_as_float(sg.kmax_bits);
+        const float lo = theta - eps, hi = theta + eps;
+        // everything at or above lo has to be among the candidates, i.e. the threshold was low enough
+        if (t == 0 && !(p.tau[row] <= lo) && n < sg.n_keys) s_fail = 1;
+        // classify: flag 1 = certainly selected, 2 = band, 0 = out
+        int my_in = 0;
+        for (int i = t; i < n; i += kSelCThreads) {
+            const float y = key_to_float(keys[i]);
+            uint32_t flag = 0;
+            if (y > hi) { flag = 1; ++my_in; }
+            else if (y >= lo) {
+                flag = 2;
+                const int slot = atomicAdd(&s_nband, 1);
+                if (slot < kMaxBand) band[slot] = i;
+            }
+            keys[i] = flag;
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) my_in += __shfl_xor_sync(0xffffffffu, my_in, off);
+        if (lane == 0 && my_in) atomicAdd(&s_nin, my_in);
+        __syncthreads();
+        const int n_band = s_nband, need = Z - s_nin;
+        if (t == 0 && (n_band > kMaxBand || need < 0 || need > n_band)) s_fail = 1;
+        __syncthreads();
+        if (!s_fail) {
+            // canonical scores of the band, then an exact rank: better = larger score, then lower key index
+            const T *Kseg = reinterpret_cast<const T *>(p.K) + size_t(sg.kb) * p.d;
+            for (int b = t; b < n_band; b += kSelCThreads)
+                band_y[b] = canonical_dot(a_row, Kseg + size_t(idxs[band[b]]) * p.d, p.d);
+            __syncthreads();
+            for (int b = t; b < n_band; b += kSelCThreads) {
+                const float y = band_y[b];
+                const int id = idxs[band[b]];
+                int rank = 0;
+                for (int o = 0; o < n_band; ++o) {
+                    const float yo = band_y[o];
+                    rank += (yo > y) || (yo == y && idxs[band[o]] < id);
+                }
+                keys[band[b]] = rank < need ? 1u : 0u;
+            }
+            __syncthreads();
+            // ordered compaction: the lists are in key order, so is the table row
+            int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
+            int base_out = 0;
+            for (int i0 = 0; i0 < n; i0 += kSelCThreads) {
+                const int i = i0 + t;
+                const bool sel = i < n && keys[i] == 1u;
+                const unsigned bal = __ballot_sync(0xffffffffu, sel);
+                if (lane == 0) warp_sel[warp] = __popc(bal);
+                __syncthreads();
+                int before = 0, total = 0;
+                for (int w = 0; w < kSelCThreads / 32; ++w) {
+                    const int c = warp_sel[w];
+                    before += w < warp ? c : 0;
+                    total += c;
+                }
+                const int pos = base_out + before + __popc(bal & ((1u << lane) - 1u));
+                if (sel && pos < Z) out[pos] = sg.kb + idxs[i];
+                base_out += total;
+                __syncthreads();
+            }
+        }
+    }
+    __syncthreads();
+    if (t == 0 && s_fail) {
+        const int slot = atomicAdd(p.fail_count, 1);
+        if (slot < kMaxFail) p.fail_list[slot] = row;
+    }
+}
+
+// ---- 6. fallback: canonical scores of a whole segment for the listed buckets, then the exact row select ---------
+template <typename T>
+__global__ void fallback_scores_kernel(const FusedSeg *__restrict__ segs, int n_seg, const int *__restrict__ fail_count,
+                                       const int *__restrict__ fail_list, const T *__restrict__ A, const T *__restrict__ K, int d,
+                                       float *__restrict__ Yf, int64_t ldf)
+{
+    if ((int)blockIdx.y >= min(*fail_count, kMaxFail)) return;
+    const int row = fail_list[blockIdx.y];
+    const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
+    const T *a_row = A + size_t(sg.cb + (row - sg.out_row0)) * d;
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < sg.n_keys; j += gridDim.x * blockDim.x)
+        Yf[size_t(blockIdx.y) * ldf + j] = canonical_dot(a_row, K + size_t(sg.kb + j) * d, d);
+}
+
+__global__ void __launch_bounds__(kSelThreads)
+fallback_select_kernel(const FusedSeg *__restrict__ segs, int n_seg, const int *__restrict__ fail_count,
+                       const int *__restrict__ fail_list, const float *__restrict__ Yf, int64_t ldf, int32_t *__restrict__ table,
+                       int *__restrict__ status)
+{
+    if (blockIdx.x == 0 && threadIdx.x == 0 && *fail_count > kMaxFail) atomicExch(status, 4);
+    if ((int)blockIdx.x >= min(*fail_count, kMaxFail)) return;
+    const int row = fail_list[blockIdx.x];
+    const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
+    topz_row(Yf + size_t(blockIdx.x) * ldf, sg.n_keys, sg.zc, sg.kb, table + sg.table_off + size_t(row - sg.out_row0) * sg.zc);
+}
+
+// ---- host ----------------------------------------------------------------------------------------------------------
+bool fused_eligible(int dtype, int d, int64_t n_keys, int64_t zc)
+{
+    // buckets much smaller than the segment (otherwise a threshold filters nothing), yet not so small that the
+    // key sample needed to estimate the threshold outgrows shared memory
+    return (dtype == FM_BF16 || dtype == FM_F16) && (d == 64 || d == 128) && n_keys >= 8192 && zc * 4 <= n_keys && zc >= 64 &&
+           n_keys <= zc * 4096 && zc <= 12288;      // and the candidate list of a bucket has to fit in shared memory
+}
+
+static int sample_rank(double z) { return (int)std::ceil(z + 6.0 * std::sqrt(z) + 2.0); }
+
+// Layout of the workspace for the eligible segments (`idx` lists them).  Groups are sized so that the sample
+// scores and the candidate lists of one group stay within ~1.5 GB.
+FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, const int64_t *zc)
+{
+    FusedPlan P = {};
+    int64_t zmin = INT64_MAX, total_b = 0;
+    for (int i = 0; i < n; ++i) { zmin = std::min(zmin, zc[i]); P.max_keys = std::max(P.max_keys, n_keys[i]); total_b += n_buckets[i]; }
+    // about 128 of a bucket's keys in the sample; a coarser step when the sampled row would not fit in shared memory
+    // (kMaxSample scores), never so coarse that fewer than 8 of them are expected
+    P.step = (int)std::max<int64_t>(std::min<int64_t>(64, zmin / 128), ceil_div(P.max_keys, kMaxSample));
+    P.step = (int)std::max<int64_t>(1, std::min<int64_t>(P.step, zmin / 8));
+    int cap = 0;
+    for (int i = 0; i < n; ++i) {
+        const double z = double(zc[i]) / P.step;
+        const double r = sample_rank(z);
+        cap = std::max(cap, (int)std::ceil(P.step * (r + 6.0 * std::sqrt(r))) + 64);
+        P.ld_sample = std::max<int64_t>(P.ld_sample, n_keys[i] / P.step + 2);
+    }
+    P.cap = (cap + 7) / 8 * 8;                               // divisible by the buffers per row (1, 1 or 2)
+    P.ld_sample = (P.ld_sample + 3) / 4 * 4;
+    const size_t per_bucket = size_t(P.ld_sample) * 4 + size_t(P.cap) * 8;
+    int64_t max_b = 0;
+    for (int i = 0; i < n; ++i) max_b = std::max(max_b, n_buckets[i]);
+    P.group_buckets = std::max<int64_t>(max_b, std::min<int64_t>(total_b, int64_t((size_t(3) << 29) / per_bucket)));
+    size_t off = 0;
+    P.off_status = off; off += 256;
+    P.off_segs = off;   off += align_up(size_t(n) * sizeof(FusedSeg), 256);
+    P.off_tcseg = off;  off += align_up(size_t(n) * sizeof(TcSeg) * 2, 256);
+    P.off_tau = off;    off += align_up(size_t(P.group_buckets) * 4, 256);
+    P.off_count = off;  off += align_up(size_t(P.group_buckets) * 4 * 4, 256);
+    P.off_fail = off;   off += align_up(size_t(kMaxFail + 1) * 4, 256);
+    P.off_ys = off;     off += align_up(size_t(P.group_buckets) * P.ld_sample * 4, 256);
+    P.off_cand = off;   off += align_up(size_t(P.group_buckets) * P.cap * 8, 256);
+    P.off_yf = off;     off += align_up(size_t(kMaxFail) * P.max_keys * 4, 256);
+    P.total = off;
+    return P;
+}
+
+// Builds the table rows of the listed segments.  status word (ws + 0): 0 = ok, 1-3 = a tensor-core pipeline
+// wait gave up, 4 = more buckets needed the fallback than it can take.
+template <typename T>
+static int fused_build_impl(const void *K, const void *A, int d, int64_t total_key_rows, int64_t total_buckets, int n,
+                            const int64_t *kb, const int64_t *nk, const int64_t *cb, const int64_t *nbk, const int64_t *zc,
+                            const int64_t *table_off, int32_t *table, char *ws, cudaStream_t st)
+{
+    const int dtype = Elem<T>::id;
+    FusedPlan P = fused_plan(n, nk, nbk, zc);
+    CUtensorMap tmA, tmK, tmKs;
+    int rc = make_tensor_map_2d(&tmA, A, dtype, (uint64_t)total_buckets, (uint64_t)d, (uint64_t)d * 2, kTcBM);
+    if (rc != FM_OK) return rc;
+    rc = make_tensor_map_2d(&tmK, K, dtype, (uint64_t)total_key_rows, (uint64_t)d, (uint64_t)d * 2, kTcBN);
+    if (rc != FM_OK) return rc;
+    rc = make_tensor_map_2d(&tmKs, K, dtype, (uint64_t)ceil_div(total_key_rows, P.step), (uint64_t)d, (uint64_t)d * 2 * P.step, kTcBN);
+    if (rc != FM_OK) return rc;
+    FM_CUDA_OK(cudaMemsetAsync(ws + P.off_status, 0, 256, st));
+
+    std::vector<FusedSeg> hs(n);
+    std::vector<TcSeg> ht(2 * n);
+    int g0 = 0;
+    while (g0 < n) {
+        // one group: consecutive segments whose buckets fit the group arrays
+        int g1 = g0;
+        int64_t rows = 0, mtiles = 0;
+        while (g1 < n && rows + nbk[g1] <= P.group_buckets) {
+            FusedSeg &s = hs[g1];
+            s.kb = (int)kb[g1]; s.n_keys = (int)nk[g1]; s.cb = (int)cb[g1]; s.n_buckets = (int)nbk[g1]; s.zc = (int)zc[g1];
+            s.rank = sample_rank(double(zc[g1]) / P.step);
+            s.ns0 = (int)ceil_div(kb[g1], P.step);
+            s.ns = (int)(ceil_div(kb[g1] + nk[g1], P.step) - s.ns0);
+            s.out_row0 = (int)rows; s.kmax_bits = 0; s.table_off = table_off[g1];
+            ht[g1] = TcSeg{s.cb, s.n_buckets, s.ns0, s.ns, (int)mtiles, s.out_row0};            // sample pass
+            ht[n + g1] = TcSeg{s.cb, s.n_buckets, s.kb, s.n_keys, (int)mtiles, s.out_row0};      // candidate pass
+            rows += nbk[g1];
+            mtiles += ceil_div(nbk[g1], kTcBM);
+            ++g1;
+        }
+        const int ng = g1 - g0;
+        FusedSeg *dsegs = (FusedSeg *)(ws + P.off_segs) + g0;
+        TcSeg *dtc_s = (TcSeg *)(ws + P.off_tcseg) + g0, *dtc_m = (TcSeg *)(ws + P.off_tcseg) + n + g0;
+        FM_CUDA_OK(cudaMemcpyAsync(dsegs, hs.data() + g0, sizeof(FusedSeg) * ng, cudaMemcpyHostToDevice, st));
+        FM_CUDA_OK(cudaMemcpyAsync(dtc_s, ht.data() + g0, sizeof(TcSeg) * ng, cudaMemcpyHostToDevice, st));
+        FM_CUDA_OK(cudaMemcpyAsync(dtc_m, ht.data() + n + g0, sizeof(TcSeg) * ng, cudaMemcpyHostToDevice, st));
+        FM_CUDA_OK(cudaMemsetAsync(ws + P.off_fail, 0, 256, st));
+        float *tau = (float *)(ws + P.off_tau);
+        int *counts = (int *)(ws + P.off_count);
+        int *fail_count = (int *)(ws + P.off_fail), *fail_list = fail_count + 1;
+        float *Ys = (float *)(ws + P.off_ys);
+        uint2 *cand = (uint2 *)(ws + P.off_cand);
+        float *Yf = (float *)(ws + P.off_yf);
+
+        key_norm_max_kernel<T><<<dim3(std::max(1, 2 * sm_count() / ng), ng), 256, 0, st>>>((const T *)K, d, dsegs);
+        FM_LAUNCHED("key_norm_max_kernel");
+
+        const int sms = sm_count();
+        TcParams tp = {};
+        tp.segs = dtc_s; tp.n_seg = ng; tp.status = (int *)(ws + P.off_status);
+        tp.Y = Ys; tp.ldy = P.ld_sample;
+        {
+            const int64_t tiles = ceil_div(P.ld_sample, kTcBN);
+            tp.n_ranges = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, ceil_div(2 * sms, mtiles)));
+            rc = tc_project_launch(tmA, tmKs, tp, int(mtiles) * tp.n_ranges, d, true, dtype == FM_BF16, st);
+            if (rc != FM_OK) return rc;
+        }
+        FM_CUDA_OK(cudaFuncSetAttribute(sample_tau_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(P.ld_sample * 4)));
+        sample_tau_kernel<<<(unsigned)rows, kSelCThreads, size_t(P.ld_sample) * 4, st>>>(Ys, P.ld_sample, dsegs, ng, tau);
+        FM_LAUNCHED("sample_tau_kernel");
+
+        tp.segs = dtc_m;
+        tp.tau = tau; tp.cand = cand; tp.cap = P.cap; tp.cand_count = counts;
+        tp.n_ranges = mtiles * 10 >= sms * 8 ? 1 : (mtiles * 10 >= sms * 4 ? 2 : 4);
+        rc = tc_project_launch(tmA, tmK, tp, int(mtiles) * tp.n_ranges, d, false, dtype == FM_BF16, st);
+        if (rc != FM_OK) return rc;
+
+        SelParams sp = {dsegs, ng, tp.n_ranges, P.cap, cand, counts, tau, A, K, d, table, fail_count, fail_list};
+        const size_t sel_smem = size_t(P.cap) * 8 + size_t(kMaxBand) * 8;
+        FM_CUDA_OK(cudaFuncSetAttribute(candidate_select_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sel_smem));
+        candidate_select_kernel<T><<<(unsigned)rows, kSelCThreads, sel_smem, st>>>(sp);
+        FM_LAUNCHED("candidate_select_kernel");
+
+        fallback_scores_kernel<T><<<dim3((unsigned)std::min<int64_t>(ceil_div(P.max_keys, 256), 4 * sms), kMaxFail), 256, 0, st>>>(
+            dsegs, ng, fail_count, fail_list, (const T *)A, (const T *)K, d, Yf, P.max_keys);
+        FM_LAUNCHED("fallback_scores_kernel");
+        fallback_select_kernel<<<kMaxFail, kSelThreads, 0, st>>>(dsegs, ng, fail_count, fail_list, Yf, P.max_keys, table,
+                                                                  (int *)(ws + P.off_status));
+        FM_LAUNCHED("fallback_select_kernel");
+        g0 = g1;
+    }
+    return FM_OK;
+}
+
+int fused_index_build(const void *K, const void *A, int dtype, int d, int64_t total_key_rows, int64_t total_buckets, int n,
+                      const int64_t *kb, const int64_t *nk, const int64_t *cb, const int64_t *nbk, const int64_t *zc,
+                      const int64_t *table_off, int32_t *table, void *ws, cudaStream_t st)
+{
+    if (dtype == FM_BF16)
+        return fused_build_impl<__nv_bfloat16>(K, A, d, total_key_rows, total_buckets, n, kb, nk, cb, nbk, zc, table_off, table, (char *)ws, st);
+    return fused_build_impl<__half>(K, A, d, total_key_rows, total_buckets, n, kb, nk, cb, nbk, zc, table_off, table, (char *)ws, st);
+}
+
+}  // namespace fm

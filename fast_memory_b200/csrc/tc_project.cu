@@ -9,7 +9,7 @@
 // Per 256-key tile: K tile -> shared memory (3-stage ring, 64 KB per stage at d = 128), 8 UMMAs
 // (M = 128, N = 256, K = 16) into one of two 256-column accumulators, so the MMAs of tile t + 1 overlap the
 // epilogue of tile t.  Every mbarrier wait is bounded; on a give-up the CTA records a status and unwinds.
-#include "tc_utils.cuh"
+#include "tc_project.cuh"
 
 #include <mutex>
 
@@ -17,35 +17,12 @@ namespace fm {
 
 namespace {
 
-constexpr int kBM = 128;                    // bucket rows per tile (UMMA M)
-constexpr int kBN = 256;                    // keys per tile (UMMA N)
+constexpr int kBM = kTcBM;                  // bucket rows per tile (UMMA M)
+constexpr int kBN = kTcBN;                  // keys per tile (UMMA N)
 constexpr int kStagesTc = 3;
 constexpr int kTcThreads = 192;
 
 }  // namespace
-
-struct TcSeg {
-    int a_row0;        // first row of A of this segment (tensor-map row)
-    int n_buckets;
-    int k_row0;        // first key row of this segment in the key tensor map's row coordinate
-    int n_keys;        // columns of this segment's projection (keys, or sampled keys)
-    int mtile0;        // index of the segment's first bucket tile in the global list
-};
-
-struct TcParams {
-    const TcSeg *segs;
-    int n_seg;
-    int n_ranges;          // key ranges per bucket tile
-    // dense epilogue
-    float *Y;
-    int64_t ldy;
-    // candidate epilogue
-    const float *tau;      // [total buckets] threshold of every bucket
-    uint2 *cand;           // [total buckets][cap] (score bits, key index local to the segment)
-    int cap;
-    int *cand_count;       // [total buckets][n_ranges]
-    int *status;           // set non-zero when a wait gave up
-};
 
 template <int D, bool DENSE>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -148,7 +125,7 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int q = warp & 3;                              // TMEM lane quarter this warp may read
         const int m = q * 32 + lane;                         // row of the tile
         const bool row_ok = m0 + m < sg.n_buckets;
-        const int grow = sg.a_row0 + m0 + m;                 // global bucket
+        const int grow = sg.out_row0 + m0 + m;               // row of this bucket in the outputs
         float tau = 0.f;
         uint2 *list = nullptr;
         int cursor = 0, dir = 1, sub_cap = 0;
@@ -303,7 +280,7 @@ extern "C" int fm_project_tc(const void *A, const void *K, int dtype, int64_t C,
     if (rc != FM_OK) return rc;
     rc = make_tensor_map_2d(&tmK, K, dtype, (uint64_t)n_cols, (uint64_t)d, (uint64_t)d * 2 * key_step, kBN);
     if (rc != FM_OK) return rc;
-    TcSeg seg = {0, (int)C, 0, (int)n_cols, 0};
+    TcSeg seg = {0, (int)C, 0, (int)n_cols, 0, 0};
     char *ws = (char *)workspace;
     FM_CUDA_OK(cudaMemsetAsync(ws, 0, 256, st));
     FM_CUDA_OK(cudaMemcpyAsync(ws + 64, &seg, sizeof(seg), cudaMemcpyHostToDevice, st));

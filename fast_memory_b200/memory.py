@@ -74,7 +74,7 @@ class Memory:
     def build(cls, k: torch.Tensor, v: torch.Tensor, *, n_buckets: Optional[IntOrSeq] = None,
               bucket_size: IntOrSeq, A: Optional[torch.Tensor] = None, kmeans_iters: int = 2,
               kmeans_init: Optional[torch.Tensor] = None, cu_seqlens_k: Optional[Sequence[int]] = None,
-              key_range: Optional[Tuple[int, int]] = None) -> "Memory":
+              key_range: Optional[Tuple[int, int]] = None, check: bool = True, exact_only: bool = False) -> "Memory":
         """Index ``k`` / ``v``.
 
         :param k, v: ``[H, N, d]`` (or ``[H, N_total, d]`` with ``cu_seqlens_k``)
@@ -85,6 +85,9 @@ class Memory:
             ``kmeans_init``
         :param kmeans_init: rows whose first C (per segment) seed the centroids: ``[H, >=C, d]`` (varlen:
             packed like A).  Defaults to the first C keys of each segment
+        :param check: read the build's status word back (one device sync) and raise if the tensor-core path
+            gave up; pass False to stay asynchronous and call :meth:`check_build` later
+        :param exact_only: score every key with the fp32 chain instead of the tensor-core filter
         :param key_range: keep only table entries whose per-head key index lies in ``[lo, hi)`` (the
             filter the reference hard-codes at tk:283); uniform memories only
         """
@@ -152,11 +155,15 @@ class Memory:
 
         table = torch.empty(max(table_off[-1], 1), dtype=torch.int32, device=dev)
         kb, cb, zz, to = L.host_i64(seg_kb), L.host_i64(seg_cb), L.host_i64(seg_z), L.host_i64(table_off[:-1])
-        need = L.lib().fm_index_build_workspace_bytes(n_seg, kb, cb, zz, d, L.dtype_id(k.dtype))
+        flags = 1 if exact_only else 0
+        need = L.lib().fm_index_build_workspace_bytes(n_seg, kb, cb, zz, d, L.dtype_id(k.dtype), flags)
         ws = ops._ws.get("build", need, dev)
         L.check(L.lib().fm_index_build(L.ptr(kf), L.ptr(A2), L.dtype_id(k.dtype), d, n_seg, kb, cb, zz, to,
-                                       L.ptr(table), L.ptr(ws), ws.numel(), L.stream_ptr(dev)), "fm_index_build")
+                                       L.ptr(table), flags, L.ptr(ws), ws.numel(), L.stream_ptr(dev)), "fm_index_build")
+        self.build_status = ws[:4].view(torch.int32)[0].clone()  # device scalar: 0 = ok (see check_build)
         self.table = table
+        if check:
+            self.check_build()
         blen = torch.tensor(bucket_len, dtype=torch.int64)
         bucket_off = torch.zeros(total_c + 1, dtype=torch.int64)
         torch.cumsum(blen, 0, out=bucket_off[1:])
@@ -166,6 +173,12 @@ class Memory:
         if key_range is not None:
             self._apply_key_range(key_range)
         return self
+
+    def check_build(self) -> None:
+        """Raise if the index build reported a failure (synchronises with the device)."""
+        status = int(self.build_status.item())
+        if status:
+            raise L.FastMemError(f"index build failed with status {status}: rebuild with exact_only=True")
 
     def _apply_key_range(self, key_range):
         """Keep table entries whose per-head key index is in [lo, hi) (compaction like tk:283-286)."""

@@ -162,13 +162,20 @@ int fm_topz_select(const float *Y, int64_t n_rows, int64_t N, int64_t ldy, int64
  * Index build for a whole memory: for every segment, table rows of its buckets = top-min(Z_s, N_s)
  * keys by projection, as ABSOLUTE key rows in ascending order.
  * Replaces: einsum + topk, mem:261 + 273 and tk:277-278.
+ * 16-bit keys with d = 64 / 128 and buckets much smaller than the segment take the fused path: tcgen05
+ * projection whose epilogue keeps only scores above a per-bucket threshold (estimated from a key sample),
+ * then an exact selection that re-scores near-ties with the fp32 chain - same table bits as the all-fp32
+ * path, which every other case (and flags = FM_BUILD_EXACT_ONLY) uses.  After the stream has completed,
+ * the first int32 of the workspace is a status word: 0 = ok, non-zero = the fused path gave up (rebuild
+ * with FM_BUILD_EXACT_ONLY).
  * seg_kb, seg_cb [n_seg+1] and seg_z [n_seg] are HOST arrays.  Bucket b of segment s is written at
  * table + table_off[s] + (b - seg_cb[s]) * min(seg_z[s], N_s)  (table_off: HOST, n_seg entries).
  * ------------------------------------------------------------------------------------------- */
+#define FM_BUILD_EXACT_ONLY 1 /* flags: skip the tensor-core path, score every key with the fp32 chain */
 size_t fm_index_build_workspace_bytes(int n_seg, const int64_t *seg_kb, const int64_t *seg_cb, const int64_t *seg_z,
-                                      int d, int dtype);
+                                      int d, int dtype, int flags);
 int fm_index_build(const void *K, const void *A, int dtype, int d, int n_seg, const int64_t *seg_kb,
-                   const int64_t *seg_cb, const int64_t *seg_z, const int64_t *table_off, int32_t *table,
+                   const int64_t *seg_cb, const int64_t *seg_z, const int64_t *table_off, int32_t *table, int flags,
                    void *workspace, size_t workspace_bytes, fm_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------

@@ -164,6 +164,61 @@ def test_cut_down_configs(name, H, N, S):
     assert_attn_close(o.reshape(H, G * S, -1), lse.reshape(H, G * S), o_ref, lse_ref, cfg.dtype)
 
 
+@pytest.mark.parametrize("dtype,d", [(torch.bfloat16, 128), (torch.float16, 64)])
+def test_fused_build_equals_exact_build(dtype, d):
+    """Tensor-core filter + exact band re-scoring against the all-fp32 build: same table, bit for bit."""
+    g = torch.Generator().manual_seed(77)
+    H, N, C, Z = 2, 40000, 160, 512                       # 2 bucket tiles per head, the second one ragged
+    cent = torch.nn.functional.normalize(torch.randn(64, d, generator=g), dim=-1)
+    k = (cent[torch.randint(64, (H * N,), generator=g)] + 0.25 * torch.randn(H * N, d, generator=g)).reshape(H, N, d).to(dtype)
+    v = torch.randn(H, N, d, generator=g).to(dtype)
+    A = torch.nn.functional.normalize(torch.randn(H, C, d, generator=g), dim=-1).to(dtype)
+    fused = fm.Memory.build(k.to(DEV), v.to(DEV), A=A.to(DEV), bucket_size=Z)
+    exact = fm.Memory.build(k.to(DEV), v.to(DEV), A=A.to(DEV), bucket_size=Z, exact_only=True)
+    assert torch.equal(fused.table, exact.table)
+    ok, why = tables_equal_as_sets(fused.table_of(1).cpu().numpy(), O.topz(O.project(A[1], k[1]), Z))
+    assert ok, why
+
+
+def test_fused_build_with_massive_ties_uses_the_fallback():
+    """Every key repeated 64 times: exact ties straddle the Z-th score and are resolved by index inside the
+    band.  With 8 distinct keys repeated 4096 times the band is larger than the kernel re-scores in place and
+    the buckets are rebuilt by the fallback; lower index must still win."""
+    g = torch.Generator().manual_seed(78)
+    N, C, Z, d = 32768, 16, 1000, 128
+    base = torch.randn(512, d, generator=g).bfloat16()
+    k = base.repeat(64, 1)[torch.randperm(N, generator=g)][None].contiguous()
+    A = torch.randn(1, C, d, generator=g).bfloat16()
+    mem = fm.Memory.build(k.to(DEV), k.to(DEV), A=A.to(DEV), bucket_size=Z)
+    ok, why = tables_equal_as_sets(mem.table_of(0).cpu().numpy(), O.topz(O.project(A[0], k[0]), Z))
+    assert ok, why
+    k = base[:8].repeat(4096, 1)[torch.randperm(N, generator=g)][None].contiguous()
+    A = torch.randn(1, C, d, generator=g).bfloat16()
+    mem = fm.Memory.build(k.to(DEV), k.to(DEV), A=A.to(DEV), bucket_size=Z)
+    ok, why = tables_equal_as_sets(mem.table_of(0).cpu().numpy(), O.topz(O.project(A[0], k[0]), Z))
+    assert ok, why
+    # with more such buckets than the fallback takes, the build reports it and the exact path still works
+    A2 = torch.randn(1, 128, d, generator=g).bfloat16()
+    with pytest.raises(fm.FastMemError):
+        fm.Memory.build(k.to(DEV), k.to(DEV), A=A2.to(DEV), bucket_size=Z)
+    mem2 = fm.Memory.build(k.to(DEV), k.to(DEV), A=A2.to(DEV), bucket_size=Z, exact_only=True)
+    ok, why = tables_equal_as_sets(mem2.table_of(0).cpu().numpy(), O.topz(O.project(A2[0], k[0]), Z))
+    assert ok, why
+
+
+def test_fused_build_keys_sorted_by_score():
+    """Keys ordered so that one bucket's best keys all sit at the end of the segment (one key range)."""
+    g = torch.Generator().manual_seed(79)
+    N, C, Z, d = 65536, 128, 1024, 128
+    A = torch.nn.functional.normalize(torch.randn(1, C, d, generator=g), dim=-1).bfloat16()
+    k = torch.randn(N, d, generator=g).bfloat16()
+    order = torch.argsort(k.float() @ A[0, 5].float())            # ascending score for bucket 5
+    k = k[order][None].contiguous()
+    mem = fm.Memory.build(k.to(DEV), k.to(DEV), A=A.to(DEV), bucket_size=Z)
+    ok, why = tables_equal_as_sets(mem.table_of(0).cpu().numpy(), O.topz(O.project(A[0], k[0]), Z))
+    assert ok, why
+
+
 def test_varlen_memory_matches_per_sequence_calls():
     """cfg4 layout cut down: packed keys/queries with cu_seqlens equal independent per-sequence memories."""
     cfg = synth.config("cfg4")
