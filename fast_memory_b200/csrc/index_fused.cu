@@ -85,55 +85,159 @@ __device__ __forceinline__ float key_to_float(uint32_t key)
     return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
 }
 
-// r-th largest of n keys held in shared memory (all threads of the CTA call; result in every thread).
-// Returns the key and, through `take_equal`, how many entries equal to it lie within the top r.
-__device__ __forceinline__ uint32_t smem_radix_select(const uint32_t *__restrict__ keys, int n, int r, int *hist, int *s_scratch,
-                                                      int &take_equal)
+// ---- selection of the r-th largest of n floats in shared memory --------------------------------------------------
+// All threads of the CTA call.  The values are binned LINEARLY between their minimum and maximum (scores near a
+// threshold are spread over a narrow interval, where radix digits of the float would all collide), the bin that
+// holds the r-th largest is found from the top, and the search recurses into that bin until it holds at most
+// kSmallSel values, which are ranked directly.  Returns theta = the r-th largest value; every thread gets it.
+constexpr int kSelBins = 2048;
+constexpr int kSmallSel = 256;
+
+struct SelScratch {
+    int hist[kSelBins];
+    float small[kSmallSel];
+    float red[64];
+    int bin, want, count, n_small;
+    float lo, hi, theta;
+};
+
+__device__ __forceinline__ void block_minmax(const float *__restrict__ y, int n, float lo, float hi, SelScratch &S,
+                                             float &out_lo, float &out_hi)
 {
-    uint32_t prefix = 0, mask = 0;
-    int want = r;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
-        __syncthreads();
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const uint32_t key = keys[i];
-            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+    // min / max of the values inside [lo, hi]
+    float mn = INFINITY, mx = -INFINITY;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = y[i];
+        if (v >= lo && v <= hi) { mn = fminf(mn, v); mx = fmaxf(mx, v); }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) { S.red[warp] = mn; S.red[32 + warp] = mx; }
+    __syncthreads();
+    if (warp == 0) {
+        mn = lane < nw ? S.red[lane] : INFINITY;
+        mx = lane < nw ? S.red[32 + lane] : -INFINITY;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
         }
+        if (lane == 0) { S.lo = mn; S.hi = mx; }
+    }
+    __syncthreads();
+    out_lo = S.lo;
+    out_hi = S.hi;
+}
+
+__device__ __forceinline__ float smem_select_rth(const float *__restrict__ y, int n, int r, SelScratch &S)
+{
+    float lo, hi;
+    block_minmax(y, n, -INFINITY, INFINITY, S, lo, hi);
+    int want = r;                                            // rank from the top inside [lo, hi]
+    for (int iter = 0; iter < 40; ++iter) {
+        if (!(hi > lo)) return lo;                           // every remaining value is equal
+        for (int i = threadIdx.x; i < kSelBins; i += blockDim.x) S.hist[i] = 0;
+        __syncthreads();
+        const float scale = float(kSelBins) / (hi - lo);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = y[i];
+            if (v >= lo && v <= hi) atomicAdd(&S.hist[min(kSelBins - 1, int((v - lo) * scale))], 1);
+        }
+        __syncthreads();
+        // find the bin from the top: thread t owns bins [t * per, (t + 1) * per)
+        {
+            const int per = kSelBins / blockDim.x > 0 ? kSelBins / blockDim.x : 1;
+            const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nw = blockDim.x >> 5;
+            int mine = 0;
+            if (t * per < kSelBins)
+                for (int k = 0; k < per; ++k) mine += S.hist[t * per + k];
+            // suffix sum over threads (exclusive: how many values lie in bins above this thread's)
+            int inc = mine;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int o = __shfl_down_sync(0xffffffffu, inc, off);
+                if (lane + off < 32) inc += o;
+            }
+            int *wsum = reinterpret_cast<int *>(S.red);
+            if (lane == 0) wsum[warp] = inc;
+            __syncthreads();
+            int above = inc - mine;
+            for (int w = warp + 1; w < nw; ++w) above += wsum[w];
+            if (mine > 0 && above < want && want <= above + mine) {
+                int acc = above;
+                for (int k = per - 1; k >= 0; --k) {
+                    const int h = S.hist[t * per + k];
+                    if (want <= acc + h) { S.bin = t * per + k; S.want = want - acc; S.count = h; break; }
+                    acc += h;
+                }
+            }
+            __syncthreads();
+        }
+        const int bin = S.bin, cnt = S.count;
+        want = S.want;
+        if (cnt <= kSmallSel) {
+            if (threadIdx.x == 0) S.n_small = 0;
+            __syncthreads();
+            for (int i = threadIdx.x; i < n; i += blockDim.x) {
+                const float v = y[i];
+                if (v >= lo && v <= hi && min(kSelBins - 1, int((v - lo) * scale)) == bin) S.small[atomicAdd(&S.n_small, 1)] = v;
+            }
+            __syncthreads();
+            for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+                const float v = S.small[i];
+                int gt = 0, eq = 0;
+                for (int o = 0; o < cnt; ++o) { gt += S.small[o] > v; eq += S.small[o] == v; }
+                if (gt < want && want <= gt + eq) S.theta = v;     // all writers hold the same value
+            }
+            __syncthreads();
+            return S.theta;
+        }
+        // recurse into the bin: its exact value range
+        float nlo = INFINITY, nhi = -INFINITY;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = y[i];
+            if (v >= lo && v <= hi && min(kSelBins - 1, int((v - lo) * scale)) == bin) { nlo = fminf(nlo, v); nhi = fmaxf(nhi, v); }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            nlo = fminf(nlo, __shfl_xor_sync(0xffffffffu, nlo, off));
+            nhi = fmaxf(nhi, __shfl_xor_sync(0xffffffffu, nhi, off));
+        }
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) { S.red[threadIdx.x >> 5] = nlo; S.red[32 + (threadIdx.x >> 5)] = nhi; }
         __syncthreads();
         if (threadIdx.x == 0) {
-            int b = 255, w = want;
-            for (; b > 0; --b) {
-                if (hist[b] >= w) break;
-                w -= hist[b];
-            }
-            s_scratch[0] = b;
-            s_scratch[1] = w;
+            float a = INFINITY, c = -INFINITY;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { a = fminf(a, S.red[w]); c = fmaxf(c, S.red[32 + w]); }
+            S.lo = a;
+            S.hi = c;
         }
         __syncthreads();
-        prefix |= uint32_t(s_scratch[0]) << shift;
-        want = s_scratch[1];
-        mask |= 255u << shift;
+        lo = S.lo;
+        hi = S.hi;
         __syncthreads();
     }
-    take_equal = want;
-    return prefix;
+    return lo;
 }
 
 // ---- 3. thresholds from the sample scores -----------------------------------------------------------------------
 __global__ void __launch_bounds__(kSelCThreads)
 sample_tau_kernel(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg, float *__restrict__ tau)
 {
-    extern __shared__ uint32_t keys[];
-    __shared__ int hist[256];
-    __shared__ int scratch[2];
+    extern __shared__ float ys[];
+    __shared__ SelScratch S;
     const int row = blockIdx.x;
     const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
     const float *y = Ys + size_t(row) * ldy;
-    for (int i = threadIdx.x; i < sg.ns; i += blockDim.x) keys[i] = float_key(y[i]);
+    for (int i = threadIdx.x; i < sg.ns; i += blockDim.x) ys[i] = y[i];
     __syncthreads();
-    int take;
-    const uint32_t k = smem_radix_select(keys, sg.ns, min(sg.rank, sg.ns), hist, scratch, take);
-    if (threadIdx.x == 0) tau[row] = key_to_float(k);
+    const float th = smem_select_rth(ys, sg.ns, min(sg.rank, sg.ns), S);
+    if (threadIdx.x == 0) tau[row] = th;
 }
 
 // ---- 5. exact selection among the candidates ---------------------------------------------------------------------
@@ -142,7 +246,7 @@ struct SelParams {
     int n_seg;
     int n_ranges, cap;
     const uint2 *cand;
-    const int *cand_count;
+    const int *cand_count;     // [rows][n_ranges][2]
     const float *tau;
     const void *A, *K;
     int d;
@@ -151,18 +255,20 @@ struct SelParams {
     int *fail_list;            // their rows inside the group
 };
 
+constexpr int kMaxRanges = 4;
+
 template <typename T>
 __global__ void __launch_bounds__(kSelCThreads)
 candidate_select_kernel(SelParams p)
 {
     extern __shared__ __align__(16) unsigned char sel_smem[];
-    uint32_t *keys = reinterpret_cast<uint32_t *>(sel_smem);           // [cap] score keys, later the selection flags
-    int32_t *idxs = reinterpret_cast<int32_t *>(keys + p.cap);         // [cap] key index inside the segment
+    float *ys = reinterpret_cast<float *>(sel_smem);                    // [cap + 1] scores, later flags, later prefix sums
+    int32_t *idxs = reinterpret_cast<int32_t *>(ys + p.cap + 1);        // [cap] key index inside the segment
     int32_t *band = idxs + p.cap;                                       // [kMaxBand] candidate positions of the band
     float *band_y = reinterpret_cast<float *>(band + kMaxBand);        // [kMaxBand] their canonical scores
-    __shared__ int hist[256];
-    __shared__ int scratch[2];
+    __shared__ SelScratch S;
     __shared__ int s_n, s_fail, s_nin, s_nband;
+    __shared__ int s_start[2 * kMaxRanges + 1];                         // sub-list starts: (range, group) in order
     __shared__ int warp_sel[kSelCThreads / 32];
     __shared__ float s_anorm;
 
@@ -171,19 +277,21 @@ candidate_select_kernel(SelParams p)
     const int bucket = sg.cb + (row - sg.out_row0);
     const int Z = sg.zc;
     const T *a_row = reinterpret_cast<const T *>(p.A) + size_t(bucket) * p.d;
+    const int sub_cap = p.cap / p.n_ranges;
 
-    // candidate counts per range; two ranges share a buffer and must not have met in the middle
+    // sub-list sizes; the two groups of a range share a buffer and must not have met in the middle
     if (t == 0) {
-        const int nb = max(1, p.n_ranges / 2), sub_cap = p.cap / nb;
         int n = 0, fail = 0;
-        for (int b = 0; b < nb; ++b) {
-            const int c0 = p.cand_count[size_t(row) * p.n_ranges + 2 * b];
-            const int c1 = p.n_ranges > 1 ? p.cand_count[size_t(row) * p.n_ranges + 2 * b + 1] : 0;
-            if (c0 + c1 > sub_cap) fail = 1;
+        for (int r = 0; r < p.n_ranges; ++r) {
+            const int c0 = p.cand_count[(size_t(row) * p.n_ranges + r) * 2], c1 = p.cand_count[(size_t(row) * p.n_ranges + r) * 2 + 1];
+            if (c0 > sub_cap || c1 > sub_cap || c0 + c1 > sub_cap) fail = 1;
+            s_start[2 * r] = n;
+            s_start[2 * r + 1] = n + c0;
             n += c0 + c1;
         }
+        s_start[2 * p.n_ranges] = n;
         if (n < Z) fail = 1;
-        s_n = n;
+        s_n = fail ? 0 : n;
         s_fail = fail;
         s_nin = 0;
         s_nband = 0;
@@ -201,23 +309,18 @@ candidate_select_kernel(SelParams p)
     __syncthreads();
     const int n = s_n;
     if (!s_fail) {
-        // gather the lists in key order: range 0 upward, range 1 downward from the end of the shared buffer, ...
-        const int nb = max(1, p.n_ranges / 2), sub_cap = p.cap / nb;
-        int base = 0;
-        for (int r = 0; r < p.n_ranges; ++r) {
-            const int cnt = p.cand_count[size_t(row) * p.n_ranges + r];
-            const uint2 *buf = p.cand + size_t(row) * p.cap + size_t(r / 2) * sub_cap;
+        // gather the sub-lists: (range 0, group 0), (range 0, group 1), (range 1, group 0), ...  Each one is in key order.
+        for (int sl = 0; sl < 2 * p.n_ranges; ++sl) {
+            const int start = s_start[sl], cnt = s_start[sl + 1] - start;
+            const uint2 *buf = p.cand + size_t(row) * p.cap + size_t(sl >> 1) * sub_cap;
             for (int i = t; i < cnt; i += kSelCThreads) {
-                const uint2 e = (r & 1) ? buf[sub_cap - 1 - i] : buf[i];
-                keys[base + i] = float_key(__uint_as_float(e.x));
-                idxs[base + i] = int32_t(e.y);
+                const uint2 e = (sl & 1) ? buf[sub_cap - 1 - i] : buf[i];
+                ys[start + i] = __uint_as_float(e.x);
+                idxs[start + i] = int32_t(e.y);
             }
-            base += cnt;
         }
         __syncthreads();
-        int take;
-        const uint32_t theta_key = smem_radix_select(keys, n, Z, hist, scratch, take);
-        const float theta = key_to_float(theta_key);
+        const float theta = smem_select_rth(ys, n, Z, S);
         const float eps = kBandEps * s_anorm * __uint_as_float(sg.kmax_bits);
         const float lo = theta - eps, hi = theta + eps;
         // everything at or above lo has to be among the candidates, i.e. the threshold was low enough
@@ -225,15 +328,15 @@ candidate_select_kernel(SelParams p)
         // classify: flag 1 = certainly selected, 2 = band, 0 = out
         int my_in = 0;
         for (int i = t; i < n; i += kSelCThreads) {
-            const float y = key_to_float(keys[i]);
-            uint32_t flag = 0;
-            if (y > hi) { flag = 1; ++my_in; }
+            const float y = ys[i];
+            float flag = 0.f;
+            if (y > hi) { flag = 1.f; ++my_in; }
             else if (y >= lo) {
-                flag = 2;
+                flag = 2.f;
                 const int slot = atomicAdd(&s_nband, 1);
                 if (slot < kMaxBand) band[slot] = i;
             }
-            keys[i] = flag;
+            ys[i] = flag;
         }
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) my_in += __shfl_xor_sync(0xffffffffu, my_in, off);
@@ -256,15 +359,15 @@ candidate_select_kernel(SelParams p)
                     const float yo = band_y[o];
                     rank += (yo > y) || (yo == y && idxs[band[o]] < id);
                 }
-                keys[band[b]] = rank < need ? 1u : 0u;
+                ys[band[b]] = rank < need ? 1.f : 0.f;
             }
             __syncthreads();
-            // ordered compaction: the lists are in key order, so is the table row
-            int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
-            int base_out = 0;
+            // exclusive prefix sums of the selection flags, in place (ys[i] = selected before i, ys[n] = total)
+            int *pre = reinterpret_cast<int *>(ys);
+            int base_cnt = 0;
             for (int i0 = 0; i0 < n; i0 += kSelCThreads) {
                 const int i = i0 + t;
-                const bool sel = i < n && keys[i] == 1u;
+                const bool sel = i < n && ys[i] == 1.f;
                 const unsigned bal = __ballot_sync(0xffffffffu, sel);
                 if (lane == 0) warp_sel[warp] = __popc(bal);
                 __syncthreads();
@@ -274,10 +377,30 @@ candidate_select_kernel(SelParams p)
                     before += w < warp ? c : 0;
                     total += c;
                 }
-                const int pos = base_out + before + __popc(bal & ((1u << lane) - 1u));
-                if (sel && pos < Z) out[pos] = sg.kb + idxs[i];
-                base_out += total;
+                if (i < n) pre[i] = base_cnt + before + __popc(bal & ((1u << lane) - 1u));
+                base_cnt += total;
                 __syncthreads();
+            }
+            if (t == 0) pre[n] = base_cnt;
+            __syncthreads();
+            // merge the two groups of every range by key: output position = selected entries of the own sub-list
+            // before this one + selected entries of the sibling sub-list with a smaller key
+            int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
+            for (int sl = 0; sl < 2 * p.n_ranges; ++sl) {
+                const int start = s_start[sl], end = s_start[sl + 1];
+                const int sib = sl ^ 1, sstart = s_start[sib], send = s_start[sib + 1];
+                const int range_first = s_start[sl & ~1];                  // first entry of the range (its group-0 list)
+                for (int i = start + t; i < end; i += kSelCThreads) {
+                    if (pre[i + 1] == pre[i]) continue;                    // not selected
+                    const int key = idxs[i];
+                    int a = sstart, b = send;                              // first sibling entry with key > this key
+                    while (a < b) {
+                        const int mid = (a + b) >> 1;
+                        if (idxs[mid] < key) a = mid + 1; else b = mid;
+                    }
+                    const int pos = pre[range_first] + (pre[i] - pre[start]) + (pre[a] - pre[sstart]);
+                    if (pos < Z) out[pos] = sg.kb + key;
+                }
             }
         }
     }
@@ -343,7 +466,7 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
         cap = std::max(cap, (int)std::ceil(P.step * (r + 6.0 * std::sqrt(r))) + 64);
         P.ld_sample = std::max<int64_t>(P.ld_sample, n_keys[i] / P.step + 2);
     }
-    P.cap = (cap + 7) / 8 * 8;                               // divisible by the buffers per row (1, 1 or 2)
+    P.cap = (cap + 7) / 8 * 8;                               // divisible by the key ranges per bucket tile (1, 2 or 4)
     P.ld_sample = (P.ld_sample + 3) / 4 * 4;
     const size_t per_bucket = size_t(P.ld_sample) * 4 + size_t(P.cap) * 8;
     int64_t max_b = 0;
@@ -354,7 +477,7 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
     P.off_segs = off;   off += align_up(size_t(n) * sizeof(FusedSeg), 256);
     P.off_tcseg = off;  off += align_up(size_t(n) * sizeof(TcSeg) * 2, 256);
     P.off_tau = off;    off += align_up(size_t(P.group_buckets) * 4, 256);
-    P.off_count = off;  off += align_up(size_t(P.group_buckets) * 4 * 4, 256);
+    P.off_count = off;  off += align_up(size_t(P.group_buckets) * kMaxRanges * 2 * 4, 256);
     P.off_fail = off;   off += align_up(size_t(kMaxFail + 1) * 4, 256);
     P.off_ys = off;     off += align_up(size_t(P.group_buckets) * P.ld_sample * 4, 256);
     P.off_cand = off;   off += align_up(size_t(P.group_buckets) * P.cap * 8, 256);
@@ -439,7 +562,7 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         if (rc != FM_OK) return rc;
 
         SelParams sp = {dsegs, ng, tp.n_ranges, P.cap, cand, counts, tau, A, K, d, table, fail_count, fail_list};
-        const size_t sel_smem = size_t(P.cap) * 8 + size_t(kMaxBand) * 8;
+        const size_t sel_smem = size_t(P.cap) * 8 + 16 + size_t(kMaxBand) * 8;
         FM_CUDA_OK(cudaFuncSetAttribute(candidate_select_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sel_smem));
         candidate_select_kernel<T><<<(unsigned)rows, kSelCThreads, sel_smem, st>>>(sp);
         FM_LAUNCHED("candidate_select_kernel");

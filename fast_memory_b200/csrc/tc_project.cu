@@ -4,13 +4,15 @@
 // threshold and appends the survivors (score, key) to the bucket's candidate list.  A dense-store epilogue of
 // the same kernel produces the small score matrix of the key sample from which the thresholds are estimated.
 //
-// CTA = 192 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and TMEM owner,
-// warps 2-5 = epilogue (TMEM lane quarter = warp % 4).  Work unit = (segment, 128-bucket tile, key range).
-// Per 256-key tile: K tile -> shared memory (3-stage ring, 64 KB per stage at d = 128), 8 UMMAs
-// (M = 128, N = 256, K = 16) into one of two 256-column accumulators, so the MMAs of tile t + 1 overlap the
-// epilogue of tile t.  Every mbarrier wait is bounded; on a give-up the CTA records a status and unwinds.
+// CTA = 320 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and TMEM owner,
+// warps 2-5 = epilogue group 0, warps 6-9 = epilogue group 1 (TMEM lane quarter = warp % 4).
+// Work unit = (segment, 128-bucket tile, key range).  Per 256-key tile: K tile -> shared memory (ring of
+// 64 KB stages at d = 128), 8 UMMAs (M = 128, N = 256, K = 16) into accumulator t % 2 (256 TMEM columns each);
+// epilogue group t % 2 drains it while the MMAs of the next tile fill the other one.
+// Every mbarrier wait is bounded; on a give-up the CTA records a status and unwinds.
 #include "tc_project.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace fm {
@@ -19,8 +21,10 @@ namespace {
 
 constexpr int kBM = kTcBM;                  // bucket rows per tile (UMMA M)
 constexpr int kBN = kTcBN;                  // keys per tile (UMMA N)
-constexpr int kStagesTc = 3;
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;
+constexpr int kTrLd = 33;                   // row stride (floats) of the per-warp transpose buffer of the dense epilogue
+
+template <bool DENSE> struct TcCfg { static constexpr int STAGES = DENSE ? 2 : 3; };
 
 }  // namespace
 
@@ -28,11 +32,12 @@ template <int D, bool DENSE>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmK, TcParams p, uint32_t idesc)
 {
+    constexpr int STAGES = TcCfg<DENSE>::STAGES;
     constexpr int KB = D / 64;                               // 64-element (128-byte) k-blocks
     constexpr uint32_t A_BYTES = KB * kBM * 128;
     constexpr uint32_t STAGE_BYTES = KB * kBN * 128;
     extern __shared__ unsigned char smem_dyn[];
-    __shared__ __align__(8) uint64_t bars[2 * kStagesTc + 1 + 4];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1 + 4];
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
 
@@ -41,10 +46,10 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t a_smem = base, k_smem = base + A_BYTES;
     const uint32_t bar0 = tc::smem_addr(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
-    auto empty_bar = [&](int s) { return bar0 + 8u * (kStagesTc + s); };
-    const uint32_t a_bar = bar0 + 8u * (2 * kStagesTc);
-    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kStagesTc + 1 + a); };
-    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kStagesTc + 3 + a); };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    const uint32_t a_bar = bar0 + 8u * (2 * STAGES);
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 1 + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 3 + a); };
 
     // ---- which unit -----------------------------------------------------------------------------------------
     const int unit = blockIdx.x;
@@ -67,7 +72,7 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int n_tiles = t_end - t_begin;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStagesTc; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
         tc::mbar_init(a_bar, 1);
         for (int a = 0; a < 2; ++a) { tc::mbar_init(tfull_bar(a), 1); tc::mbar_init(tempty_bar(a), 4); }
         tc::mbar_fence_init();
@@ -87,8 +92,8 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tc::mbar_arrive_expect_tx(a_bar, A_BYTES);
             for (int kb = 0; kb < KB; ++kb) tc::tma_load_2d(a_smem + kb * (kBM * 128), &tmA, kb * 64, sg.a_row0 + m0, a_bar);
             for (int t = 0; t < n_tiles; ++t) {
-                const int s = t % kStagesTc;
-                if (!tc::mbar_wait(empty_bar(s), ((t / kStagesTc) & 1) ^ 1)) { atomicExch(p.status, 1); s_abort = 1; break; }
+                const int s = t % STAGES;
+                if (!tc::mbar_wait(empty_bar(s), ((t / STAGES) & 1) ^ 1)) { atomicExch(p.status, 1); s_abort = 1; break; }
                 if (*(volatile int *)&s_abort) break;
                 tc::mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
                 const int key_row = sg.k_row0 + (t_begin + t) * kBN;
@@ -101,8 +106,8 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (lane == 0 && n_tiles > 0) {
             bool ok = tc::mbar_wait(a_bar, 0);
             for (int t = 0; ok && t < n_tiles; ++t) {
-                const int s = t % kStagesTc, acc = t & 1;
-                ok = tc::mbar_wait(tempty_bar(acc), ((t >> 1) & 1) ^ 1) && tc::mbar_wait(full_bar(s), (t / kStagesTc) & 1);
+                const int s = t % STAGES, acc = t & 1;
+                ok = tc::mbar_wait(tempty_bar(acc), ((t >> 1) & 1) ^ 1) && tc::mbar_wait(full_bar(s), (t / STAGES) & 1);
                 if (!ok || *(volatile int *)&s_abort) { ok = false; break; }
                 tc::fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
@@ -121,70 +126,88 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             if (!ok) { atomicExch(p.status, 2); s_abort = 1; }
         }
     } else {
-        // ---- epilogue: one bucket row per thread --------------------------------------------------------------
+        // ---- epilogue: group g drains accumulator g (tiles t = g, g + 2, ...); one bucket row per thread -----
+        const int g = (warp - 2) >> 2;
         const int q = warp & 3;                              // TMEM lane quarter this warp may read
         const int m = q * 32 + lane;                         // row of the tile
         const bool row_ok = m0 + m < sg.n_buckets;
         const int grow = sg.out_row0 + m0 + m;               // row of this bucket in the outputs
         float tau = 0.f;
-        uint2 *list = nullptr;
-        int cursor = 0, dir = 1, sub_cap = 0;
-        if constexpr (!DENSE) {
+        uint2 *wp = nullptr, *list0 = nullptr;
+        int step = 1, sub_cap = 0, cursor = 0;
+        bool overflow = false;
+        float *tr = nullptr;
+        if constexpr (DENSE) {
+            tr = reinterpret_cast<float *>(smem_dyn + (base - tc::smem_addr(smem_dyn)) + A_BYTES + STAGES * STAGE_BYTES) +
+                 (warp - 2) * 32 * kTrLd;
+        } else {
             if (row_ok) {
+                // one buffer per key range, shared by the two groups: group 0 fills it upward, group 1 downward
                 tau = p.tau[grow];
-                const int nb = max(1, p.n_ranges / 2);       // buffers per row; two ranges share one, growing toward each other
-                sub_cap = p.cap / nb;
-                list = p.cand + size_t(grow) * p.cap + size_t(range / 2) * sub_cap;
-                if (p.n_ranges > 1 && (range & 1)) { dir = -1; list += sub_cap - 1; }
+                sub_cap = p.cap / p.n_ranges;
+                list0 = p.cand + size_t(grow) * p.cap + size_t(range) * sub_cap;
+                if (g) { step = -1; list0 += sub_cap - 1; }
+                wp = list0;
             }
         }
         bool ok = true;
-        for (int t = 0; t < n_tiles; ++t) {
-            const int acc = t & 1;
-            ok = tc::mbar_wait(tfull_bar(acc), (t >> 1) & 1) && !*(volatile int *)&s_abort;
+        for (int t = g; t < n_tiles; t += 2) {
+            ok = tc::mbar_wait(tfull_bar(g), (t >> 1) & 1) && !*(volatile int *)&s_abort;
             ok = __all_sync(0xffffffffu, ok);                // the TMEM loads below need the whole warp
             if (!ok) break;
             tc::fence_after_sync();
             const int col0 = (t_begin + t) * kBN;
+            const bool last = col0 + kBN > sg.n_keys;        // only the segment's last tile can be partial
 #pragma unroll 1
             for (int b = 0; b < kBN / 32; ++b) {
                 uint32_t v[32];
-                tc::tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * kBN + b * 32, v);
+                tc::tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + g * kBN + b * 32, v);
                 tc::tmem_ld_wait();
                 const int c0 = col0 + b * 32;
                 if constexpr (DENSE) {
-                    if (row_ok) {
-                        float *dst = p.Y + size_t(grow) * p.ldy + c0;
-                        if (c0 + 32 <= sg.n_keys && ((uintptr_t)dst & 15) == 0) {
+                    // transpose the warp's 32 x 32 block through shared memory so that every store instruction
+                    // writes one 128-byte piece of a row
 #pragma unroll
-                            for (int e = 0; e < 32; e += 4)
-                                *reinterpret_cast<uint4 *>(dst + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 32; ++e)
-                                if (c0 + e < sg.n_keys) dst[e] = __uint_as_float(v[e]);
-                        }
+                    for (int e = 0; e < 32; ++e) tr[lane * kTrLd + e] = __uint_as_float(v[e]);
+                    __syncwarp();
+                    const int rows_here = min(32, sg.n_buckets - (m0 + q * 32));
+                    if (c0 + lane < sg.n_keys) {
+                        float *dst = p.Y + size_t(sg.out_row0 + m0 + q * 32) * p.ldy + c0 + lane;
+                        for (int r = 0; r < rows_here; ++r) dst[size_t(r) * p.ldy] = tr[r * kTrLd + lane];
                     }
+                    __syncwarp();
                 } else {
-                    if (row_ok) {
+                    if (last) {
                         const int live = sg.n_keys - c0;     // columns of this batch that exist
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            if (__uint_as_float(v[e]) >= tau && e < live) {
-                                if (cursor < sub_cap) list[cursor * dir] = make_uint2(v[e], uint32_t(c0 + e));
-                                ++cursor;                    // keeps counting past the capacity: the overflow is detected later
+                        for (int e = 0; e < 32; ++e)
+                            if (e >= live) v[e] = 0xff800000u;                       // -inf never passes
+                    }
+                    if (row_ok) {
+                        if (!overflow && cursor + 32 <= sub_cap) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                if (__uint_as_float(v[e]) >= tau) {
+                                    *wp = make_uint2(v[e], uint32_t(c0 + e));
+                                    wp += step;
+                                }
                             }
+                            cursor = int((wp - list0) * step);
+                        } else {
+                            overflow = true;                 // keep counting so that the selection sees the overflow
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) cursor += __uint_as_float(v[e]) >= tau ? 1 : 0;
                         }
                     }
                 }
             }
             tc::fence_before_sync();
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(tempty_bar(acc));
+            if (lane == 0) tc::mbar_arrive(tempty_bar(g));
         }
         if (!ok && lane == 0) { atomicExch(p.status, 3); s_abort = 1; }
         if constexpr (!DENSE) {
-            if (row_ok) p.cand_count[size_t(grow) * p.n_ranges + range] = cursor;
+            if (row_ok) p.cand_count[(size_t(grow) * p.n_ranges + range) * 2 + g] = overflow ? sub_cap + 1 : cursor;
         }
     }
 
@@ -239,7 +262,8 @@ int make_tensor_map_2d(CUtensorMap *map, const void *base_ptr, int dtype, uint64
 template <int D, bool DENSE>
 static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmK, const TcParams &p, int units, bool bf16, cudaStream_t st)
 {
-    constexpr size_t smem = size_t(D / 64) * (kBM * 128 + kStagesTc * kBN * 128) + 1024;
+    constexpr size_t smem = size_t(D / 64) * (kBM * 128 + TcCfg<DENSE>::STAGES * kBN * 128) + 1024 +
+                            (DENSE ? size_t(8) * 32 * kTrLd * 4 : 0);
     FM_CUDA_OK(cudaFuncSetAttribute(tc_project_kernel<D, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     tc_project_kernel<D, DENSE><<<units, kTcThreads, smem, st>>>(tmA, tmK, p, tc::instr_desc_f16(bf16, kBM, kBN));
     FM_LAUNCHED("tc_project_kernel");

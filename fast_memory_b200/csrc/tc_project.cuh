@@ -20,15 +20,17 @@ struct TcSeg {
 struct TcParams {
     const TcSeg *segs;
     int n_seg;
-    int n_ranges;          // key ranges per bucket tile (1, or an even number: two ranges share a candidate buffer)
+    int n_ranges;          // key ranges per bucket tile
     // dense epilogue
     float *Y;              // row = global bucket, column = key of the segment
     int64_t ldy;
     // candidate epilogue
     const float *tau;      // [total buckets] threshold of every bucket
-    uint2 *cand;           // [total buckets][cap] (score bits, key index local to the segment)
+    uint2 *cand;           // [total buckets][cap] (score bits, key index local to the segment); one buffer of
+                           // cap / n_ranges slots per range, filled upward by epilogue group 0 (even tiles of the
+                           // range) and downward by group 1 (odd tiles)
     int cap;
-    int *cand_count;       // [total buckets][n_ranges]
+    int *cand_count;       // [total buckets][n_ranges][2]; cap / n_ranges + 1 marks an overflow
     int *status;           // set non-zero when a wait gave up
 };
 

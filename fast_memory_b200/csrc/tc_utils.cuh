@@ -35,19 +35,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
                  "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");     // suspend at most ~1 us per poll
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Waits for the phase with the given parity, giving up after a bounded number of polls.  Returns false on
-// give-up; the caller records the failure and unwinds (no wait in this library is unbounded).
-constexpr uint32_t kMaxPolls = 1u << 21;      // ~2 s at the 1 us suspend hint
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for the phase with the given parity, giving up after about two seconds (checked against the global
+// timer every 256 polls).  Returns false on give-up; the caller records the failure and unwinds: no wait in
+// this library is unbounded.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
-    for (uint32_t i = 0; i < kMaxPolls; ++i)
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-    return false;
+        if ((i & 255u) == 255u) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) return false;
+        }
+    }
 }
 
 // ---- TMA ------------------------------------------------------------------------------------------------
