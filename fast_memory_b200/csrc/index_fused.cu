@@ -55,15 +55,25 @@ __global__ void key_norm_max_kernel(const T *__restrict__ K, int d, FusedSeg *__
     const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int n_warps = gridDim.x * (blockDim.x >> 5);
     float best = 0.f;
-    for (int r = warp_global * rows_per_warp + rsel; r < sg.n_keys; r += n_warps * rows_per_warp) {
-        uint4 raw = *reinterpret_cast<const uint4 *>(K + size_t(sg.kb + r) * d + sub * 8);
-        float f[8];
-        widen8(raw, f, T());
-        float n2 = 0.f;
+    const int stride = n_warps * rows_per_warp;
+    // four rows per iteration: the loads are issued together, which is what keeps enough bytes in flight
+    for (int r0 = warp_global * rows_per_warp + rsel; r0 < sg.n_keys; r0 += 4 * stride) {
+        uint4 raw[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) n2 = fmaf(f[e], f[e], n2);
-        for (int off = 1; off < lanes_per_row; off <<= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, off);
-        best = fmaxf(best, n2);
+        for (int u = 0; u < 4; ++u) {
+            const int r = r0 + u * stride;
+            raw[u] = r < sg.n_keys ? *reinterpret_cast<const uint4 *>(K + size_t(sg.kb + r) * d + sub * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float f[8];
+            widen8(raw[u], f, T());
+            float n2 = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) n2 = fmaf(f[e], f[e], n2);
+            for (int off = 1; off < lanes_per_row; off <<= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, off);
+            best = fmaxf(best, n2);
+        }
     }
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, off));
@@ -233,8 +243,8 @@ sample_tau_kernel(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__r
     __shared__ SelScratch S;
     const int row = blockIdx.x;
     const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
-    const float *y = Ys + size_t(row) * ldy;
-    for (int i = threadIdx.x; i < sg.ns; i += blockDim.x) ys[i] = y[i];
+    if (row - sg.out_row0 >= sg.n_buckets) return;           // padding between segments
+    for (int i = threadIdx.x; i < sg.ns; i += blockDim.x) ys[i] = Ys[dense_offset(row, i, ldy)];
     __syncthreads();
     const float th = smem_select_rth(ys, sg.ns, min(sg.rank, sg.ns), S);
     if (threadIdx.x == 0) tau[row] = th;
@@ -266,6 +276,8 @@ candidate_select_kernel(SelParams p)
     int32_t *idxs = reinterpret_cast<int32_t *>(ys + p.cap + 1);        // [cap] key index inside the segment
     int32_t *band = idxs + p.cap;                                       // [kMaxBand] candidate positions of the band
     float *band_y = reinterpret_cast<float *>(band + kMaxBand);        // [kMaxBand] their canonical scores
+    int32_t *band_id = reinterpret_cast<int32_t *>(band_y + kMaxBand); // [kMaxBand] their key indices
+    int32_t *band_rank = band_id + kMaxBand;                            // [kMaxBand] how many band entries beat them
     __shared__ SelScratch S;
     __shared__ int s_n, s_fail, s_nin, s_nband;
     __shared__ int s_start[2 * kMaxRanges + 1];                         // sub-list starts: (range, group) in order
@@ -274,6 +286,7 @@ candidate_select_kernel(SelParams p)
 
     const int row = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const FusedSeg sg = p.segs[seg_of_out_row(p.segs, p.n_seg, row)];
+    if (row - sg.out_row0 >= sg.n_buckets) return;           // padding between segments
     const int bucket = sg.cb + (row - sg.out_row0);
     const int Z = sg.zc;
     const T *a_row = reinterpret_cast<const T *>(p.A) + size_t(bucket) * p.d;
@@ -309,7 +322,7 @@ candidate_select_kernel(SelParams p)
     __syncthreads();
     const int n = s_n;
     if (!s_fail) {
-        // gather the sub-lists: (range 0, group 0), (range 0, group 1), (range 1, group 0), ...  Each one is in key order.
+        // gather the sub-lists: (range 0, group 0), (range 0, group 1), (range 1, group 0), ...: key order overall
         for (int sl = 0; sl < 2 * p.n_ranges; ++sl) {
             const int start = s_start[sl], cnt = s_start[sl + 1] - start;
             const uint2 *buf = p.cand + size_t(row) * p.cap + size_t(sl >> 1) * sub_cap;
@@ -348,23 +361,46 @@ candidate_select_kernel(SelParams p)
         if (!s_fail) {
             // canonical scores of the band, then an exact rank: better = larger score, then lower key index
             const T *Kseg = reinterpret_cast<const T *>(p.K) + size_t(sg.kb) * p.d;
-            for (int b = t; b < n_band; b += kSelCThreads)
-                band_y[b] = canonical_dot(a_row, Kseg + size_t(idxs[band[b]]) * p.d, p.d);
+            float *a_f32 = reinterpret_cast<float *>(S.hist);                   // the histogram is no longer needed
+            for (int i = t; i < p.d; i += kSelCThreads) a_f32[i] = Elem<T>::to_f32(a_row[i]);
             __syncthreads();
             for (int b = t; b < n_band; b += kSelCThreads) {
-                const float y = band_y[b];
                 const int id = idxs[band[b]];
-                int rank = 0;
-                for (int o = 0; o < n_band; ++o) {
-                    const float yo = band_y[o];
-                    rank += (yo > y) || (yo == y && idxs[band[o]] < id);
+                const T *krow = Kseg + size_t(id) * p.d;
+                float y = 0.f;
+                for (int e = 0; e < p.d; e += 8) {
+                    float f[8];
+                    if constexpr (sizeof(T) == 2) widen8(*reinterpret_cast<const uint4 *>(krow + e), f, T());
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) y = fmaf(a_f32[e + u], f[u], y);
                 }
-                ys[band[b]] = rank < need ? 1.f : 0.f;
+                band_y[b] = y;
+                band_id[b] = id;
             }
             __syncthreads();
-            // exclusive prefix sums of the selection flags, in place (ys[i] = selected before i, ys[n] = total)
-            int *pre = reinterpret_cast<int *>(ys);
-            int base_cnt = 0;
+            // rank of every band entry, all threads: entry b is looked at by `parts` threads that split the others
+            for (int b = t; b < n_band; b += kSelCThreads) band_rank[b] = 0;
+            __syncthreads();
+            {
+                const int parts = max(1, kSelCThreads / max(n_band, 1));
+                for (int w = t; w < n_band * parts; w += kSelCThreads) {
+                    const int b = w / parts, part = w - b * parts;
+                    const float y = band_y[b];
+                    const int id = band_id[b];
+                    int rank = 0;
+                    for (int o = part; o < n_band; o += parts) {
+                        const float yo = band_y[o];
+                        rank += (yo > y) || (yo == y && band_id[o] < id);
+                    }
+                    if (rank) atomicAdd(&band_rank[b], rank);
+                }
+            }
+            __syncthreads();
+            for (int b = t; b < n_band; b += kSelCThreads) ys[band[b]] = band_rank[b] < need ? 1.f : 0.f;
+            __syncthreads();
+            // ordered compaction: the concatenated sub-lists are in key order, so is the table row
+            int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
+            int base_out = 0;
             for (int i0 = 0; i0 < n; i0 += kSelCThreads) {
                 const int i = i0 + t;
                 const bool sel = i < n && ys[i] == 1.f;
@@ -377,30 +413,10 @@ candidate_select_kernel(SelParams p)
                     before += w < warp ? c : 0;
                     total += c;
                 }
-                if (i < n) pre[i] = base_cnt + before + __popc(bal & ((1u << lane) - 1u));
-                base_cnt += total;
+                const int pos = base_out + before + __popc(bal & ((1u << lane) - 1u));
+                if (sel && pos < Z) out[pos] = sg.kb + idxs[i];
+                base_out += total;
                 __syncthreads();
-            }
-            if (t == 0) pre[n] = base_cnt;
-            __syncthreads();
-            // merge the two groups of every range by key: output position = selected entries of the own sub-list
-            // before this one + selected entries of the sibling sub-list with a smaller key
-            int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
-            for (int sl = 0; sl < 2 * p.n_ranges; ++sl) {
-                const int start = s_start[sl], end = s_start[sl + 1];
-                const int sib = sl ^ 1, sstart = s_start[sib], send = s_start[sib + 1];
-                const int range_first = s_start[sl & ~1];                  // first entry of the range (its group-0 list)
-                for (int i = start + t; i < end; i += kSelCThreads) {
-                    if (pre[i + 1] == pre[i]) continue;                    // not selected
-                    const int key = idxs[i];
-                    int a = sstart, b = send;                              // first sibling entry with key > this key
-                    while (a < b) {
-                        const int mid = (a + b) >> 1;
-                        if (idxs[mid] < key) a = mid + 1; else b = mid;
-                    }
-                    const int pos = pre[range_first] + (pre[i] - pre[start]) + (pre[a] - pre[sstart]);
-                    if (pos < Z) out[pos] = sg.kb + key;
-                }
             }
         }
     }
@@ -443,7 +459,7 @@ bool fused_eligible(int dtype, int d, int64_t n_keys, int64_t zc)
     // buckets much smaller than the segment (otherwise a threshold filters nothing), yet not so small that the
     // key sample needed to estimate the threshold outgrows shared memory
     return (dtype == FM_BF16 || dtype == FM_F16) && (d == 64 || d == 128) && n_keys >= 8192 && zc * 4 <= n_keys && zc >= 64 &&
-           n_keys <= zc * 4096 && zc <= 12288;      // and the candidate list of a bucket has to fit in shared memory
+           n_keys <= zc * 4096 && zc <= 10240;      // and the candidate list of a bucket has to fit in shared memory
 }
 
 static int sample_rank(double z) { return (int)std::ceil(z + 6.0 * std::sqrt(z) + 2.0); }
@@ -467,11 +483,12 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
         P.ld_sample = std::max<int64_t>(P.ld_sample, n_keys[i] / P.step + 2);
     }
     P.cap = (cap + 7) / 8 * 8;                               // divisible by the key ranges per bucket tile (1, 2 or 4)
-    P.ld_sample = (P.ld_sample + 3) / 4 * 4;
+    P.ld_sample = (P.ld_sample + 31) / 32 * 32;              // the dense scores are stored in 32 x 32 blocks
     const size_t per_bucket = size_t(P.ld_sample) * 4 + size_t(P.cap) * 8;
-    int64_t max_b = 0;
-    for (int i = 0; i < n; ++i) max_b = std::max(max_b, n_buckets[i]);
-    P.group_buckets = std::max<int64_t>(max_b, std::min<int64_t>(total_b, int64_t((size_t(3) << 29) / per_bucket)));
+    // rows of a group: every segment starts on a multiple of 32 rows
+    int64_t max_b = 0, total_pad = 0;
+    for (int i = 0; i < n; ++i) { max_b = std::max(max_b, ceil_div(n_buckets[i], 32) * 32); total_pad += ceil_div(n_buckets[i], 32) * 32; }
+    P.group_buckets = std::max<int64_t>(max_b, std::min<int64_t>(total_pad, int64_t((size_t(3) << 29) / per_bucket)));
     size_t off = 0;
     P.off_status = off; off += 256;
     P.off_segs = off;   off += align_up(size_t(n) * sizeof(FusedSeg), 256);
@@ -511,7 +528,7 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         // one group: consecutive segments whose buckets fit the group arrays
         int g1 = g0;
         int64_t rows = 0, mtiles = 0;
-        while (g1 < n && rows + nbk[g1] <= P.group_buckets) {
+        while (g1 < n && rows + ceil_div(nbk[g1], 32) * 32 <= P.group_buckets) {
             FusedSeg &s = hs[g1];
             s.kb = (int)kb[g1]; s.n_keys = (int)nk[g1]; s.cb = (int)cb[g1]; s.n_buckets = (int)nbk[g1]; s.zc = (int)zc[g1];
             s.rank = sample_rank(double(zc[g1]) / P.step);
@@ -520,7 +537,7 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
             s.out_row0 = (int)rows; s.kmax_bits = 0; s.table_off = table_off[g1];
             ht[g1] = TcSeg{s.cb, s.n_buckets, s.ns0, s.ns, (int)mtiles, s.out_row0};            // sample pass
             ht[n + g1] = TcSeg{s.cb, s.n_buckets, s.kb, s.n_keys, (int)mtiles, s.out_row0};      // candidate pass
-            rows += nbk[g1];
+            rows += ceil_div(nbk[g1], 32) * 32;
             mtiles += ceil_div(nbk[g1], kTcBM);
             ++g1;
         }
@@ -538,7 +555,7 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         uint2 *cand = (uint2 *)(ws + P.off_cand);
         float *Yf = (float *)(ws + P.off_yf);
 
-        key_norm_max_kernel<T><<<dim3(std::max(1, 2 * sm_count() / ng), ng), 256, 0, st>>>((const T *)K, d, dsegs);
+        key_norm_max_kernel<T><<<dim3(std::max(1, 8 * sm_count() / ng), ng), 256, 0, st>>>((const T *)K, d, dsegs);
         FM_LAUNCHED("key_norm_max_kernel");
 
         const int sms = sm_count();
@@ -562,7 +579,7 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         if (rc != FM_OK) return rc;
 
         SelParams sp = {dsegs, ng, tp.n_ranges, P.cap, cand, counts, tau, A, K, d, table, fail_count, fail_list};
-        const size_t sel_smem = size_t(P.cap) * 8 + 16 + size_t(kMaxBand) * 8;
+        const size_t sel_smem = size_t(P.cap) * 8 + 16 + size_t(kMaxBand) * 16;
         FM_CUDA_OK(cudaFuncSetAttribute(candidate_select_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sel_smem));
         candidate_select_kernel<T><<<(unsigned)rows, kSelCThreads, sel_smem, st>>>(sp);
         FM_LAUNCHED("candidate_select_kernel");

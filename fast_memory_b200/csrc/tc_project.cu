@@ -22,9 +22,8 @@ namespace {
 constexpr int kBM = kTcBM;                  // bucket rows per tile (UMMA M)
 constexpr int kBN = kTcBN;                  // keys per tile (UMMA N)
 constexpr int kTcThreads = 320;
-constexpr int kTrLd = 33;                   // row stride (floats) of the per-warp transpose buffer of the dense epilogue
 
-template <bool DENSE> struct TcCfg { static constexpr int STAGES = DENSE ? 2 : 3; };
+template <bool DENSE> struct TcCfg { static constexpr int STAGES = 3; };
 
 }  // namespace
 
@@ -70,6 +69,11 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int per_range = (n_tiles_seg + p.n_ranges - 1) / p.n_ranges;
     const int t_begin = min(range * per_range, n_tiles_seg), t_end = min(t_begin + per_range, n_tiles_seg);
     const int n_tiles = t_end - t_begin;
+    // Tiles are visited in the order 0, H, 1, H + 1, ... (H = half the range): accumulator / epilogue group 0 sees the
+    // first half of the range in ascending order and group 1 the second half, so the two candidate lists of a range
+    // simply concatenate into key order.
+    const int half = (n_tiles + 1) >> 1;
+    auto tile_of = [&](int s) { return (s & 1) ? half + (s >> 1) : (s >> 1); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
@@ -96,7 +100,7 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (!tc::mbar_wait(empty_bar(s), ((t / STAGES) & 1) ^ 1)) { atomicExch(p.status, 1); s_abort = 1; break; }
                 if (*(volatile int *)&s_abort) break;
                 tc::mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
-                const int key_row = sg.k_row0 + (t_begin + t) * kBN;
+                const int key_row = sg.k_row0 + (t_begin + tile_of(t)) * kBN;
                 for (int kb = 0; kb < KB; ++kb)
                     tc::tma_load_2d(k_smem + s * STAGE_BYTES + kb * (kBN * 128), &tmK, kb * 64, key_row, full_bar(s));
             }
@@ -135,18 +139,15 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         float tau = 0.f;
         uint2 *wp = nullptr, *list0 = nullptr;
         int step = 1, sub_cap = 0, cursor = 0;
+        long long step_bytes = 8;
         bool overflow = false;
-        float *tr = nullptr;
-        if constexpr (DENSE) {
-            tr = reinterpret_cast<float *>(smem_dyn + (base - tc::smem_addr(smem_dyn)) + A_BYTES + STAGES * STAGE_BYTES) +
-                 (warp - 2) * 32 * kTrLd;
-        } else {
+        if constexpr (!DENSE) {
             if (row_ok) {
                 // one buffer per key range, shared by the two groups: group 0 fills it upward, group 1 downward
                 tau = p.tau[grow];
                 sub_cap = p.cap / p.n_ranges;
                 list0 = p.cand + size_t(grow) * p.cap + size_t(range) * sub_cap;
-                if (g) { step = -1; list0 += sub_cap - 1; }
+                if (g) { step = -1; step_bytes = -8; list0 += sub_cap - 1; }
                 wp = list0;
             }
         }
@@ -156,7 +157,7 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             ok = __all_sync(0xffffffffu, ok);                // the TMEM loads below need the whole warp
             if (!ok) break;
             tc::fence_after_sync();
-            const int col0 = (t_begin + t) * kBN;
+            const int col0 = (t_begin + tile_of(t)) * kBN;
             const bool last = col0 + kBN > sg.n_keys;        // only the segment's last tile can be partial
 #pragma unroll 1
             for (int b = 0; b < kBN / 32; ++b) {
@@ -165,17 +166,13 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 tc::tmem_ld_wait();
                 const int c0 = col0 + b * 32;
                 if constexpr (DENSE) {
-                    // transpose the warp's 32 x 32 block through shared memory so that every store instruction
-                    // writes one 128-byte piece of a row
+                    // blocked layout (see dense_offset): the 32 lanes of a store instruction write 512 contiguous bytes
+                    if (q * 32 < sg.n_buckets - m0 && c0 < sg.n_keys) {
+                        float *blk = p.Y + dense_block_offset(sg.out_row0 + m0 + q * 32, c0, p.ldy);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) tr[lane * kTrLd + e] = __uint_as_float(v[e]);
-                    __syncwarp();
-                    const int rows_here = min(32, sg.n_buckets - (m0 + q * 32));
-                    if (c0 + lane < sg.n_keys) {
-                        float *dst = p.Y + size_t(sg.out_row0 + m0 + q * 32) * p.ldy + c0 + lane;
-                        for (int r = 0; r < rows_here; ++r) dst[size_t(r) * p.ldy] = tr[r * kTrLd + lane];
+                        for (int j = 0; j < 8; ++j)
+                            *reinterpret_cast<uint4 *>(blk + j * 128 + lane * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                     }
-                    __syncwarp();
                 } else {
                     if (last) {
                         const int live = sg.n_keys - c0;     // columns of this batch that exist
@@ -185,12 +182,16 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     }
                     if (row_ok) {
                         if (!overflow && cursor + 32 <= sub_cap) {
+                            // predicated (branch-free) append: a divergent branch per score would cost far more than
+                            // the three predicated instructions
+                            uint32_t col = uint32_t(c0);
 #pragma unroll
                             for (int e = 0; e < 32; ++e) {
-                                if (__uint_as_float(v[e]) >= tau) {
-                                    *wp = make_uint2(v[e], uint32_t(c0 + e));
-                                    wp += step;
-                                }
+                                asm volatile("{\n\t.reg .pred p;\n\t"
+                                             "setp.ge.f32 p, %1, %2;\n\t"
+                                             "@p st.global.v2.u32 [%0], {%3, %4};\n\t"
+                                             "@p add.s64 %0, %0, %5;\n\t}"
+                                             : "+l"(wp) : "f"(__uint_as_float(v[e])), "f"(tau), "r"(v[e]), "r"(col + e), "l"(step_bytes) : "memory");
                             }
                             cursor = int((wp - list0) * step);
                         } else {
@@ -262,8 +263,7 @@ int make_tensor_map_2d(CUtensorMap *map, const void *base_ptr, int dtype, uint64
 template <int D, bool DENSE>
 static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmK, const TcParams &p, int units, bool bf16, cudaStream_t st)
 {
-    constexpr size_t smem = size_t(D / 64) * (kBM * 128 + TcCfg<DENSE>::STAGES * kBN * 128) + 1024 +
-                            (DENSE ? size_t(8) * 32 * kTrLd * 4 : 0);
+    constexpr size_t smem = size_t(D / 64) * (kBM * 128 + TcCfg<DENSE>::STAGES * kBN * 128) + 1024;
     FM_CUDA_OK(cudaFuncSetAttribute(tc_project_kernel<D, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     tc_project_kernel<D, DENSE><<<units, kTcThreads, smem, st>>>(tmA, tmK, p, tc::instr_desc_f16(bf16, kBM, kBN));
     FM_LAUNCHED("tc_project_kernel");
@@ -281,16 +281,32 @@ int tc_project_launch(const CUtensorMap &tmA, const CUtensorMap &tmK, const TcPa
 
 }  // namespace fm
 
+namespace fm {
+__global__ void unblock_scores_kernel(const float *__restrict__ blocked, int64_t ld_blocked, int64_t rows, int64_t cols,
+                                      float *__restrict__ Y, int64_t ldy)
+{
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * cols) return;
+    const int64_t r = i / cols, c = i - r * cols;
+    Y[r * ldy + c] = blocked[dense_offset(r, c, ld_blocked)];
+}
+}  // namespace fm
+
+extern "C" size_t fm_project_tc_workspace_bytes(int64_t C, int64_t n_key_rows, int64_t key_step)
+{
+    const int64_t n_cols = (n_key_rows + key_step - 1) / key_step;
+    return 256 + size_t(fm::ceil_div(C, 32) * 32) * size_t(fm::ceil_div(n_cols, 32) * 32) * 4;
+}
+
 // Dense tensor-core projection of ONE segment: Y[c, j] ~= A[c] . K[j * key_step] for j < n_cols, fp32
 // accumulation in the tensor cores' own order (NOT the canonical chain: for scores that feed an index use
-// fm_project).  workspace: 256 bytes.
+// fm_project).
 extern "C" int fm_project_tc(const void *A, const void *K, int dtype, int64_t C, int64_t n_key_rows, int d, int64_t key_step,
                              float *Y, int64_t ldy, void *workspace, size_t workspace_bytes, fm_stream_t stream)
 {
     using namespace fm;
     FM_REQUIRE(A && K && Y && workspace, "fm_project_tc: null pointer");
     FM_REQUIRE(C > 0 && n_key_rows > 0 && key_step >= 1, "fm_project_tc: bad sizes");
-    FM_REQUIRE(workspace_bytes >= 256, "fm_project_tc: workspace must be at least 256 bytes");
     FM_REQUIRE(((uintptr_t)A | (uintptr_t)K) % 16 == 0, "fm_project_tc: A and K must be 16-byte aligned");
     if ((dtype != FM_BF16 && dtype != FM_F16) || (d != 64 && d != 128)) {
         set_error("fm_project_tc: needs bf16/fp16 and head dim 64 or 128");
@@ -298,6 +314,10 @@ extern "C" int fm_project_tc(const void *A, const void *K, int dtype, int64_t C,
     }
     const int64_t n_cols = (n_key_rows + key_step - 1) / key_step;
     FM_REQUIRE(ldy >= n_cols, "fm_project_tc: ldy too small");
+    if (workspace_bytes < fm_project_tc_workspace_bytes(C, n_key_rows, key_step)) {
+        set_error("fm_project_tc: workspace %zu too small", workspace_bytes);
+        return FM_ERR_WORKSPACE;
+    }
     cudaStream_t st = (cudaStream_t)stream;
     CUtensorMap tmA, tmK;
     int rc = make_tensor_map_2d(&tmA, A, dtype, (uint64_t)C, (uint64_t)d, (uint64_t)d * 2, kBM);
@@ -314,8 +334,12 @@ extern "C" int fm_project_tc(const void *A, const void *K, int dtype, int64_t C,
     const int m_tiles = (int)ceil_div(C, kBM);
     const int n_tiles = (int)ceil_div(n_cols, kBN);
     p.n_ranges = (int)std::max<int64_t>(1, std::min<int64_t>(n_tiles, ceil_div(2 * sm_count(), m_tiles)));
-    p.Y = Y;
-    p.ldy = ldy;
+    p.Y = (float *)(ws + 256);
+    p.ldy = ceil_div(n_cols, 32) * 32;
     p.status = (int *)ws;
-    return tc_project_launch(tmA, tmK, p, m_tiles * p.n_ranges, d, true, dtype == FM_BF16, st);
+    rc = tc_project_launch(tmA, tmK, p, m_tiles * p.n_ranges, d, true, dtype == FM_BF16, st);
+    if (rc != FM_OK) return rc;
+    unblock_scores_kernel<<<(unsigned)ceil_div(C * n_cols, 256), 256, 0, st>>>(p.Y, p.ldy, C, n_cols, Y, ldy);
+    FM_LAUNCHED("unblock_scores_kernel");
+    return FM_OK;
 }

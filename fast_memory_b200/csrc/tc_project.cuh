@@ -21,18 +21,31 @@ struct TcParams {
     const TcSeg *segs;
     int n_seg;
     int n_ranges;          // key ranges per bucket tile
-    // dense epilogue
-    float *Y;              // row = global bucket, column = key of the segment
-    int64_t ldy;
+    // dense epilogue: scores in the blocked layout of dense_offset()
+    float *Y;
+    int64_t ldy;           // columns per row, a multiple of 32
     // candidate epilogue
     const float *tau;      // [total buckets] threshold of every bucket
     uint2 *cand;           // [total buckets][cap] (score bits, key index local to the segment); one buffer of
-                           // cap / n_ranges slots per range, filled upward by epilogue group 0 (even tiles of the
-                           // range) and downward by group 1 (odd tiles)
+                           // cap / n_ranges slots per range, filled upward by epilogue group 0 (first half of the
+                           // range's tiles) and downward by group 1 (second half): both in ascending key order
     int cap;
     int *cand_count;       // [total buckets][n_ranges][2]; cap / n_ranges + 1 marks an overflow
     int *status;           // set non-zero when a wait gave up
 };
+
+// Dense scores are stored in blocks of 32 rows x 32 columns (4 KB); inside a block the element (r, c) sits at
+// (c / 4) * 128 + r * 4 + c % 4, so that the 32 threads of an epilogue warp (one row each) write 512 contiguous
+// bytes per instruction.  Blocks are ordered row-block major.  ldy = columns per row (multiple of 32); the
+// array must cover rows rounded up to a multiple of 32.
+__host__ __device__ inline size_t dense_block_offset(int64_t row, int64_t col, int64_t ldy)
+{
+    return (size_t(row >> 5) * size_t(ldy >> 5) + size_t(col >> 5)) * 1024;
+}
+__host__ __device__ inline size_t dense_offset(int64_t row, int64_t col, int64_t ldy)
+{
+    return dense_block_offset(row, col, ldy) + size_t((col & 31) >> 2) * 128 + size_t(row & 31) * 4 + size_t(col & 3);
+}
 
 // units = (total bucket tiles) * n_ranges CTAs
 int tc_project_launch(const CUtensorMap &tmA, const CUtensorMap &tmK, const TcParams &p, int units, int d, bool dense, bool bf16,

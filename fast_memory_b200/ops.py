@@ -137,7 +137,7 @@ def project_tc(A: torch.Tensor, K: torch.Tensor, key_step: int = 1) -> torch.Ten
     assert A.dtype == K.dtype and A.is_contiguous() and K.is_contiguous() and A.shape[1] == K.shape[1]
     n_cols = (K.shape[0] + key_step - 1) // key_step
     Y = torch.empty(A.shape[0], n_cols, dtype=torch.float32, device=dev)
-    ws = _ws.get("project_tc", 256, dev)
+    ws = _ws.get("project_tc", L.lib().fm_project_tc_workspace_bytes(A.shape[0], K.shape[0], int(key_step)), dev)
     L.check(L.lib().fm_project_tc(L.ptr(A), L.ptr(K), L.dtype_id(A.dtype), A.shape[0], K.shape[0], A.shape[1],
                                   int(key_step), L.ptr(Y), n_cols, L.ptr(ws), ws.numel(), L.stream_ptr(dev)),
             "fm_project_tc")

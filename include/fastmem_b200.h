@@ -145,8 +145,10 @@ int fm_project(const void *A, const void *K, int dtype, int64_t C, int64_t N, in
  * d = 64 or 128, optionally over every key_step-th key row: Y[c, j] ~ A[c, :] . K[j * key_step, :]
  * for j < ceil(n_key_rows / key_step).  The summation order is the hardware's, so these scores are
  * approximate (about 1e-6 relative): they drive threshold estimates, never an index decision.
- * Same reference lines as fm_project.  workspace: at least 256 bytes.
+ * Same reference lines as fm_project.  After the stream completes the first int32 of the workspace is
+ * a status word (0 = ok).
  * ------------------------------------------------------------------------------------------- */
+size_t fm_project_tc_workspace_bytes(int64_t C, int64_t n_key_rows, int64_t key_step);
 int fm_project_tc(const void *A, const void *K, int dtype, int64_t C, int64_t n_key_rows, int d, int64_t key_step,
                   float *Y, int64_t ldy, void *workspace, size_t workspace_bytes, fm_stream_t stream);
 
