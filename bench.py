@@ -279,6 +279,137 @@ def run_ours(args, rank, world):
     return res
 
 
+def run_ring(args, rank, world):
+    """cfg5: keys sharded over the sequence into 8 logical shards (fixed, so the result does not depend on the
+    GPU count), every rank indexes its own shards, all queries attend everywhere, partial (O, LSE) are merged
+    around the ring.  Strong scaling: the same job on 1, 2, 4 or 8 GPUs."""
+    import fast_memory_b200 as fm
+    from fast_memory_b200 import synth
+    from fast_memory_b200.dist import ShardedMemory
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    cfg = synth.config("cfg5")
+    if args.kv_heads:
+        cfg.kv_heads = args.kv_heads
+    H, d, S = cfg.kv_heads, cfg.d, cfg.n_queries
+    shard_len = cfg.n_keys // cfg.shards
+    if cfg.shards % world:
+        raise SystemExit(f"cfg5 has {cfg.shards} shards: the GPU count must divide it")
+    per = cfg.shards // world
+    lo, hi = rank * per * shard_len, (rank + 1) * per * shard_len
+    sm_scale = d ** -0.5
+    q = torch.empty(H, S, d, dtype=cfg.dtype, device=dev)
+    k = torch.empty(H, hi - lo, d, dtype=cfg.dtype, device=dev)
+    v = torch.empty_like(k)
+    A = torch.empty(H, cfg.n_buckets, d, dtype=cfg.dtype, device=dev)
+    for h in range(H):                       # every rank draws the whole head from the same seed and keeps its slice
+        gen = torch.Generator(device=dev).manual_seed(args.seed * 1000 + h)
+        qh, kh, vh = synth.make_head(cfg.n_keys, S, d, cfg.n_clusters, cfg.sigma, cfg.norm_sigma, cfg.dtype, gen, dev)
+        q[h], k[h], v[h] = qh, kh[lo:hi], vh[lo:hi]
+        # shared projection matrix: k-means over the head's first shard, seeded with its first C queries
+        A[h], _ = fm.kmeans_projection(kh[:shard_len].contiguous(), qh[:cfg.n_buckets].contiguous(), cfg.kmeans_iters,
+                                       [0, shard_len], [0, cfg.n_buckets])
+        del qh, kh, vh
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    build_ms = []
+    for it in range(args.build_steps + 1):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        mem = ShardedMemory.build(k, v, shard_len, A=A, bucket_size=cfg.bucket_size, group=None, check=False)
+        e1.record()
+        torch.cuda.synchronize()
+        mem.local.check_build()
+        if it > 0 or args.build_steps == 0:
+            build_ms.append(e0.elapsed_time(e1))
+
+    for _ in range(args.warmup):
+        mem.query(q, sm_scale)
+    barrier()
+    launches0 = fm.launch_count()
+    with ClockSampler(dev.index or 0) as clocks:
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            mem.query(q, sm_scale)
+        t1.record()
+        barrier()
+        step_ms = t0.elapsed_time(t1) / args.steps
+    launches = fm.launch_count() - launches0
+
+    # attention alone on the local shards (the dominant kernel)
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(2):
+        mem.query_partial(q, sm_scale)
+    torch.cuda.synchronize()
+    a0.record()
+    for _ in range(args.steps):
+        mem.query_partial(q, sm_scale)
+    a1.record()
+    torch.cuda.synchronize()
+    part_ms = a0.elapsed_time(a1) / args.steps
+    n_buckets_total = H * cfg.n_buckets
+    attn_bytes = n_buckets_total * per * min(cfg.bucket_size, shard_len) * (4 + 2 * d * 2) + H * S * (2 * d * 2 + 8)
+
+    q_host = q.cpu().pin_memory()
+    o_host = torch.empty(H, S, d, dtype=torch.float32).pin_memory()
+    l_host = torch.empty(H, S, dtype=torch.float32).pin_memory()
+    q_dev = torch.empty_like(q)
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        o, lse = mem.query(q_dev, sm_scale)
+        if rank == 0:
+            o_host.copy_(o, non_blocking=True)
+            l_host.copy_(lse, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+
+    build_med = statistics.median(build_ms)
+    if world > 1:
+        t = torch.tensor([step_ms, e2e_ms, build_med, part_ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        step_ms, e2e_ms, build_med, part_ms = t.tolist()
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    n_queries = H * S
+    achieved = attn_bytes / (part_ms * 1e-3) / 1e9
+    return {
+        "metric": METRIC, "value": n_queries / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": ("CUT-DOWN " if args.kv_heads else "") + f"cfg5: {H} heads, d={d}, N={cfg.n_keys} keys/head in {cfg.shards} shards of "
+                               f"{shard_len}, C={cfg.n_buckets}, Z={cfg.bucket_size} per shard, {S} queries/head",
+                   "parallelism": f"{per} shard(s) per GPU, ring reduce-scatter of partial (O, LSE) + all-gather",
+                   "l2": f"inputs larger than L2 ({attn_bytes / 1e9:.1f} GB gathered per GPU per step)"},
+        "clocks": clocks.summary(),
+        "e2e": {"value": n_queries / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": o_host.numel() * 4 + l_host.numel() * 4},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "hashed attention forward (hash + group + attention over the local shards)", "bound": "hbm",
+                     "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                     "peak_source": peaks["source"], "traffic": None, "algorithmic_bytes": attn_bytes, "ms_per_launch": part_ms},
+        "index_build": {"metric": "index_build_keys_per_s", "value": H * cfg.n_keys / (build_med * 1e-3), "unit": "keys/s",
+                        "ms": build_med, "tflops": 2.0 * cfg.n_buckets * cfg.n_keys * d * H / (build_med * 1e-3) / 1e12},
+    }
+
+
 # ---------------------------------------------------------------------------------------------------
 # CPU arm: the oracle port of the reference algorithm on the host cores
 # ---------------------------------------------------------------------------------------------------
@@ -377,7 +508,7 @@ def main():
     else:
         if world > 1:
             torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
-        res = run_ours(args, rank, world)
+        res = run_ring(args, rank, world) if args.workload == "cfg5" else run_ours(args, rank, world)
         if world > 1:
             torch.distributed.destroy_process_group()
     if res is not None:

@@ -1,0 +1,192 @@
+"""Sequence-sharded memories: every rank indexes its own key shards, partial (O, LSE) results are merged
+around a ring.
+
+The reference rotates the K / V shards themselves around the ring (``SendRecv`` + the loop at mem:291-338) and
+re-filters a global table at every step (mem:131-142).  Here the keys never move: each rank attends all
+queries to its local shards in ONE pass (the table of a bucket is the concatenation of the per-shard tables,
+so every bucket row is staged once), and only the partial results travel - a ring reduce-scatter of
+(O, LSE) in W - 1 steps of NCCL send/recv, each received slice folded in with the LSE-merge kernel
+(mem:54-71), then an all-gather of the finished slices.  Per step a rank sends rows / W x (d + 1) fp32
+values, which is tiny next to the attention itself.
+
+``SendRecv`` keeps the reference's interface (mem:13-50): ``send_recv`` queues a pair of P2P operations to
+the next / from the previous rank, ``commit`` posts the batch, ``wait`` blocks on it; misuse raises the same
+``RuntimeError`` messages.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+from .memory import Memory, kmeans_projection
+
+MergeFn = Callable[[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor], None]
+
+
+class SendRecv:
+    """Batched exchange with the ring neighbours (drop-in for mem:13-50)."""
+
+    def __init__(self, msg: str = "", group: Optional[dist.ProcessGroup] = None):
+        self._pending_operations: List[dist.P2POp] = []
+        self._active_requests = None
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        self.send_rank = (self.rank + 1) % self.world_size
+        self.recv_rank = (self.rank + self.world_size - 1) % self.world_size
+
+    def _global(self, group_rank: int) -> int:
+        return group_rank if self.group is None else dist.get_global_rank(self.group, group_rank)
+
+    def send_recv(self, tensor_to_send: torch.Tensor, recv_tensor: Optional[torch.Tensor] = None) -> torch.Tensor:
+        result_tensor = torch.zeros_like(tensor_to_send) if recv_tensor is None else recv_tensor
+        send_operation = dist.P2POp(dist.isend, tensor_to_send, self._global(self.send_rank), group=self.group)
+        recv_operation = dist.P2POp(dist.irecv, result_tensor, self._global(self.recv_rank), group=self.group)
+        # same ordering rule as the reference (mem:31-34): the higher neighbour is addressed first
+        if self.send_rank > self.rank:
+            self._pending_operations.extend([send_operation, recv_operation])
+        else:
+            self._pending_operations.extend([recv_operation, send_operation])
+        return result_tensor
+
+    def commit(self):
+        if self._active_requests is not None:
+            raise RuntimeError("Commit called twice")
+        self._active_requests = dist.batch_isend_irecv(self._pending_operations)
+        self._pending_operations = []
+
+    def wait(self):
+        if self._active_requests is None:
+            raise RuntimeError("Wait called before commit")
+        for request in self._active_requests:
+            request.wait()
+        self._active_requests = None
+        assert not self._pending_operations
+
+
+def _default_merge(out: torch.Tensor, lse: torch.Tensor, blk_out: torch.Tensor, blk_lse: torch.Tensor) -> None:
+    ops.lse_merge(out, lse, blk_out, blk_lse)
+
+
+def ring_reduce_scatter_partials(out: torch.Tensor, lse: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
+                                 merge_fn: MergeFn = _default_merge) -> Tuple[torch.Tensor, torch.Tensor, int]:
+    """Merge the partial results of all ranks.
+
+    ``out`` fp32 ``[rows, d]`` and ``lse`` fp32 ``[rows]`` (rows a multiple of the world size) hold this rank's
+    partial attention over ITS keys for ALL queries; they are used as scratch.  After W - 1 ring steps rank r
+    holds the complete result for the rows of chunk ``(r + 1) % W``.  Returns views ``(out_chunk, lse_chunk)`` of
+    that chunk and its index.
+    """
+    W, r = dist.get_world_size(group), dist.get_rank(group)
+    rows, d = out.shape
+    assert rows % W == 0 and lse.shape == (rows,) and out.dtype == torch.float32 and lse.dtype == torch.float32
+    n = rows // W
+    if W == 1:
+        return out, lse, 0
+    recv_o = torch.empty(n, d, dtype=torch.float32, device=out.device)
+    recv_l = torch.empty(n, dtype=torch.float32, device=out.device)
+    for s in range(W - 1):
+        send_c, recv_c = (r - s) % W, (r - s - 1) % W
+        comm = SendRecv("partials", group)
+        comm.send_recv(out[send_c * n:(send_c + 1) * n], recv_o)
+        comm.send_recv(lse[send_c * n:(send_c + 1) * n], recv_l)
+        comm.commit()
+        comm.wait()
+        merge_fn(out[recv_c * n:(recv_c + 1) * n], lse[recv_c * n:(recv_c + 1) * n], recv_o, recv_l)
+    own = (r + 1) % W
+    return out[own * n:(own + 1) * n], lse[own * n:(own + 1) * n], own
+
+
+def all_gather_chunks(chunk: torch.Tensor, own: int, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Rank r contributes the chunk it owns (index ``own = (r + 1) % W``); returns all chunks in row order."""
+    W = dist.get_world_size(group)
+    if W == 1:
+        return chunk
+    gathered = torch.empty((W * chunk.shape[0],) + tuple(chunk.shape[1:]), dtype=chunk.dtype, device=chunk.device)
+    dist.all_gather_into_tensor(gathered, chunk.contiguous(), group=group)
+    # slot r of the gather holds chunk (r + 1) % W: rotate by one slot to get row order
+    n = chunk.shape[0]
+    return torch.cat([gathered[(W - 1) * n:], gathered[:(W - 1) * n]], 0)
+
+
+class ShardedMemory:
+    """A memory whose keys are cut into contiguous shards, each with its own index (local top-Z per bucket),
+    spread over the ranks of a process group.  All shards share the projection matrix A, so a query is hashed
+    once.  ``query`` returns the attention over the union of all shards' buckets."""
+
+    def __init__(self):
+        self.local: Optional[Memory] = None
+        self.group = None
+        self.n_shards = self.n_local = 0
+
+    @classmethod
+    def build(cls, k_local: torch.Tensor, v_local: torch.Tensor, shard_len: int, *, A: torch.Tensor, bucket_size: int,
+              group: Optional[dist.ProcessGroup] = None, check: bool = True) -> "ShardedMemory":
+        """``k_local`` / ``v_local``: this rank's shards back to back, ``[H, n_local * shard_len, d]``.
+        ``A``: ``[H, C, d]`` in the key dtype, identical on every rank."""
+        H, n_total, d = k_local.shape
+        if n_total % shard_len:
+            raise ValueError("the local key count must be a multiple of shard_len")
+        n_local = n_total // shard_len
+        C = A.shape[1]
+        self = cls()
+        self.group = group
+        self.n_local = n_local
+        self.n_shards = n_local * (dist.get_world_size(group) if dist.is_initialized() else 1)
+        cu = [s * shard_len for s in range(n_local + 1)]
+        # one segment per (head, shard), all shards of a head sharing its A
+        A_rep = A[:, None].expand(H, n_local, C, d).reshape(H, n_local * C, d).contiguous()
+        per_shard = Memory.build(k_local, v_local, n_buckets=[C] * n_local, bucket_size=[bucket_size] * n_local, A=A_rep,
+                                 cu_seqlens_k=cu, check=check)
+        z = min(bucket_size, shard_len)
+        # bucket (h, c) of the local memory = the concatenation over shards of the shard buckets (h, s, c): ascending rows
+        table = per_shard.table.reshape(H, n_local, C, z).permute(0, 2, 1, 3).reshape(-1).contiguous()
+        mem = Memory()
+        mem.k, mem.v, mem.A = per_shard.k, per_shard.v, A.reshape(H * C, d).contiguous()
+        mem.n_heads, mem.n_seq, mem.d = H, 1, d
+        mem.seg_kb = [h * n_total for h in range(H + 1)]
+        mem.seg_cb = [h * C for h in range(H + 1)]
+        mem.seg_z = [n_local * z] * H
+        mem.table_off = [h * C * n_local * z for h in range(H + 1)]
+        mem.seq_buckets = [C]
+        mem.cu_seqlens_k = [0, n_total]
+        mem.table = table
+        mem.bucket_off = torch.arange(0, (H * C + 1) * n_local * z, n_local * z, dtype=torch.int64, device=k_local.device)
+        mem.max_bucket_len = n_local * z
+        mem._seg_cb_dev = torch.tensor(mem.seg_cb, dtype=torch.int32, device=k_local.device)
+        mem.build_status = per_shard.build_status
+        mem.centroids_f32 = None
+        self.local = mem
+        return self
+
+    def query_partial(self, q: torch.Tensor, sm_scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+        """This rank's partial result over its own shards: o in q's dtype, fp32 lse."""
+        return self.local.query(q, sm_scale)
+
+    def query(self, q: torch.Tensor, sm_scale: float, gather: bool = True, merge_fn: MergeFn = _default_merge
+              ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """q ``[Hq, S, d]``, the same on every rank.  Returns fp32 ``(out [Hq, S, d], lse [Hq, S])`` over all
+        shards of all ranks (``gather=False``: only the rows this rank ends up owning, plus their range)."""
+        Hq, S, d = q.shape
+        o, lse = self.local.query(q, sm_scale)
+        W = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        rows = Hq * S
+        if W == 1:
+            return o.float(), lse
+        pad = (-rows) % W
+        out = torch.empty(rows + pad, d, dtype=torch.float32, device=q.device)
+        out[:rows].copy_(o.reshape(rows, d))
+        l = torch.full((rows + pad,), float("-inf"), dtype=torch.float32, device=q.device)
+        l[:rows].copy_(lse.reshape(rows))
+        if pad:
+            out[rows:].zero_()
+        oc, lc, own = ring_reduce_scatter_partials(out, l, self.group, merge_fn)
+        if not gather:
+            n = (rows + pad) // W
+            return oc, lc, (own * n, min((own + 1) * n, rows))
+        full_o = all_gather_chunks(oc, own, self.group)[:rows].reshape(Hq, S, d)
+        full_l = all_gather_chunks(lc, own, self.group)[:rows].reshape(Hq, S)
+        return full_o, full_l
