@@ -81,10 +81,16 @@ hash_rows_kernel(const T *__restrict__ x, const T *__restrict__ A, int d, int n_
 constexpr float kHashEps = 1.0f / 4096.0f;
 constexpr int kHashThreads = 128;
 
-__device__ __forceinline__ void top2_push(float v, int c, float &best, int &arg, float &second)
+// running top three scores of a row (indices kept for the best two)
+struct Top3 {
+    float best, second, third;
+    int arg, arg2;
+};
+__device__ __forceinline__ void top3_push(Top3 &t, float v, int c)
 {
-    if (v > best) { second = best; best = v; arg = c; }
-    else if (v > second) second = v;
+    if (v > t.best) { t.third = t.second; t.second = t.best; t.arg2 = t.arg; t.best = v; t.arg = c; }
+    else if (v > t.second) { t.third = t.second; t.second = v; t.arg2 = c; }
+    else if (v > t.third) t.third = v;
 }
 
 // amax[s] = max row norm of the A rows of segment s (as the bits of a non-negative float, via atomicMax)
@@ -171,8 +177,9 @@ hash_rows_mma_kernel(const T *__restrict__ x, const T *__restrict__ A, int n_row
         }
     }
 
-    float best[2] = {-INFINITY, -INFINITY}, second[2] = {-INFINITY, -INFINITY};
-    int arg[2] = {0, 0};
+    Top3 top[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) top[r] = Top3{-INFINITY, -INFINITY, -INFINITY, 0, 0};
     const int n_at = (C + kTile - 1) / kTile;
     for (int ta = 0; ta < n_at; ++ta) {
         issue(ta + 1);
@@ -193,10 +200,10 @@ hash_rows_mma_kernel(const T *__restrict__ x, const T *__restrict__ A, int n_row
                 mma16816<T>(s1, qf[ks], b[2], b[3]);
             }
             const int ca = c0 + nt2 * 16 + tq * 2;             // bucket of s0[0] / s0[2]; s1 is 8 further
-            if (ca < C) { top2_push(s0[0], ca, best[0], arg[0], second[0]); top2_push(s0[2], ca, best[1], arg[1], second[1]); }
-            if (ca + 1 < C) { top2_push(s0[1], ca + 1, best[0], arg[0], second[0]); top2_push(s0[3], ca + 1, best[1], arg[1], second[1]); }
-            if (ca + 8 < C) { top2_push(s1[0], ca + 8, best[0], arg[0], second[0]); top2_push(s1[2], ca + 8, best[1], arg[1], second[1]); }
-            if (ca + 9 < C) { top2_push(s1[1], ca + 9, best[0], arg[0], second[0]); top2_push(s1[3], ca + 9, best[1], arg[1], second[1]); }
+            if (ca < C) { top3_push(top[0], s0[0], ca); top3_push(top[1], s0[2], ca); }
+            if (ca + 1 < C) { top3_push(top[0], s0[1], ca + 1); top3_push(top[1], s0[3], ca + 1); }
+            if (ca + 8 < C) { top3_push(top[0], s1[0], ca + 8); top3_push(top[1], s1[2], ca + 8); }
+            if (ca + 9 < C) { top3_push(top[0], s1[1], ca + 9); top3_push(top[1], s1[3], ca + 9); }
         }
         __syncthreads();                                         // tile consumed before its buffer is refilled
     }
@@ -207,17 +214,30 @@ hash_rows_mma_kernel(const T *__restrict__ x, const T *__restrict__ A, int n_row
     for (int r = 0; r < 2; ++r) {
 #pragma unroll
         for (int off = 1; off <= 2; off <<= 1) {                 // fold the 4 lanes of the quad that share a row
-            const float ob = __shfl_xor_sync(0xffffffffu, best[r], off);
-            const float os = __shfl_xor_sync(0xffffffffu, second[r], off);
-            const int oa = __shfl_xor_sync(0xffffffffu, arg[r], off);
-            if (ob > best[r]) { second[r] = fmaxf(best[r], os); best[r] = ob; arg[r] = oa; }
-            else second[r] = fmaxf(second[r], ob);               // includes ob == best: a tie is always re-checked
+            const float ob = __shfl_xor_sync(0xffffffffu, top[r].best, off), os = __shfl_xor_sync(0xffffffffu, top[r].second, off);
+            const float ot = __shfl_xor_sync(0xffffffffu, top[r].third, off);
+            const int oa = __shfl_xor_sync(0xffffffffu, top[r].arg, off), oa2 = __shfl_xor_sync(0xffffffffu, top[r].arg2, off);
+            top3_push(top[r], ob, oa);
+            top3_push(top[r], os, oa2);
+            top3_push(top[r], ot, 0);                           // can only land in `third`, whose index is not kept
         }
         const int row = r0 + warp * 16 + g + 8 * r;
         if (tq == 0 && row < row1) {
-            hash_out[row] = arg[r];
+            // Scores closer than eps to the best may beat it under the canonical order.  None: done.  Exactly one
+            // (the usual near-tie): the two are compared with the fp32 chain right here.  More: full re-check.
             const float eps = kHashEps * sqrtf(xn2[r]) * a_max;
-            if (!(best[r] - second[r] > eps)) recheck[atomicAdd(n_recheck, 1)] = row;
+            int choice = top[r].arg;
+            if (!(top[r].best - top[r].second > eps)) {
+                if (top[r].best - top[r].third > eps) {
+                    const T *xr = x + size_t(row) * D;
+                    const float y1 = canonical_dot(A + size_t(cb0 + top[r].arg) * D, xr, D);
+                    const float y2 = canonical_dot(A + size_t(cb0 + top[r].arg2) * D, xr, D);
+                    if (y2 > y1 || (y2 == y1 && top[r].arg2 < top[r].arg)) choice = top[r].arg2;
+                } else {
+                    recheck[atomicAdd(n_recheck, 1)] = row;
+                }
+            }
+            hash_out[row] = choice;
         }
     }
 }
