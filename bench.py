@@ -35,6 +35,10 @@ import torch
 METRIC = "hashed_attn_queries_per_s"
 UNIT = "queries/s"
 
+# DRAM bytes (read + write) of one attention launch per KV head of cfg2, from the ncu capture summarised in
+# profiles/attn_mma_kernel_cfg2_8heads.md (1.352 GB for 8 heads); traffic grows in proportion to the heads.
+NCU_ATTN_DRAM_BYTES_PER_HEAD = {"cfg2": 1.352e9 / 8}
+
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -269,7 +273,8 @@ def run_ours(args, rank, world):
         "gpu_launches": int(launches),
         "roofline": {"kernel": "hashed attention forward", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                     "traffic": None, "algorithmic_bytes": attn_bytes, "ms_per_launch": attn_ms},
+                     "traffic": (NCU_ATTN_DRAM_BYTES_PER_HEAD[cfg.name] * H if cfg.name in NCU_ATTN_DRAM_BYTES_PER_HEAD else None),
+                     "algorithmic_bytes": attn_bytes, "ms_per_launch": attn_ms},
         "index_build": {"metric": "index_build_keys_per_s", "value": world * H * N / (build_med * 1e-3), "unit": "keys/s",
                         "ms": build_med, "tflops": build_flops / (build_med * 1e-3) / 1e12,
                         "frac_of_tensor_peak": build_flops / (build_med * 1e-3) / 1e12 / peaks["bf16_tflops"]},
