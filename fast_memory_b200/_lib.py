@@ -47,6 +47,9 @@ _SIGNATURES = {
     "fm_hashed_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p,
                                    c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p,
                                    c_void_p, c_int64, c_void_p, c_size_t, c_void_p]),
+    "fm_shard_filter_workspace_bytes": (c_size_t, [c_int64, c_int64]),
+    "fm_shard_filter": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                c_size_t, c_void_p]),
     "fm_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_void_p]),
     "fm_project": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),
     "fm_project_tc_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),

@@ -28,9 +28,9 @@ namespace fm {
 // canonical chain within 2^-17 M (M = ||a|| ||k|| >= sum |a_i k_i|, d <= 128), so two keys can compare
 // differently under the two orders only if their tensor-core scores differ by less than 3 * 2^-16 M.
 constexpr float kBandEps = 1.0f / 4096.0f;
-constexpr int kMaxBand = 2048;              // largest band re-scored exactly; beyond it the bucket goes to the fallback
+constexpr int kMaxBand = 512;               // largest band re-scored exactly; beyond it the bucket goes to the fallback
 constexpr int kMaxFail = 64;                // buckets the fallback can take per group of segments
-constexpr int kSelCThreads = 512;
+constexpr int kSelCThreads = 512;           // upper bound of the CTA size of the selection kernels
 constexpr int kMaxSample = 49152;           // sample scores of one bucket held in shared memory (192 KB)
 
 struct FusedSeg {
@@ -100,7 +100,7 @@ __device__ __forceinline__ float key_to_float(uint32_t key)
 // threshold are spread over a narrow interval, where radix digits of the float would all collide), the bin that
 // holds the r-th largest is found from the top, and the search recurses into that bin until it holds at most
 // kSmallSel values, which are ranked directly.  Returns theta = the r-th largest value; every thread gets it.
-constexpr int kSelBins = 2048;
+constexpr int kSelBins = 1024;
 constexpr int kSmallSel = 256;
 
 struct SelScratch {
@@ -281,10 +281,11 @@ candidate_select_kernel(SelParams p)
     __shared__ SelScratch S;
     __shared__ int s_n, s_fail, s_nin, s_nband;
     __shared__ int s_start[2 * kMaxRanges + 1];                         // sub-list starts: (range, group) in order
-    __shared__ int warp_sel[kSelCThreads / 32];
+    __shared__ int warp_sel[32];
     __shared__ float s_anorm;
 
     const int row = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int nthreads = blockDim.x, nwarps = blockDim.x >> 5;
     const FusedSeg sg = p.segs[seg_of_out_row(p.segs, p.n_seg, row)];
     if (row - sg.out_row0 >= sg.n_buckets) return;           // padding between segments
     const int bucket = sg.cb + (row - sg.out_row0);
@@ -326,7 +327,7 @@ candidate_select_kernel(SelParams p)
         for (int sl = 0; sl < 2 * p.n_ranges; ++sl) {
             const int start = s_start[sl], cnt = s_start[sl + 1] - start;
             const uint2 *buf = p.cand + size_t(row) * p.cap + size_t(sl >> 1) * sub_cap;
-            for (int i = t; i < cnt; i += kSelCThreads) {
+            for (int i = t; i < cnt; i += nthreads) {
                 const uint2 e = (sl & 1) ? buf[sub_cap - 1 - i] : buf[i];
                 ys[start + i] = __uint_as_float(e.x);
                 idxs[start + i] = int32_t(e.y);
@@ -340,7 +341,7 @@ candidate_select_kernel(SelParams p)
         if (t == 0 && !(p.tau[row] <= lo) && n < sg.n_keys) s_fail = 1;
         // classify: flag 1 = certainly selected, 2 = band, 0 = out
         int my_in = 0;
-        for (int i = t; i < n; i += kSelCThreads) {
+        for (int i = t; i < n; i += nthreads) {
             const float y = ys[i];
             float flag = 0.f;
             if (y > hi) { flag = 1.f; ++my_in; }
@@ -362,9 +363,9 @@ candidate_select_kernel(SelParams p)
             // canonical scores of the band, then an exact rank: better = larger score, then lower key index
             const T *Kseg = reinterpret_cast<const T *>(p.K) + size_t(sg.kb) * p.d;
             float *a_f32 = reinterpret_cast<float *>(S.hist);                   // the histogram is no longer needed
-            for (int i = t; i < p.d; i += kSelCThreads) a_f32[i] = Elem<T>::to_f32(a_row[i]);
+            for (int i = t; i < p.d; i += nthreads) a_f32[i] = Elem<T>::to_f32(a_row[i]);
             __syncthreads();
-            for (int b = t; b < n_band; b += kSelCThreads) {
+            for (int b = t; b < n_band; b += nthreads) {
                 const int id = idxs[band[b]];
                 const T *krow = Kseg + size_t(id) * p.d;
                 float y = 0.f;
@@ -379,11 +380,11 @@ candidate_select_kernel(SelParams p)
             }
             __syncthreads();
             // rank of every band entry, all threads: entry b is looked at by `parts` threads that split the others
-            for (int b = t; b < n_band; b += kSelCThreads) band_rank[b] = 0;
+            for (int b = t; b < n_band; b += nthreads) band_rank[b] = 0;
             __syncthreads();
             {
-                const int parts = max(1, kSelCThreads / max(n_band, 1));
-                for (int w = t; w < n_band * parts; w += kSelCThreads) {
+                const int parts = max(1, nthreads / max(n_band, 1));
+                for (int w = t; w < n_band * parts; w += nthreads) {
                     const int b = w / parts, part = w - b * parts;
                     const float y = band_y[b];
                     const int id = band_id[b];
@@ -396,19 +397,19 @@ candidate_select_kernel(SelParams p)
                 }
             }
             __syncthreads();
-            for (int b = t; b < n_band; b += kSelCThreads) ys[band[b]] = band_rank[b] < need ? 1.f : 0.f;
+            for (int b = t; b < n_band; b += nthreads) ys[band[b]] = band_rank[b] < need ? 1.f : 0.f;
             __syncthreads();
             // ordered compaction: the concatenated sub-lists are in key order, so is the table row
             int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
             int base_out = 0;
-            for (int i0 = 0; i0 < n; i0 += kSelCThreads) {
+            for (int i0 = 0; i0 < n; i0 += nthreads) {
                 const int i = i0 + t;
                 const bool sel = i < n && ys[i] == 1.f;
                 const unsigned bal = __ballot_sync(0xffffffffu, sel);
                 if (lane == 0) warp_sel[warp] = __popc(bal);
                 __syncthreads();
                 int before = 0, total = 0;
-                for (int w = 0; w < kSelCThreads / 32; ++w) {
+                for (int w = 0; w < nwarps; ++w) {
                     const int c = warp_sel[w];
                     before += w < warp ? c : 0;
                     total += c;

@@ -158,6 +158,23 @@ def topz_select(Y: torch.Tensor, Z: int, index_base: int = 0) -> torch.Tensor:
     return out
 
 
+def shard_filter(k_hashes: torch.Tensor, lo: int, hi: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``k_hashes`` ``[C, H, Z]`` int64 global key indices -> (flat int64 indices of the entries in ``[lo, hi)``
+    rebased by ``lo`` and packed (head, bucket, slot); counts ``[H, C]`` int64).  The flat tensor keeps its full
+    ``C*H*Z`` capacity (only the first ``counts.sum()`` entries are meaningful), which avoids reading the total
+    back from the device."""
+    dev = L.require_cuda(k_hashes)
+    assert k_hashes.dim() == 3 and k_hashes.dtype == torch.int64
+    k_hashes = k_hashes.contiguous()
+    C, H, Z = k_hashes.shape
+    flat = torch.empty(C * H * Z, dtype=torch.int64, device=dev)
+    counts = torch.empty(H, C, dtype=torch.int64, device=dev)
+    ws = _ws.get("shard_filter", L.lib().fm_shard_filter_workspace_bytes(C, H), dev)
+    L.check(L.lib().fm_shard_filter(L.ptr(k_hashes), C, H, Z, int(lo), int(hi), L.ptr(flat), L.ptr(counts), L.ptr(ws),
+                                    ws.numel(), L.stream_ptr(dev)), "fm_shard_filter")
+    return flat, counts
+
+
 def unit_rows(X: torch.Tensor) -> torch.Tensor:
     dev = L.require_cuda(X)
     X2 = X.reshape(-1, X.shape[-1]).contiguous()
@@ -301,12 +318,9 @@ def ring_attention_masked_forward(k_hashes, q_hashes, q, k, v, sm_scale, rank):
     assert q_hashes.shape[0] == k_heads
     assert q_hashes.shape[1] == n_heads // k_heads
     assert q_hashes.shape[2] == seq_len
-    k_hashes = k_hashes.permute(1, 0, 2)
     q_hashes = q_hashes.reshape(k_heads, -1)
-    mask = torch.logical_and(rank * context_len <= k_hashes, k_hashes < (rank + 1) * context_len)
-    counts = mask.to(torch.long).sum(-1)
     assert k_hashes.numel() > 0, k_hashes.shape
-    flat = k_hashes[mask] - rank * context_len
+    flat, counts = shard_filter(k_hashes, rank * context_len, (rank + 1) * context_len)
     out, lse = attention_hash_varlen(q.reshape(k_heads, -1, d_head), k.reshape(k_heads, -1, d_head),
                                      v.reshape(k_heads, -1, d_head), flat, counts, q_hashes, sm_scale)
     return out.reshape(batch_size, n_heads, seq_len, d_head), lse.reshape(batch_size, n_heads, seq_len)

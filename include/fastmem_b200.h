@@ -124,6 +124,16 @@ int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, int dtype, i
                        int64_t key_chunk, void *workspace, size_t workspace_bytes, fm_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Shard filter of a globally indexed table: for every (head, bucket) row of k_hashes [C, H, Z] (int64
+ * GLOBAL key indices) keep the entries in [lo, hi), rebased to the shard (index - lo), slot order kept,
+ * packed (head, bucket, slot) into flat_out (room for C*H*Z entries); counts_out [H, C] int64.
+ * Replaces: the mask / sum / boolean compaction / rebase of ring_attention_masked_forward, mem:128-142.
+ * ------------------------------------------------------------------------------------------- */
+size_t fm_shard_filter_workspace_bytes(int64_t C, int64_t H);
+int fm_shard_filter(const int64_t *k_hashes, int64_t C, int64_t H, int64_t Z, int64_t lo, int64_t hi,
+                    int64_t *flat_out, int64_t *counts_out, void *workspace, size_t workspace_bytes, fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * LSE merge, in place on fp32 accumulators:
  *   lse <- log(e^lse + e^blk_lse);  out <- out - sigmoid(blk_lse - lse) (out - blk_out)
  * Replaces: update_out_and_lse, mem:54-71 (the branch with existing accumulators, mem:67-69).

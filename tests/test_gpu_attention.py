@@ -120,6 +120,20 @@ def test_ring_attention_masked_forward_matches_reference_dense(golden_dir):
     assert (lse.cpu() - torch.from_numpy(z["lse_merged"])).abs().max() <= 1e-3
 
 
+def test_shard_filter_matches_reference_statement():
+    """mem:128-142: range mask, per-row counts, compaction in slot order, rebase."""
+    g = torch.Generator().manual_seed(12)
+    C, H, Z, ctx, W = 37, 3, 70, 500, 4
+    k_hashes = torch.topk(torch.rand(C, H, W * ctx, generator=g), dim=-1, k=Z)[1]
+    for rank in (0, 2, 3):
+        flat, counts = fm.shard_filter(k_hashes.to(DEV), rank * ctx, (rank + 1) * ctx)
+        ref_flat, ref_counts = O.shard_filter(k_hashes, rank, ctx)
+        assert torch.equal(counts.cpu(), ref_counts)
+        assert torch.equal(flat.cpu()[:ref_flat.numel()], ref_flat)
+    flat, counts = fm.shard_filter(k_hashes.to(DEV), 10 ** 9, 10 ** 9 + 5)      # nothing in range
+    assert int(counts.sum()) == 0
+
+
 def test_merge_matches_reference(golden_dir):
     z = np.load(os.path.join(golden_dir, "merge_chain.npz"))
     out, lse = None, None
