@@ -30,7 +30,6 @@ namespace fm {
 constexpr float kBandEps = 1.0f / 4096.0f;
 constexpr int kMaxBand = 512;               // largest band re-scored exactly; beyond it the bucket goes to the fallback
 constexpr int kMaxFail = 64;                // buckets the fallback can take per group of segments
-constexpr int kSelCThreads = 512;           // upper bound of the CTA size of the selection kernels
 constexpr int kMaxSample = 49152;           // sample scores of one bucket held in shared memory (192 KB)
 
 struct FusedSeg {
@@ -95,93 +94,86 @@ __device__ __forceinline__ float key_to_float(uint32_t key)
     return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
 }
 
-// ---- selection of the r-th largest of n floats in shared memory --------------------------------------------------
-// All threads of the CTA call.  The values are binned LINEARLY between their minimum and maximum (scores near a
-// threshold are spread over a narrow interval, where radix digits of the float would all collide), the bin that
-// holds the r-th largest is found from the top, and the search recurses into that bin until it holds at most
-// kSmallSel values, which are ranked directly.  Returns theta = the r-th largest value; every thread gets it.
-constexpr int kSelBins = 1024;
+// ---- selection of the r-th largest of n floats ----------------------------------------------------------------------
+// All threads of the CTA call; `load(i)` returns value i (from global memory / L2: the lists are re-read in a few
+// passes instead of being held in shared memory, which keeps a CTA's footprint at a few KB and many CTAs per SM
+// in flight).  The values are binned LINEARLY between their minimum and maximum (scores near a threshold are
+// spread over a narrow interval, where the radix digits of the floats would all collide), the bin holding the
+// r-th largest is found from the top, and the search recurses into that bin until it holds at most kSmallSel
+// values, which are ranked directly.  Returns theta = the r-th largest value (the same in every thread).
+constexpr int kSelBins = 512;
+constexpr int kHistCopies = 8;              // lanes spread their increments over 8 copies of the histogram: scores pile up
+                                            // in a few bins and same-address shared-memory atomics serialise
 constexpr int kSmallSel = 256;
 
 struct SelScratch {
-    int hist[kSelBins];
+    int hist[kHistCopies * kSelBins];
     float small[kSmallSel];
     float red[64];
     int bin, want, count, n_small;
     float lo, hi, theta;
 };
 
-__device__ __forceinline__ void block_minmax(const float *__restrict__ y, int n, float lo, float hi, SelScratch &S,
-                                             float &out_lo, float &out_hi)
+// A value source exposes  template <class F> void for_each(F f)  which calls f(ordinal, score) for the values this
+// thread owns, issuing several loads before the first is used (the lists live in L2 / HBM).
+template <class Source>
+__device__ __forceinline__ float select_rth(const Source &src, int n, int r, SelScratch &S)
 {
-    // min / max of the values inside [lo, hi]
-    float mn = INFINITY, mx = -INFINITY;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = y[i];
-        if (v >= lo && v <= hi) { mn = fminf(mn, v); mx = fmaxf(mx, v); }
-    }
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    __syncthreads();
-    if (lane == 0) { S.red[warp] = mn; S.red[32 + warp] = mx; }
-    __syncthreads();
-    if (warp == 0) {
-        mn = lane < nw ? S.red[lane] : INFINITY;
-        mx = lane < nw ? S.red[32 + lane] : -INFINITY;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nthreads = blockDim.x, nw = nthreads >> 5;
+    float lo = -INFINITY, hi = INFINITY;
+    int want = r;                                            // rank from the top inside [lo, hi]
+    for (int iter = 0; iter < 40; ++iter) {
+        // exact value range of what is left
+        float mn = INFINITY, mx = -INFINITY;
+        src.for_each([&](int, float v) {
+            if (v >= lo && v <= hi) { mn = fminf(mn, v); mx = fmaxf(mx, v); }
+        });
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) {
             mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
         }
-        if (lane == 0) { S.lo = mn; S.hi = mx; }
-    }
-    __syncthreads();
-    out_lo = S.lo;
-    out_hi = S.hi;
-}
-
-__device__ __forceinline__ float smem_select_rth(const float *__restrict__ y, int n, int r, SelScratch &S)
-{
-    float lo, hi;
-    block_minmax(y, n, -INFINITY, INFINITY, S, lo, hi);
-    int want = r;                                            // rank from the top inside [lo, hi]
-    for (int iter = 0; iter < 40; ++iter) {
-        if (!(hi > lo)) return lo;                           // every remaining value is equal
-        for (int i = threadIdx.x; i < kSelBins; i += blockDim.x) S.hist[i] = 0;
         __syncthreads();
+        if (lane == 0) { S.red[warp] = mn; S.red[32 + warp] = mx; }
+        for (int i = t; i < kHistCopies * kSelBins; i += nthreads) S.hist[i] = 0;
+        __syncthreads();
+        mn = INFINITY; mx = -INFINITY;
+        for (int w = 0; w < nw; ++w) { mn = fminf(mn, S.red[w]); mx = fmaxf(mx, S.red[32 + w]); }
+        lo = mn; hi = mx;
+        if (!(hi > lo)) return lo;                           // every remaining value is equal (uniform across the CTA)
         const float scale = float(kSelBins) / (hi - lo);
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const float v = y[i];
-            if (v >= lo && v <= hi) atomicAdd(&S.hist[min(kSelBins - 1, int((v - lo) * scale))], 1);
+        src.for_each([&](int, float v) {
+            if (v >= lo && v <= hi) atomicAdd(&S.hist[(lane & (kHistCopies - 1)) * kSelBins + min(kSelBins - 1, int((v - lo) * scale))], 1);
+        });
+        __syncthreads();
+        for (int i = t; i < kSelBins; i += nthreads) {       // fold the copies into copy 0
+            int sum = 0;
+#pragma unroll
+            for (int c = 0; c < kHistCopies; ++c) sum += S.hist[c * kSelBins + i];
+            S.hist[i] = sum;
         }
         __syncthreads();
         // find the bin from the top: thread t owns bins [t * per, (t + 1) * per)
         {
-            const int per = kSelBins / blockDim.x > 0 ? kSelBins / blockDim.x : 1;
-            const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nw = blockDim.x >> 5;
+            const int per = (kSelBins + nthreads - 1) / nthreads;
             int mine = 0;
-            if (t * per < kSelBins)
-                for (int k = 0; k < per; ++k) mine += S.hist[t * per + k];
-            // suffix sum over threads (exclusive: how many values lie in bins above this thread's)
-            int inc = mine;
+            for (int k = 0; k < per; ++k) mine += t * per + k < kSelBins ? S.hist[t * per + k] : 0;
+            int inc = mine;                                  // suffix sum inside the warp
 #pragma unroll
             for (int off = 1; off < 32; off <<= 1) {
                 const int o = __shfl_down_sync(0xffffffffu, inc, off);
                 if (lane + off < 32) inc += o;
             }
             int *wsum = reinterpret_cast<int *>(S.red);
+            __syncthreads();
             if (lane == 0) wsum[warp] = inc;
             __syncthreads();
-            int above = inc - mine;
+            int above = inc - mine;                          // values in bins above this thread's
             for (int w = warp + 1; w < nw; ++w) above += wsum[w];
             if (mine > 0 && above < want && want <= above + mine) {
                 int acc = above;
                 for (int k = per - 1; k >= 0; --k) {
-                    const int h = S.hist[t * per + k];
+                    const int h = t * per + k < kSelBins ? S.hist[t * per + k] : 0;
                     if (want <= acc + h) { S.bin = t * per + k; S.want = want - acc; S.count = h; break; }
                     acc += h;
                 }
@@ -191,14 +183,13 @@ __device__ __forceinline__ float smem_select_rth(const float *__restrict__ y, in
         const int bin = S.bin, cnt = S.count;
         want = S.want;
         if (cnt <= kSmallSel) {
-            if (threadIdx.x == 0) S.n_small = 0;
+            if (t == 0) S.n_small = 0;
             __syncthreads();
-            for (int i = threadIdx.x; i < n; i += blockDim.x) {
-                const float v = y[i];
+            src.for_each([&](int, float v) {
                 if (v >= lo && v <= hi && min(kSelBins - 1, int((v - lo) * scale)) == bin) S.small[atomicAdd(&S.n_small, 1)] = v;
-            }
+            });
             __syncthreads();
-            for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+            for (int i = t; i < cnt; i += nthreads) {
                 const float v = S.small[i];
                 int gt = 0, eq = 0;
                 for (int o = 0; o < cnt; ++o) { gt += S.small[o] > v; eq += S.small[o] == v; }
@@ -207,46 +198,69 @@ __device__ __forceinline__ float smem_select_rth(const float *__restrict__ y, in
             __syncthreads();
             return S.theta;
         }
-        // recurse into the bin: its exact value range
-        float nlo = INFINITY, nhi = -INFINITY;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const float v = y[i];
-            if (v >= lo && v <= hi && min(kSelBins - 1, int((v - lo) * scale)) == bin) { nlo = fminf(nlo, v); nhi = fmaxf(nhi, v); }
-        }
+        // recurse into the bin: narrow [lo, hi] to the bin's value interval (the next round finds its exact range)
+        {
+            float nlo = INFINITY, nhi = -INFINITY;
+            src.for_each([&](int, float v) {
+                if (v >= lo && v <= hi && min(kSelBins - 1, int((v - lo) * scale)) == bin) { nlo = fminf(nlo, v); nhi = fmaxf(nhi, v); }
+            });
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) {
-            nlo = fminf(nlo, __shfl_xor_sync(0xffffffffu, nlo, off));
-            nhi = fmaxf(nhi, __shfl_xor_sync(0xffffffffu, nhi, off));
+            for (int off = 16; off >= 1; off >>= 1) {
+                nlo = fminf(nlo, __shfl_xor_sync(0xffffffffu, nlo, off));
+                nhi = fmaxf(nhi, __shfl_xor_sync(0xffffffffu, nhi, off));
+            }
+            __syncthreads();
+            if (lane == 0) { S.red[warp] = nlo; S.red[32 + warp] = nhi; }
+            __syncthreads();
+            nlo = INFINITY; nhi = -INFINITY;
+            for (int w = 0; w < nw; ++w) { nlo = fminf(nlo, S.red[w]); nhi = fmaxf(nhi, S.red[32 + w]); }
+            lo = nlo; hi = nhi;
+            __syncthreads();
         }
-        __syncthreads();
-        if ((threadIdx.x & 31) == 0) { S.red[threadIdx.x >> 5] = nlo; S.red[32 + (threadIdx.x >> 5)] = nhi; }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float a = INFINITY, c = -INFINITY;
-            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { a = fminf(a, S.red[w]); c = fmaxf(c, S.red[32 + w]); }
-            S.lo = a;
-            S.hi = c;
-        }
-        __syncthreads();
-        lo = S.lo;
-        hi = S.hi;
-        __syncthreads();
     }
     return lo;
 }
 
 // ---- 3. thresholds from the sample scores -----------------------------------------------------------------------
+constexpr int kSelCThreads = 256;
+
+// One row of the blocked dense scores: four consecutive columns are 16 contiguous bytes.
+struct SampleRow {
+    const float *blk;          // block row base + this row's offset inside a block
+    int n;
+    template <class F> __device__ __forceinline__ void for_each(F f) const
+    {
+        const int t = threadIdx.x, nthreads = blockDim.x, n4 = (n + 3) >> 2;
+        for (int g0 = t; g0 < n4; g0 += 2 * nthreads) {
+            float4 v[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int g = min(g0 + u * nthreads, n4 - 1);                      // group of 4 columns
+                v[u] = *reinterpret_cast<const float4 *>(blk + size_t(g >> 3) * 1024 + size_t(g & 7) * 128);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int g = g0 + u * nthreads;
+                if (g >= n4) break;
+                const int i = g * 4;
+                f(i, v[u].x);
+                if (i + 1 < n) f(i + 1, v[u].y);
+                if (i + 2 < n) f(i + 2, v[u].z);
+                if (i + 3 < n) f(i + 3, v[u].w);
+            }
+        }
+    }
+};
+
 __global__ void __launch_bounds__(kSelCThreads)
 sample_tau_kernel(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg, float *__restrict__ tau)
 {
-    extern __shared__ float ys[];
     __shared__ SelScratch S;
     const int row = blockIdx.x;
     const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
     if (row - sg.out_row0 >= sg.n_buckets) return;           // padding between segments
-    for (int i = threadIdx.x; i < sg.ns; i += blockDim.x) ys[i] = Ys[dense_offset(row, i, ldy)];
-    __syncthreads();
-    const float th = smem_select_rth(ys, sg.ns, min(sg.rank, sg.ns), S);
+    const SampleRow src{Ys + dense_block_offset(row, 0, ldy) + size_t(row & 31) * 4, sg.ns};
+    const float th = select_rth(src, sg.ns, min(sg.rank, sg.ns), S);
     if (threadIdx.x == 0) tau[row] = th;
 }
 
@@ -266,19 +280,49 @@ struct SelParams {
 };
 
 constexpr int kMaxRanges = 4;
+constexpr int kSelBitWords = 1024;          // selection bitmap: up to 32768 candidates per bucket
+
+// The candidate lists of one bucket: sub-lists (range 0, group 0), (range 0, group 1), (range 1, group 0), ...
+// Group 0 of a range was written upward from the start of the range's buffer, group 1 downward from its end;
+// concatenated in this order the entries are in key order.  `visit` hands out (ordinal, entry).
+struct CandLists {
+    const uint2 *lists;        // the bucket's buffers
+    const int *start;          // [n_sl + 1] ordinals where the sub-lists begin (shared memory)
+    int n_sl, sub_cap;
+    template <class F> __device__ __forceinline__ void visit(F f) const
+    {
+        const int t = threadIdx.x, nthreads = blockDim.x;
+        for (int sl = 0; sl < n_sl; ++sl) {
+            const int s0 = start[sl], cnt = start[sl + 1] - s0;
+            const uint2 *buf = lists + size_t(sl >> 1) * sub_cap + ((sl & 1) ? sub_cap - 1 : 0);
+            const int dir = (sl & 1) ? -1 : 1;
+            for (int j0 = t; j0 < cnt; j0 += 4 * nthreads) {
+                uint2 e[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) e[u] = buf[dir * min(j0 + u * nthreads, cnt - 1)];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (j0 + u * nthreads < cnt) f(s0 + j0 + u * nthreads, e[u]);
+            }
+        }
+    }
+    template <class F> __device__ __forceinline__ void for_each(F f) const
+    {
+        visit([&](int i, uint2 e) { f(i, __uint_as_float(e.x)); });
+    }
+};
 
 template <typename T>
 __global__ void __launch_bounds__(kSelCThreads)
 candidate_select_kernel(SelParams p)
 {
-    extern __shared__ __align__(16) unsigned char sel_smem[];
-    float *ys = reinterpret_cast<float *>(sel_smem);                    // [cap + 1] scores, later flags, later prefix sums
-    int32_t *idxs = reinterpret_cast<int32_t *>(ys + p.cap + 1);        // [cap] key index inside the segment
-    int32_t *band = idxs + p.cap;                                       // [kMaxBand] candidate positions of the band
-    float *band_y = reinterpret_cast<float *>(band + kMaxBand);        // [kMaxBand] their canonical scores
-    int32_t *band_id = reinterpret_cast<int32_t *>(band_y + kMaxBand); // [kMaxBand] their key indices
-    int32_t *band_rank = band_id + kMaxBand;                            // [kMaxBand] how many band entries beat them
     __shared__ SelScratch S;
+    __shared__ int band[kMaxBand];                                      // ordinals of the band entries
+    __shared__ int band_id[kMaxBand];                                   // their key indices
+    __shared__ float band_y[kMaxBand];                                  // their canonical scores
+    __shared__ int band_rank[kMaxBand];
+    __shared__ unsigned selbits[kSelBitWords];                          // band entries that made it
+    __shared__ float a_f32[256];
     __shared__ int s_n, s_fail, s_nin, s_nband;
     __shared__ int s_start[2 * kMaxRanges + 1];                         // sub-list starts: (range, group) in order
     __shared__ int warp_sel[32];
@@ -292,6 +336,7 @@ candidate_select_kernel(SelParams p)
     const int Z = sg.zc;
     const T *a_row = reinterpret_cast<const T *>(p.A) + size_t(bucket) * p.d;
     const int sub_cap = p.cap / p.n_ranges;
+    const uint2 *lists = p.cand + size_t(row) * p.cap;
 
     // sub-list sizes; the two groups of a range share a buffer and must not have met in the middle
     if (t == 0) {
@@ -304,54 +349,42 @@ candidate_select_kernel(SelParams p)
             n += c0 + c1;
         }
         s_start[2 * p.n_ranges] = n;
-        if (n < Z) fail = 1;
+        if (n < Z || n > kSelBitWords * 32) fail = 1;
         s_n = fail ? 0 : n;
         s_fail = fail;
         s_nin = 0;
         s_nband = 0;
     }
-    if (warp == 1) {                                         // ||a_b||
+    for (int i = t; i < p.d; i += nthreads) a_f32[i] = Elem<T>::to_f32(a_row[i]);
+    for (int i = t; i < kSelBitWords; i += nthreads) selbits[i] = 0;
+    __syncthreads();
+    if (warp == 0) {                                         // ||a_b||
         float n2 = 0.f;
-        for (int i = lane; i < p.d; i += 32) {
-            const float v = Elem<T>::to_f32(a_row[i]);
-            n2 = fmaf(v, v, n2);
-        }
+        for (int i = lane; i < p.d; i += 32) n2 = fmaf(a_f32[i], a_f32[i], n2);
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, off);
         if (lane == 0) s_anorm = sqrtf(n2) * 1.0001f;
     }
     __syncthreads();
     const int n = s_n;
+    const CandLists src{lists, s_start, 2 * p.n_ranges, sub_cap};
+
     if (!s_fail) {
-        // gather the sub-lists: (range 0, group 0), (range 0, group 1), (range 1, group 0), ...: key order overall
-        for (int sl = 0; sl < 2 * p.n_ranges; ++sl) {
-            const int start = s_start[sl], cnt = s_start[sl + 1] - start;
-            const uint2 *buf = p.cand + size_t(row) * p.cap + size_t(sl >> 1) * sub_cap;
-            for (int i = t; i < cnt; i += nthreads) {
-                const uint2 e = (sl & 1) ? buf[sub_cap - 1 - i] : buf[i];
-                ys[start + i] = __uint_as_float(e.x);
-                idxs[start + i] = int32_t(e.y);
-            }
-        }
-        __syncthreads();
-        const float theta = smem_select_rth(ys, n, Z, S);
+        const float theta = select_rth(src, n, Z, S);
         const float eps = kBandEps * s_anorm * __uint_as_float(sg.kmax_bits);
         const float lo = theta - eps, hi = theta + eps;
         // everything at or above lo has to be among the candidates, i.e. the threshold was low enough
         if (t == 0 && !(p.tau[row] <= lo) && n < sg.n_keys) s_fail = 1;
-        // classify: flag 1 = certainly selected, 2 = band, 0 = out
+        // count the certain entries (score > hi) and list the band [lo, hi]
         int my_in = 0;
-        for (int i = t; i < n; i += nthreads) {
-            const float y = ys[i];
-            float flag = 0.f;
-            if (y > hi) { flag = 1.f; ++my_in; }
+        src.visit([&](int i, uint2 e) {
+            const float y = __uint_as_float(e.x);
+            if (y > hi) ++my_in;
             else if (y >= lo) {
-                flag = 2.f;
                 const int slot = atomicAdd(&s_nband, 1);
-                if (slot < kMaxBand) band[slot] = i;
+                if (slot < kMaxBand) { band[slot] = i; band_id[slot] = int(e.y); }
             }
-            ys[i] = flag;
-        }
+        });
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) my_in += __shfl_xor_sync(0xffffffffu, my_in, off);
         if (lane == 0 && my_in) atomicAdd(&s_nin, my_in);
@@ -362,12 +395,8 @@ candidate_select_kernel(SelParams p)
         if (!s_fail) {
             // canonical scores of the band, then an exact rank: better = larger score, then lower key index
             const T *Kseg = reinterpret_cast<const T *>(p.K) + size_t(sg.kb) * p.d;
-            float *a_f32 = reinterpret_cast<float *>(S.hist);                   // the histogram is no longer needed
-            for (int i = t; i < p.d; i += nthreads) a_f32[i] = Elem<T>::to_f32(a_row[i]);
-            __syncthreads();
             for (int b = t; b < n_band; b += nthreads) {
-                const int id = idxs[band[b]];
-                const T *krow = Kseg + size_t(id) * p.d;
+                const T *krow = Kseg + size_t(band_id[b]) * p.d;
                 float y = 0.f;
                 for (int e = 0; e < p.d; e += 8) {
                     float f[8];
@@ -376,11 +405,8 @@ candidate_select_kernel(SelParams p)
                     for (int u = 0; u < 8; ++u) y = fmaf(a_f32[e + u], f[u], y);
                 }
                 band_y[b] = y;
-                band_id[b] = id;
+                band_rank[b] = 0;
             }
-            __syncthreads();
-            // rank of every band entry, all threads: entry b is looked at by `parts` threads that split the others
-            for (int b = t; b < n_band; b += nthreads) band_rank[b] = 0;
             __syncthreads();
             {
                 const int parts = max(1, nthreads / max(n_band, 1));
@@ -397,27 +423,44 @@ candidate_select_kernel(SelParams p)
                 }
             }
             __syncthreads();
-            for (int b = t; b < n_band; b += nthreads) ys[band[b]] = band_rank[b] < need ? 1.f : 0.f;
+            for (int b = t; b < n_band; b += nthreads)
+                if (band_rank[b] < need) atomicOr(&selbits[band[b] >> 5], 1u << (band[b] & 31));
             __syncthreads();
             // ordered compaction: the concatenated sub-lists are in key order, so is the table row
             int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
             int base_out = 0;
-            for (int i0 = 0; i0 < n; i0 += nthreads) {
-                const int i = i0 + t;
-                const bool sel = i < n && ys[i] == 1.f;
-                const unsigned bal = __ballot_sync(0xffffffffu, sel);
-                if (lane == 0) warp_sel[warp] = __popc(bal);
-                __syncthreads();
-                int before = 0, total = 0;
-                for (int w = 0; w < nwarps; ++w) {
-                    const int c = warp_sel[w];
-                    before += w < warp ? c : 0;
-                    total += c;
+            for (int sl = 0; sl < src.n_sl; ++sl) {
+                const int s0 = s_start[sl], cnt = s_start[sl + 1] - s0;
+                const uint2 *buf = lists + size_t(sl >> 1) * sub_cap + ((sl & 1) ? sub_cap - 1 : 0);
+                const int dir = (sl & 1) ? -1 : 1;
+                for (int j0 = 0; j0 < cnt; j0 += 4 * nthreads) {
+                    uint2 pre[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) pre[u] = buf[dir * min(j0 + u * nthreads + t, cnt - 1)];   // fetched ahead
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (j0 + u * nthreads >= cnt) break;
+                        const int j = j0 + u * nthreads + t, i = s0 + j;
+                        bool sel = false;
+                        if (j < cnt) {
+                            const float y = __uint_as_float(pre[u].x);
+                            sel = y > hi || (y >= lo && ((selbits[i >> 5] >> (i & 31)) & 1u));
+                        }
+                        const unsigned bal = __ballot_sync(0xffffffffu, sel);
+                        if (lane == 0) warp_sel[warp] = __popc(bal);
+                        __syncthreads();
+                        int before = 0, total = 0;
+                        for (int w = 0; w < nwarps; ++w) {
+                            const int c = warp_sel[w];
+                            before += w < warp ? c : 0;
+                            total += c;
+                        }
+                        const int pos = base_out + before + __popc(bal & ((1u << lane) - 1u));
+                        if (sel && pos < Z) out[pos] = sg.kb + int(pre[u].y);
+                        base_out += total;
+                        __syncthreads();
+                    }
                 }
-                const int pos = base_out + before + __popc(bal & ((1u << lane) - 1u));
-                if (sel && pos < Z) out[pos] = sg.kb + idxs[i];
-                base_out += total;
-                __syncthreads();
             }
         }
     }
@@ -460,7 +503,7 @@ bool fused_eligible(int dtype, int d, int64_t n_keys, int64_t zc)
     // buckets much smaller than the segment (otherwise a threshold filters nothing), yet not so small that the
     // key sample needed to estimate the threshold outgrows shared memory
     return (dtype == FM_BF16 || dtype == FM_F16) && (d == 64 || d == 128) && n_keys >= 8192 && zc * 4 <= n_keys && zc >= 64 &&
-           n_keys <= zc * 4096 && zc <= 10240;      // and the candidate list of a bucket has to fit in shared memory
+           n_keys <= zc * 4096 && zc <= 12288;      // and a bucket's candidates have to fit the selection bitmap
 }
 
 static int sample_rank(double z) { return (int)std::ceil(z + 6.0 * std::sqrt(z) + 2.0); }
@@ -569,8 +612,7 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
             rc = tc_project_launch(tmA, tmKs, tp, int(mtiles) * tp.n_ranges, d, true, dtype == FM_BF16, st);
             if (rc != FM_OK) return rc;
         }
-        FM_CUDA_OK(cudaFuncSetAttribute(sample_tau_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(P.ld_sample * 4)));
-        sample_tau_kernel<<<(unsigned)rows, kSelCThreads, size_t(P.ld_sample) * 4, st>>>(Ys, P.ld_sample, dsegs, ng, tau);
+        sample_tau_kernel<<<(unsigned)rows, kSelCThreads, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau);
         FM_LAUNCHED("sample_tau_kernel");
 
         tp.segs = dtc_m;
@@ -580,9 +622,7 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         if (rc != FM_OK) return rc;
 
         SelParams sp = {dsegs, ng, tp.n_ranges, P.cap, cand, counts, tau, A, K, d, table, fail_count, fail_list};
-        const size_t sel_smem = size_t(P.cap) * 8 + 16 + size_t(kMaxBand) * 16;
-        FM_CUDA_OK(cudaFuncSetAttribute(candidate_select_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sel_smem));
-        candidate_select_kernel<T><<<(unsigned)rows, kSelCThreads, sel_smem, st>>>(sp);
+        candidate_select_kernel<T><<<(unsigned)rows, kSelCThreads, 0, st>>>(sp);
         FM_LAUNCHED("candidate_select_kernel");
 
         fallback_scores_kernel<T><<<dim3((unsigned)std::min<int64_t>(ceil_div(P.max_keys, 256), 4 * sms), kMaxFail), 256, 0, st>>>(

@@ -246,26 +246,96 @@ class Memory:
         return h.reshape(Hq, S)
 
     def query(self, q: torch.Tensor, sm_scale: float, cu_seqlens_q: Optional[Sequence[int]] = None,
-              q_hashes: Optional[torch.Tensor] = None, key_chunk: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+              q_hashes: Optional[torch.Tensor] = None, key_chunk: int = 0,
+              head_range: Optional[Tuple[int, int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """q ``[Hq, S, d]`` -> (o ``[Hq, S, d]`` in q's dtype, lse ``[Hq, S]`` fp32 natural log; ``-inf``
-        and o = 0 where the query's bucket is empty)."""
+        and o = 0 where the query's bucket is empty).  ``head_range = (h0, h1)``: ``q`` holds only the queries of
+        KV heads ``h0 .. h1-1`` (uniform memories; heads are independent, so a batch can be served in slices)."""
         dev = L.require_cuda(q)
-        if q.dim() != 3 or q.shape[2] != self.d or q.shape[0] % self.n_heads:
-            raise ValueError(f"q must be [Hq, S, {self.d}] with Hq a multiple of {self.n_heads}, got {tuple(q.shape)}")
+        n_heads = self.n_heads if head_range is None else head_range[1] - head_range[0]
+        if head_range is not None and (self.n_seq != 1 or cu_seqlens_q is not None or not 0 <= head_range[0] < head_range[1] <= self.n_heads):
+            raise ValueError("head_range needs a uniform memory and 0 <= h0 < h1 <= n_heads")
+        if q.dim() != 3 or q.shape[2] != self.d or q.shape[0] % n_heads:
+            raise ValueError(f"q must be [Hq, S, {self.d}] with Hq a multiple of {n_heads}, got {tuple(q.shape)}")
         if q.dtype != self.k.dtype:
             raise TypeError(f"q ({q.dtype}) must be in the memory's dtype ({self.k.dtype})")
         q = q.contiguous()
         Hq, S, d = q.shape
-        seg_xb, max_rows = self._query_segments(Hq, S, cu_seqlens_q, dev)
+        if head_range is None:
+            seg_xb, max_rows = self._query_segments(Hq, S, cu_seqlens_q, dev)
+            seg_cb = self._seg_cb_dev
+        else:
+            key = ("range", Hq, S, n_heads)
+            hit = self._q_seg_cache.get(key)
+            if hit is None:
+                rows = (Hq // n_heads) * S
+                hit = (torch.arange(0, (n_heads + 1) * rows, rows, dtype=torch.int32, device=dev), rows)
+                self._q_seg_cache[key] = hit
+            seg_xb, max_rows = hit
+            seg_cb = self._seg_cb_dev[head_range[0]: head_range[1] + 1]
         qf = q.reshape(Hq * S, d)
         if q_hashes is None:
-            hashes = ops.hash_rows(qf, self.A, seg_xb, self._seg_cb_dev, max_rows)
+            hashes = ops.hash_rows(qf, self.A, seg_xb, seg_cb, max_rows)
         else:
             hashes = q_hashes.reshape(-1).to(torch.int32).contiguous()
-        group_off, perm = ops.group_rows(hashes, self.total_buckets, seg_xb, self._seg_cb_dev)
+        group_off, perm = ops.group_rows(hashes, self.total_buckets, seg_xb, seg_cb)
         o, lse = ops.hashed_attention(qf, self.k.reshape(-1, d), self.v.reshape(-1, d), self.table, self.bucket_off,
                                       group_off, perm, sm_scale, self.max_bucket_len, key_chunk=key_chunk)
         return o.reshape(Hq, S, d), lse.reshape(Hq, S)
+
+    def query_from_host(self, q_host: torch.Tensor, sm_scale: float, o_host: torch.Tensor, lse_host: torch.Tensor,
+                        n_chunks: int = 4, local: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
+        """Serve queries that live in pinned HOST memory and leave the result in pinned host memory, overlapping the
+        copies with the kernels: the KV heads are cut into ``n_chunks`` slices; slice i + 1 is copied in and slice
+        i - 1 copied out while slice i is attended.
+
+        ``q_host`` ``[Hq, S, d]`` (memory dtype), ``o_host`` ``[Hq, S, d]`` (memory dtype), ``lse_host`` ``[Hq, S]`` fp32,
+        all pinned.  ``local = (o_local, lse_local)``: fp32 device tensors of a second attention result over other keys
+        (e.g. a local window) to LSE-merge with the memory's result before it is copied out (mem:332).
+        Returns after the work is enqueued; synchronise the current stream before reading the host tensors."""
+        if self.n_seq != 1:
+            raise ValueError("query_from_host serves uniform memories")
+        for t in (q_host, o_host, lse_host):
+            if not t.is_pinned():
+                raise ValueError("host tensors must be pinned")
+        dev = self.k.device
+        Hq, S, d = q_host.shape
+        G = Hq // self.n_heads
+        n_chunks = max(1, min(n_chunks, self.n_heads))
+        bounds = [round(i * self.n_heads / n_chunks) for i in range(n_chunks + 1)]
+        main = torch.cuda.current_stream(dev)
+        if not hasattr(self, "_copy_streams"):
+            self._copy_streams = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+        s_in, s_out = self._copy_streams
+        s_in.wait_stream(main)
+        q_dev = torch.empty(Hq, S, d, dtype=q_host.dtype, device=dev)
+        ev_in = []
+        with torch.cuda.stream(s_in):
+            for i in range(n_chunks):
+                a, b = bounds[i] * G, bounds[i + 1] * G
+                q_dev[a:b].copy_(q_host[a:b], non_blocking=True)
+                e = torch.cuda.Event()
+                e.record(s_in)
+                ev_in.append(e)
+        q_dev.record_stream(s_in)
+        for i in range(n_chunks):
+            a, b = bounds[i] * G, bounds[i + 1] * G
+            main.wait_event(ev_in[i])
+            o, lse = self.query(q_dev[a:b], sm_scale, head_range=(bounds[i], bounds[i + 1]))
+            if local is not None:
+                acc_o = local[0][a:b].clone()
+                acc_l = local[1][a:b].clone()
+                ops.lse_merge(acc_o, acc_l, o, lse)
+                o, lse = acc_o.to(q_host.dtype), acc_l
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                o_host[a:b].copy_(o, non_blocking=True)
+                lse_host[a:b].copy_(lse, non_blocking=True)
+            o.record_stream(s_out)
+            lse.record_stream(s_out)
+        main.wait_stream(s_out)
 
     # ---- persistence ---------------------------------------------------------------------------------
     def state_dict(self) -> dict:

@@ -266,6 +266,33 @@ def test_attention_hash_dropin_with_key_range():
     assert (lse.float().cpu() - O.dropin_lse(lse_ref, torch.bfloat16).float()).abs().max() <= 4e-2   # bf16 LSE (tk:111)
 
 
+def test_head_slices_and_host_pipeline_match_one_call():
+    """Queries served in slices of KV heads (with GQA folding), and the pinned-host pipeline built on them."""
+    cfg = synth.config("cfg3")
+    q, k, v = synth.make(cfg, seed=6, kv_heads=6, n_keys=8192, n_queries=40)           # q [24, 40, 128]
+    mem = fm.Memory.build(k.to(DEV), v.to(DEV), n_buckets=64, bucket_size=300, kmeans_iters=1)
+    qd = q.to(DEV)
+    o, lse = mem.query(qd, 0.1)
+    G = cfg.q_groups
+    o2, l2 = mem.query(qd[2 * G: 5 * G].contiguous(), 0.1, head_range=(2, 5))
+    assert torch.equal(o2, o[2 * G: 5 * G]) and torch.equal(l2, lse[2 * G: 5 * G])
+    q_host = q.pin_memory()
+    o_host = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    l_host = torch.empty(q.shape[:2], dtype=torch.float32).pin_memory()
+    for chunks in (1, 4):
+        o_host.zero_()
+        mem.query_from_host(q_host, 0.1, o_host, l_host, n_chunks=chunks)
+        torch.cuda.synchronize()
+        assert torch.equal(o_host, o.cpu()) and torch.equal(l_host, lse.cpu())
+    # merged with a second result before the copy-out
+    lo = torch.randn(q.shape, device=DEV)
+    ll = torch.randn(q.shape[:2], device=DEV)
+    mem.query_from_host(q_host, 0.1, o_host, l_host, n_chunks=3, local=(lo, ll))
+    torch.cuda.synchronize()
+    ro, rl = fm.merge(lo, ll, o, lse)
+    assert (o_host.float() - ro.cpu()).abs().max() <= 2e-2 and (l_host - rl.cpu()).abs().max() <= 1e-5
+
+
 def test_state_dict_round_trip():
     cfg = synth.config("cfg1")
     q, k, v = synth.make(cfg, seed=2)
