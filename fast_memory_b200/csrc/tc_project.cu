@@ -25,6 +25,46 @@ constexpr int kTcThreads = 320;
 
 template <bool DENSE> struct TcCfg { static constexpr int STAGES = 3; };
 
+constexpr int kGroupsPerBatch = 8;          // a batch of 32 columns is 8 groups of four columns
+
+// Appends a group of four scores to a candidate list when any of the four reaches tau, and sets the group's bit in
+// the batch mask.  Branch-free (some lane of the 32 almost always has a hit, so a divergent branch would run the body
+// for every group anyway).  The epilogue looks at every one of the C x N scores, so what matters is instructions per
+// score:
+//  - the four scores are four consecutive registers of the TMEM load, stored as they lie (a 16-byte store wants an
+//    aligned register quad; a column inside the entry would cost a register move per score).  Which keys an entry
+//    holds is recorded instead in one bit per group: 64 bits per (bucket, key tile), stored once per tile;
+//  - the list position is a 32-bit byte offset from the array base: predicated 64-bit pointer bumps and wide
+//    multiply-adds cost several instructions each.
+// Every operand is an untyped 32-bit register: the scores are floats to max / setp and bits to the store.
+template <int J>
+__device__ __forceinline__ void append_group(const uint4 *cand, uint32_t &off16, uint32_t step16, uint32_t &mask8, uint32_t tau_bits,
+                                             uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 m;\n\t.reg .b64 a, o;\n\t"
+                 "cvt.u64.u32 o, %0;\n\t"
+                 "add.s64 a, %2, o;\n\t"
+                 "max.f32 m, %4, %5, %6;\n\t"
+                 "max.f32 m, m, %7;\n\t"
+                 "setp.ge.f32 p, m, %3;\n\t"
+                 "@p st.global.v4.b32 [a], {%4, %5, %6, %7};\n\t"
+                 "@p add.u32 %0, %0, %8;\n\t"
+                 "@p add.u32 %1, %1, %9;\n\t}"
+                 : "+r"(off16), "+r"(mask8)
+                 : "l"(cand), "r"(tau_bits), "r"(s0), "r"(s1), "r"(s2), "r"(s3), "r"(step16), "n"(1 << J)
+                 : "memory");
+}
+
+template <int J>
+__device__ __forceinline__ void append_groups(const uint4 *cand, uint32_t &off16, uint32_t step16, uint32_t &mask8, uint32_t tau_bits,
+                                              const uint32_t (&v)[32])
+{
+    if constexpr (J < kGroupsPerBatch) {
+        append_group<J>(cand, off16, step16, mask8, tau_bits, v[4 * J], v[4 * J + 1], v[4 * J + 2], v[4 * J + 3]);
+        append_groups<J + 1>(cand, off16, step16, mask8, tau_bits, v);
+    }
+}
+
 }  // namespace
 
 template <int D, bool DENSE>
@@ -137,18 +177,17 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const bool row_ok = m0 + m < sg.n_buckets;
         const int grow = sg.out_row0 + m0 + m;               // row of this bucket in the outputs
         float tau = 0.f;
-        uint2 *wp = nullptr, *list0 = nullptr;
-        int step = 1, sub_cap = 0, cursor = 0;
-        long long step_bytes = 8;
+        uint32_t first16 = 0, off16 = 0, step16 = 16u;       // byte offsets into cand
+        int sub_cap = 0, cursor = 0;
         bool overflow = false;
         if constexpr (!DENSE) {
             if (row_ok) {
                 // one buffer per key range, shared by the two groups: group 0 fills it upward, group 1 downward
                 tau = p.tau[grow];
                 sub_cap = p.cap / p.n_ranges;
-                list0 = p.cand + size_t(grow) * p.cap + size_t(range) * sub_cap;
-                if (g) { step = -1; step_bytes = -8; list0 += sub_cap - 1; }
-                wp = list0;
+                uint32_t slot = uint32_t(grow) * uint32_t(p.cap) + uint32_t(range) * uint32_t(sub_cap);    // host: the arrays stay below 4 GB
+                if (g) { slot += sub_cap - 1; step16 = uint32_t(-16); }
+                first16 = off16 = slot * 16u;
             }
         }
         bool ok = true;
@@ -159,11 +198,9 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tc::fence_after_sync();
             const int col0 = (t_begin + tile_of(t)) * kBN;
             const bool last = col0 + kBN > sg.n_keys;        // only the segment's last tile can be partial
-#pragma unroll 1
-            for (int b = 0; b < kBN / 32; ++b) {
-                uint32_t v[32];
-                tc::tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + g * kBN + b * 32, v);
-                tc::tmem_ld_wait();
+            uint32_t mask_lo = 0, mask_hi = 0;               // which of the tile's 64 groups of four keys were appended
+            // batches of 32 columns (loading the next batch while this one is looked at was measured: no gain)
+            auto batch = [&](uint32_t (&v)[32], int b) {
                 const int c0 = col0 + b * 32;
                 if constexpr (DENSE) {
                     // blocked layout (see dense_offset): the 32 lanes of a store instruction write 512 contiguous bytes
@@ -181,30 +218,37 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                             if (e >= live) v[e] = 0xff800000u;                       // -inf never passes
                     }
                     if (row_ok) {
-                        if (!overflow && cursor + 32 <= sub_cap) {
-                            // predicated (branch-free) append: a divergent branch per score would cost far more than
-                            // the three predicated instructions
-                            uint32_t col = uint32_t(c0);
-#pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                asm volatile("{\n\t.reg .pred p;\n\t"
-                                             "setp.ge.f32 p, %1, %2;\n\t"
-                                             "@p st.global.v2.u32 [%0], {%3, %4};\n\t"
-                                             "@p add.s64 %0, %0, %5;\n\t}"
-                                             : "+l"(wp) : "f"(__uint_as_float(v[e])), "f"(tau), "r"(v[e]), "r"(col + e), "l"(step_bytes) : "memory");
-                            }
-                            cursor = int((wp - list0) * step);
+                        if (!overflow && cursor + kGroupsPerBatch <= sub_cap) {
+                            uint32_t mask8 = 0;
+                            append_groups<0>(p.cand, off16, step16, mask8, __float_as_uint(tau), v);
+                            if (b < 4) mask_lo |= mask8 << (8 * b); else mask_hi |= mask8 << (8 * b - 32);
+                            cursor = int((off16 - first16) * (g ? uint32_t(-1) : 1u)) >> 4;
                         } else {
                             overflow = true;                 // keep counting so that the selection sees the overflow
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) cursor += __uint_as_float(v[e]) >= tau ? 1 : 0;
+                            for (int j = 0; j < 32; j += 4) {
+                                const float m = fmaxf(fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 1])),
+                                                      fmaxf(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])));
+                                cursor += m >= tau ? 1 : 0;
+                            }
                         }
                     }
                 }
+            };
+            const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + g * kBN;
+#pragma unroll 1
+            for (int b = 0; b < kBN / 32; ++b) {
+                uint32_t v[32];
+                tc::tmem_ld_x32(t_addr + b * 32, v);
+                tc::tmem_ld_wait();
+                batch(v, b);
             }
             tc::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(tempty_bar(g));
+            if constexpr (!DENSE) {
+                if (row_ok) p.cand_mask[size_t(t_begin + tile_of(t)) * p.mask_ld + grow] = make_uint2(mask_lo, mask_hi);   // coalesced: 32 rows
+            }
         }
         if (!ok && lane == 0) { atomicExch(p.status, 3); s_abort = 1; }
         if constexpr (!DENSE) {

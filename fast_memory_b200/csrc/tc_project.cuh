@@ -26,9 +26,13 @@ struct TcParams {
     int64_t ldy;           // columns per row, a multiple of 32
     // candidate epilogue
     const float *tau;      // [total buckets] threshold of every bucket
-    uint2 *cand;           // [total buckets][cap] (score bits, key index local to the segment); one buffer of
-                           // cap / n_ranges slots per range, filled upward by epilogue group 0 (first half of the
-                           // range's tiles) and downward by group 1 (second half): both in ascending key order
+    uint4 *cand;           // [total buckets][cap] groups of four scores (bits) of four consecutive keys, kept when any of
+                           // the four reaches tau; one buffer of cap / n_ranges slots per range, filled upward by
+                           // epilogue group 0 (first half of the range's tiles) and downward by group 1 (second half):
+                           // both in ascending key order
+    uint2 *cand_mask;      // [key tile of the segment][mask_ld] one bit per group of the tile (bit i = keys 4i .. 4i+3 of
+                           // the tile): the groups that were appended, i.e. which keys the entries hold
+    int64_t mask_ld;       // rows of cand_mask (>= total buckets)
     int cap;
     int *cand_count;       // [total buckets][n_ranges][2]; cap / n_ranges + 1 marks an overflow
     int *status;           // set non-zero when a wait gave up
