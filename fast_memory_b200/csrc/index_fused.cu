@@ -4,7 +4,8 @@
 //   1. key_norm_max:   kmax_s = max_j ||k_j|| per segment (bounds the accumulation error of a score).
 //   2. sample scores:  tensor-core projection of every `step`-th key (dense epilogue, small).
 //   3. thresholds:     tau_b = the r-th largest sample score of bucket b, r chosen so that about
-//                      (r / z) Z keys pass and fewer than Z pass with probability ~1e-9 (z = Z / step).
+//                      (r / z) Z keys pass and fewer than Z pass with probability ~1e-6 per bucket (z = Z / step;
+//                      such a bucket goes to the fallback).
 //   4. candidates:     tensor-core projection of ALL keys; the epilogue appends (score, key) for score >= tau_b
 //                      to the bucket's candidate list, in key order.
 //   5. selection:      per bucket, theta = Z-th largest candidate score.  Scores come from the tensor cores
@@ -741,7 +742,7 @@ static int choose_ranges(int64_t mtiles, int64_t min_tiles, int sms)
     return best;
 }
 
-static int sample_rank(double z) { return (int)std::ceil(z + 6.0 * std::sqrt(z) + 2.0); }
+static int sample_rank(double z) { return (int)std::ceil(z + 5.0 * std::sqrt(z) + 2.0); }
 
 // Layout of the workspace for the eligible segments.  Groups are sized so that the sample scores and the candidate
 // lists of one group stay within ~3 GB.

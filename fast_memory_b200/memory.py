@@ -17,6 +17,7 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence, Tuple, Union
 
+import numpy as np
 import torch
 
 from . import _lib as L
@@ -115,14 +116,12 @@ class Memory:
         Zs = _per_seq(bucket_size, n_seq, "bucket_size")
         # segments tile the flat [H * N_total] key rows: segment (h, s) starts at h * N_total + cu[s]
         seg_kb = [h * N_total + cu[s] for h in range(H) for s in range(n_seq)] + [H * N_total]
-        seg_cb, seg_z, table_off, bucket_len = [0], [], [0], []
-        for h in range(H):
-            for s in range(n_seq):
-                zc = min(Zs[s], cu[s + 1] - cu[s])
-                seg_cb.append(seg_cb[-1] + Cs[s])
-                seg_z.append(Zs[s])
-                bucket_len += [zc] * Cs[s]
-                table_off.append(table_off[-1] + Cs[s] * zc)
+        seq_zc = [min(Zs[s], cu[s + 1] - cu[s]) for s in range(n_seq)]
+        seg_c = np.tile(np.asarray(Cs, dtype=np.int64), H)                       # buckets of every segment
+        seg_zc = np.tile(np.asarray(seq_zc, dtype=np.int64), H)                  # keys per bucket of every segment
+        seg_cb = [0] + np.cumsum(seg_c).tolist()
+        seg_z = [Zs[s] for _ in range(H) for s in range(n_seq)]
+        table_off = [0] + np.cumsum(seg_c * seg_zc).tolist()
         self.seg_kb, self.seg_cb, self.seg_z, self.table_off = seg_kb, seg_cb, seg_z, table_off
         self.seq_buckets = Cs
         total_c = seg_cb[-1]
@@ -162,14 +161,14 @@ class Memory:
                                        L.ptr(table), flags, L.ptr(ws), ws.numel(), L.stream_ptr(dev)), "fm_index_build")
         self.build_status = ws[:4].view(torch.int32)[0].clone()  # device scalar: 0 = ok (see check_build)
         self.table = table
+        # the host-side prefix arrays are made while the device builds the table
+        bucket_off = np.zeros(total_c + 1, dtype=np.int64)
+        np.cumsum(np.repeat(seg_zc, seg_c), out=bucket_off[1:])
+        self.bucket_off = torch.from_numpy(bucket_off).to(dev, non_blocking=True)
+        self.max_bucket_len = int(seg_zc.max()) if total_c else 0
+        self._seg_cb_dev = torch.tensor(seg_cb, dtype=torch.int32).to(dev, non_blocking=True)
         if check:
             self.check_build()
-        blen = torch.tensor(bucket_len, dtype=torch.int64)
-        bucket_off = torch.zeros(total_c + 1, dtype=torch.int64)
-        torch.cumsum(blen, 0, out=bucket_off[1:])
-        self.bucket_off = bucket_off.to(dev)
-        self.max_bucket_len = max(bucket_len) if bucket_len else 0
-        self._seg_cb_dev = torch.tensor(seg_cb, dtype=torch.int32, device=dev)
         if key_range is not None:
             self._apply_key_range(key_range)
         return self
@@ -284,7 +283,8 @@ class Memory:
         return o.reshape(Hq, S, d), lse.reshape(Hq, S)
 
     def query_from_host(self, q_host: torch.Tensor, sm_scale: float, o_host: torch.Tensor, lse_host: torch.Tensor,
-                        n_chunks: int = 4, local: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
+                        n_chunks: int = 4, local: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                        overlap_calls: bool = False) -> None:
         """Serve queries that live in pinned HOST memory and leave the result in pinned host memory, overlapping the
         copies with the kernels: the KV heads are cut into ``n_chunks`` slices; slice i + 1 is copied in and slice
         i - 1 copied out while slice i is attended.
@@ -292,7 +292,12 @@ class Memory:
         ``q_host`` ``[Hq, S, d]`` (memory dtype), ``o_host`` ``[Hq, S, d]`` (memory dtype), ``lse_host`` ``[Hq, S]`` fp32,
         all pinned.  ``local = (o_local, lse_local)``: fp32 device tensors of a second attention result over other keys
         (e.g. a local window) to LSE-merge with the memory's result before it is copied out (mem:332).
-        Returns after the work is enqueued; synchronise the current stream before reading the host tensors."""
+        Returns after the work is enqueued; synchronise the current stream before reading the host tensors.
+
+        ``overlap_calls=True`` lets consecutive calls overlap as well (the next call's first copy-in runs under this
+        call's kernels, this call's last copy-out under the next call's): the device queries are staged in two
+        alternating buffers, and the current stream no longer waits for the copy-out - call
+        :meth:`finish_host_queries` (or synchronise the device) before reading the host tensors."""
         if self.n_seq != 1:
             raise ValueError("query_from_host serves uniform memories")
         for t in (q_host, o_host, lse_host):
@@ -306,9 +311,21 @@ class Memory:
         main = torch.cuda.current_stream(dev)
         if not hasattr(self, "_copy_streams"):
             self._copy_streams = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+            self._stage = [None, None]                       # device copies of the queries, used alternately
+            self._stage_free = [None, None]                  # recorded when the kernels that read a stage are enqueued
+            self._stage_next = 0
         s_in, s_out = self._copy_streams
-        s_in.wait_stream(main)
-        q_dev = torch.empty(Hq, S, d, dtype=q_host.dtype, device=dev)
+        slot = self._stage_next
+        self._stage_next ^= 1
+        q_dev = self._stage[slot]
+        if q_dev is None or q_dev.shape != q_host.shape or q_dev.dtype != q_host.dtype:
+            s_in.wait_stream(main)
+            with torch.cuda.stream(s_in):                    # allocated on the copy stream: reuse is ordered there
+                q_dev = self._stage[slot] = torch.empty(Hq, S, d, dtype=q_host.dtype, device=dev)
+        if self._stage_free[slot] is not None:
+            s_in.wait_event(self._stage_free[slot])          # the kernels of two calls ago have read this stage
+        if not overlap_calls:
+            s_in.wait_stream(main)
         ev_in = []
         with torch.cuda.stream(s_in):
             for i in range(n_chunks):
@@ -317,7 +334,6 @@ class Memory:
                 e = torch.cuda.Event()
                 e.record(s_in)
                 ev_in.append(e)
-        q_dev.record_stream(s_in)
         for i in range(n_chunks):
             a, b = bounds[i] * G, bounds[i + 1] * G
             main.wait_event(ev_in[i])
@@ -335,7 +351,16 @@ class Memory:
                 lse_host[a:b].copy_(lse, non_blocking=True)
             o.record_stream(s_out)
             lse.record_stream(s_out)
-        main.wait_stream(s_out)
+        free = torch.cuda.Event()
+        free.record(main)
+        self._stage_free[slot] = free
+        if not overlap_calls:
+            main.wait_stream(s_out)
+
+    def finish_host_queries(self) -> None:
+        """Make the current stream wait for the copy-outs of earlier :meth:`query_from_host` calls."""
+        if hasattr(self, "_copy_streams"):
+            torch.cuda.current_stream(self.k.device).wait_stream(self._copy_streams[1])
 
     # ---- persistence ---------------------------------------------------------------------------------
     def state_dict(self) -> dict:

@@ -291,6 +291,19 @@ def test_head_slices_and_host_pipeline_match_one_call():
     torch.cuda.synchronize()
     ro, rl = fm.merge(lo, ll, o, lse)
     assert (o_host.float() - ro.cpu()).abs().max() <= 2e-2 and (l_host - rl.cpu()).abs().max() <= 1e-5
+    # consecutive calls that overlap one another: three different query sets, each into its own host tensors
+    sets = []
+    for i in range(3):
+        qi = (q.float() + 0.05 * i * torch.randn(q.shape, generator=torch.Generator().manual_seed(i))).to(q.dtype)
+        sets.append((qi.pin_memory(), torch.empty(q.shape, dtype=q.dtype).pin_memory(),
+                     torch.empty(q.shape[:2], dtype=torch.float32).pin_memory()))
+    for qi, oi, li in sets:
+        mem.query_from_host(qi, 0.1, oi, li, n_chunks=2, overlap_calls=True)
+    mem.finish_host_queries()
+    torch.cuda.current_stream().synchronize()
+    for qi, oi, li in sets:
+        o_ref, l_ref = mem.query(qi.to(DEV), 0.1)
+        assert torch.equal(oi, o_ref.cpu()) and torch.equal(li, l_ref.cpu())
 
 
 def test_state_dict_round_trip():
