@@ -2,6 +2,7 @@
 // Stands in for the einsum + argmax of the reference (memory.py:281-283, triton_kernel.py:280-281).
 #include "mma_utils.cuh"
 #include "simt_tile.cuh"
+#include "tc_utils.cuh"
 
 namespace fm {
 
@@ -86,11 +87,16 @@ struct Top3 {
     float best, second, third;
     int arg, arg2;
 };
+// Branch-free (the lanes of a warp hold different rows, so a branchy insert runs every arm): the earlier score keeps its
+// place on a tie, like "first maximum wins".
 __device__ __forceinline__ void top3_push(Top3 &t, float v, int c)
 {
-    if (v > t.best) { t.third = t.second; t.second = t.best; t.arg2 = t.arg; t.best = v; t.arg = c; }
-    else if (v > t.second) { t.third = t.second; t.second = v; t.arg2 = c; }
-    else if (v > t.third) t.third = v;
+    const bool gb = v > t.best, gs = v > t.second;
+    t.third = fmaxf(t.third, fminf(t.second, v));
+    t.second = fmaxf(t.second, fminf(t.best, v));
+    t.arg2 = gb ? t.arg : (gs ? c : t.arg2);
+    t.arg = gb ? c : t.arg;
+    t.best = fmaxf(t.best, v);
 }
 
 // amax[s] = max row norm of the A rows of segment s (as the bits of a non-negative float, via atomicMax)
@@ -200,10 +206,21 @@ hash_rows_mma_kernel(const T *__restrict__ x, const T *__restrict__ A, int n_row
                 mma16816<T>(s1, qf[ks], b[2], b[3]);
             }
             const int ca = c0 + nt2 * 16 + tq * 2;             // bucket of s0[0] / s0[2]; s1 is 8 further
-            if (ca < C) { top3_push(top[0], s0[0], ca); top3_push(top[1], s0[2], ca); }
-            if (ca + 1 < C) { top3_push(top[0], s0[1], ca + 1); top3_push(top[1], s0[3], ca + 1); }
-            if (ca + 8 < C) { top3_push(top[0], s1[0], ca + 8); top3_push(top[1], s1[2], ca + 8); }
-            if (ca + 9 < C) { top3_push(top[0], s1[1], ca + 9); top3_push(top[1], s1[3], ca + 9); }
+            if (c0 + nt2 * 16 + 16 > C) {                       // the segment's last, partial group of 16 buckets
+                if (ca >= C) { s0[0] = -INFINITY; s0[2] = -INFINITY; }
+                if (ca + 1 >= C) { s0[1] = -INFINITY; s0[3] = -INFINITY; }
+                if (ca + 8 >= C) { s1[0] = -INFINITY; s1[2] = -INFINITY; }
+                if (ca + 9 >= C) { s1[1] = -INFINITY; s1[3] = -INFINITY; }
+            }
+            // a score enters the top three only if it beats the third: one test for the four scores of a row
+            if (fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1])) > top[0].third) {
+                top3_push(top[0], s0[0], ca); top3_push(top[0], s0[1], ca + 1);
+                top3_push(top[0], s1[0], ca + 8); top3_push(top[0], s1[1], ca + 9);
+            }
+            if (fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3])) > top[1].third) {
+                top3_push(top[1], s0[2], ca); top3_push(top[1], s0[3], ca + 1);
+                top3_push(top[1], s1[2], ca + 8); top3_push(top[1], s1[3], ca + 9);
+            }
         }
         __syncthreads();                                         // tile consumed before its buffer is refilled
     }
@@ -242,47 +259,50 @@ hash_rows_mma_kernel(const T *__restrict__ x, const T *__restrict__ A, int n_row
     }
 }
 
-// One warp per listed row: canonical argmax (fp32 FMA chain per bucket, first maximum wins).
+// One CTA per listed row: canonical argmax (fp32 FMA chain per bucket, first maximum wins).  The list is short and
+// a chain is a long string of dependent steps, so the row's buckets are spread over the whole CTA and a thread fetches
+// a bucket's row in one go (up to 16 loads in flight) before it runs the chain.
+constexpr int kRecheckThreads = 256;
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kRecheckThreads)
 hash_recheck_kernel(const T *__restrict__ x, const T *__restrict__ A, int d, int n_rows, int total_buckets, int n_seg,
                     const int32_t *__restrict__ seg_xb, const int32_t *__restrict__ seg_cb,
                     const int32_t *__restrict__ recheck, const int *__restrict__ n_recheck,
                     int32_t *__restrict__ hash_out)
 {
-    __shared__ float xs[4][256];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ float xs[256];
+    __shared__ float wbest[kRecheckThreads / 32];
+    __shared__ int warg[kRecheckThreads / 32];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int n = min(*n_recheck, n_rows);
-    for (int i = blockIdx.x * 4 + warp; i < n; i += gridDim.x * 4) {
+    for (int i = blockIdx.x; i < n; i += gridDim.x) {
         const int row = recheck[i];
         const int s = seg_xb ? find_segment(seg_xb, n_seg, row) : 0;
         const int cb0 = seg_cb ? seg_cb[s] : 0;
         const int C = (seg_cb ? seg_cb[s + 1] : total_buckets) - cb0;
-        __syncwarp();
-        for (int e = lane; e < d; e += 32) xs[warp][e] = Elem<T>::to_f32(x[size_t(row) * d + e]);
-        __syncwarp();
+        __syncthreads();
+        for (int e = t; e < d; e += kRecheckThreads) xs[e] = Elem<T>::to_f32(x[size_t(row) * d + e]);
+        __syncthreads();
         float best = -INFINITY;
         int arg = 0x7fffffff;
-        // four buckets per lane at a time: the chains are independent, which hides the FMA latency
-        for (int c = lane; c < C; c += 128) {
-            float y[4] = {0.f, 0.f, 0.f, 0.f};
-            const T *a[4];
+        for (int c = t; c < C; c += kRecheckThreads) {
+            const T *a = A + size_t(cb0 + c) * d;
+            float y = 0.f;
+            for (int e0 = 0; e0 < d; e0 += 128) {
+                uint4 raw[16];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) a[u] = A + size_t(cb0 + min(c + 32 * u, C - 1)) * d;
-            for (int e = 0; e < d; e += 8) {
-                float f[4][8];
+                for (int u = 0; u < 16; ++u)
+                    if (e0 + 8 * u < d) raw[u] = *reinterpret_cast<const uint4 *>(a + e0 + 8 * u);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) widen8(*reinterpret_cast<const uint4 *>(a[u] + e), f[u], T());
+                for (int u = 0; u < 16; ++u)
+                    if (e0 + 8 * u < d) {
+                        float f[8];
+                        widen8(raw[u], f, T());
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    const float xv = xs[warp][e + v];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) y[u] = fmaf(f[u][v], xv, y[u]);
-                }
+                        for (int k = 0; k < 8; ++k) y = fmaf(f[k], xs[e0 + 8 * u + k], y);
+                    }
             }
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (c + 32 * u < C && (y[u] > best || arg == 0x7fffffff)) { best = y[u]; arg = c + 32 * u; }
+            if (y > best || arg == 0x7fffffff) { best = y; arg = c; }
         }
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) {
@@ -290,8 +310,214 @@ hash_recheck_kernel(const T *__restrict__ x, const T *__restrict__ A, int d, int
             const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
             if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
         }
-        if (lane == 0) hash_out[row] = arg == 0x7fffffff ? 0 : arg;
+        if (lane == 0) { wbest[warp] = best; warg[warp] = arg; }
+        __syncthreads();
+        if (t == 0) {
+            for (int w = 1; w < kRecheckThreads / 32; ++w) {
+                const float ob = wbest[w];
+                const int oa = warg[w];
+                if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+            }
+            hash_out[row] = arg == 0x7fffffff ? 0 : arg;
+        }
     }
+}
+
+// ---- tcgen05 path for large batches of 16-bit rows -----------------------------------------------------------
+// The same filter with the scores from the 5th-generation tensor cores: a CTA takes 128 rows (the M side of the MMA,
+// loaded once by TMA) and streams the segment's buckets through in tiles of 128 (the N side); the fp32 accumulators
+// live in TMEM (two of 128 columns, so the MMAs of one tile run under the scan of the previous one), and each of the
+// 128 epilogue threads owns one row - the 32x32b TMEM load hands a thread consecutive columns of its own lane - and
+// keeps that row's running top three in registers.  warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = epilogue.
+// Every wait is bounded; if one gives up, the CTA's rows go to the re-check list, which decides them exactly.
+constexpr int kThBM = 128, kThBN = 128, kThThreads = 192, kThStages = 2;
+constexpr int64_t kTcHashMinRows = 2048;     // below this the set-up of the tcgen05 pipeline does not pay
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThThreads, 2)
+hash_rows_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmA, const T *__restrict__ x,
+                    const T *__restrict__ A, int n_rows, int total_buckets, const int32_t *__restrict__ seg_xb,
+                    const int32_t *__restrict__ seg_cb, const unsigned *__restrict__ amax, int32_t *__restrict__ hash_out,
+                    int32_t *__restrict__ recheck, int *__restrict__ n_recheck, uint32_t idesc)
+{
+    constexpr int KB = D / 64;                               // 64-element (128-byte) k-blocks
+    constexpr uint32_t X_BYTES = KB * kThBM * 128, STAGE_BYTES = KB * kThBN * 128;
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t bars[2 * kThStages + 1 + 4];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_abort;
+
+    const int s = blockIdx.y;
+    const int row0 = seg_xb ? seg_xb[s] : 0;
+    const int row1 = seg_xb ? seg_xb[s + 1] : n_rows;
+    const int cb0 = seg_cb ? seg_cb[s] : 0;
+    const int C = (seg_cb ? seg_cb[s + 1] : total_buckets) - cb0;
+    const int r0 = row0 + blockIdx.x * kThBM;
+    if (r0 >= row1) return;                                  // before any barrier or allocation
+    const int n_tiles = (C + kThBN - 1) / kThBN;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (tc::smem_addr(smem_dyn) + 1023u) & ~1023u;          // 1024-byte aligned tiles
+    const uint32_t x_smem = base, a_smem = base + X_BYTES;
+    const uint32_t bar0 = tc::smem_addr(bars);
+    auto full_bar = [&](int i) { return bar0 + 8u * i; };
+    auto empty_bar = [&](int i) { return bar0 + 8u * (kThStages + i); };
+    const uint32_t x_bar = bar0 + 8u * (2 * kThStages);
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * kThStages + 1 + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * kThStages + 3 + a); };
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kThStages; ++i) { tc::mbar_init(full_bar(i), 1); tc::mbar_init(empty_bar(i), 1); }
+        tc::mbar_init(x_bar, 1);
+        for (int a = 0; a < 2; ++a) { tc::mbar_init(tfull_bar(a), 1); tc::mbar_init(tempty_bar(a), 4); }
+        tc::mbar_fence_init();
+        s_abort = 0;
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_addr(&tmem_slot), 2 * kThBN);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc::prefetch_tensormap(&tmX);
+            tc::prefetch_tensormap(&tmA);
+            tc::mbar_arrive_expect_tx(x_bar, X_BYTES);
+            for (int kb = 0; kb < KB; ++kb) tc::tma_load_2d(x_smem + kb * (kThBM * 128), &tmX, kb * 64, r0, x_bar);
+            for (int t = 0; t < n_tiles; ++t) {
+                const int st = t % kThStages;
+                if (!tc::mbar_wait(empty_bar(st), ((t / kThStages) & 1) ^ 1) || *(volatile int *)&s_abort) { s_abort = 1; break; }
+                tc::mbar_arrive_expect_tx(full_bar(st), STAGE_BYTES);
+                for (int kb = 0; kb < KB; ++kb)
+                    tc::tma_load_2d(a_smem + st * STAGE_BYTES + kb * (kThBN * 128), &tmA, kb * 64, cb0 + t * kThBN, full_bar(st));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = tc::mbar_wait(x_bar, 0);
+            for (int t = 0; ok && t < n_tiles; ++t) {
+                const int st = t % kThStages, acc = t & 1;
+                ok = tc::mbar_wait(tempty_bar(acc), ((t >> 1) & 1) ^ 1) && tc::mbar_wait(full_bar(st), (t / kThStages) & 1);
+                if (!ok || *(volatile int *)&s_abort) { ok = false; break; }
+                tc::fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kThBN;
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t da = tc::smem_desc_sw128(x_smem + kb * (kThBM * 128) + k * 32);
+                        const uint64_t db = tc::smem_desc_sw128(a_smem + st * STAGE_BYTES + kb * (kThBN * 128) + k * 32);
+                        tc::umma_f16(d_tmem, da, db, idesc, (kb | k) != 0);
+                    }
+                }
+                tc::umma_commit(empty_bar(st));
+                tc::umma_commit(tfull_bar(acc));
+            }
+            if (!ok) s_abort = 1;
+        }
+    } else {
+        const int q = warp & 3;                              // TMEM lane quarter this warp may read
+        const int row = r0 + q * 32 + lane;
+        const bool row_ok = row < row1;
+        Top3 top = Top3{-INFINITY, -INFINITY, -INFINITY, 0, 0};
+        bool ok = true;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int acc = t & 1;
+            ok = tc::mbar_wait(tfull_bar(acc), (t >> 1) & 1) && !*(volatile int *)&s_abort;
+            ok = __all_sync(0xffffffffu, ok);                // the TMEM loads below need the whole warp
+            if (!ok) break;
+            tc::fence_after_sync();
+            const int c0 = t * kThBN;
+#pragma unroll 1
+            for (int b = 0; b < kThBN / 32; ++b) {
+                uint32_t v[32];
+                tc::tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * kThBN + b * 32, v);
+                tc::tmem_ld_wait();
+                const int cb = c0 + b * 32;
+                if (cb + 32 > C) {                           // the segment's last, partial batch: columns of other segments
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if (cb + e >= C) v[e] = 0xff800000u;
+                }
+                // a score enters the top three only if it beats the third: one test per four scores
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float f0 = __uint_as_float(v[4 * j]), f1 = __uint_as_float(v[4 * j + 1]);
+                    const float f2 = __uint_as_float(v[4 * j + 2]), f3 = __uint_as_float(v[4 * j + 3]);
+                    if (fmaxf(fmaxf(f0, f1), fmaxf(f2, f3)) > top.third) {
+                        top3_push(top, f0, cb + 4 * j);
+                        top3_push(top, f1, cb + 4 * j + 1);
+                        top3_push(top, f2, cb + 4 * j + 2);
+                        top3_push(top, f3, cb + 4 * j + 3);
+                    }
+                }
+            }
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tempty_bar(acc));
+        }
+        if (!ok && lane == 0) s_abort = 1;
+        if (row_ok) {
+            if (!ok) {
+                recheck[atomicAdd(n_recheck, 1)] = row;      // decided exactly by the re-check kernel
+                hash_out[row] = 0;
+            } else {
+                // the row itself is still in shared memory (the M-side tile, 128-byte swizzle: 16-byte chunk c of row m
+                // sits at chunk c ^ (m & 7) of the row's 128 bytes inside each 64-element k-block)
+                const int m = q * 32 + lane;
+                tc::mbar_wait(x_bar, 0);                     // completed long ago: orders this thread after the TMA writes
+                const unsigned char *xt = smem_dyn + (x_smem - tc::smem_addr(smem_dyn)) + m * 128;
+                auto x_chunk = [&](int e) {                  // elements e .. e + 7 of the row
+                    return *reinterpret_cast<const uint4 *>(xt + (e >> 6) * (kThBM * 128) + ((((e >> 3) & 7) ^ (m & 7)) << 4));
+                };
+                float xn2 = 0.f;
+#pragma unroll
+                for (int e = 0; e < D; e += 8) {
+                    float f[8];
+                    widen8(x_chunk(e), f, T());
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) xn2 = fmaf(f[u], f[u], xn2);
+                }
+                // Scores closer than eps to the best may beat it under the canonical order.  None: done.  Exactly one
+                // (the usual near-tie): the two are compared with the fp32 chain right here.  More: full re-check.
+                const float eps = kHashEps * sqrtf(xn2) * 1.0001f * __uint_as_float(amax[s]);
+                int choice = top.arg;
+                if (!(top.best - top.second > eps)) {
+                    if (top.best - top.third > eps) {
+                        // both canonical chains at once, the two bucket rows fetched four chunks ahead
+                        const T *a1 = A + size_t(cb0 + top.arg) * D, *a2 = A + size_t(cb0 + top.arg2) * D;
+                        float y1 = 0.f, y2 = 0.f;
+                        for (int e0 = 0; e0 < D; e0 += 32) {
+                            uint4 r1[4], r2[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                r1[u] = *reinterpret_cast<const uint4 *>(a1 + e0 + 8 * u);
+                                r2[u] = *reinterpret_cast<const uint4 *>(a2 + e0 + 8 * u);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                float fx[8], f1[8], f2[8];
+                                widen8(x_chunk(e0 + 8 * u), fx, T());
+                                widen8(r1[u], f1, T());
+                                widen8(r2[u], f2, T());
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) { y1 = fmaf(f1[k], fx[k], y1); y2 = fmaf(f2[k], fx[k], y2); }
+                            }
+                        }
+                        if (y2 > y1 || (y2 == y1 && top.arg2 < top.arg)) choice = top.arg2;
+                    } else {
+                        recheck[atomicAdd(n_recheck, 1)] = row;
+                    }
+                }
+                hash_out[row] = choice;
+            }
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tc::tmem_dealloc(tmem_base, 2 * kThBN);
 }
 
 struct HashLayout { size_t off_amax, off_count, off_list, total; };
@@ -317,14 +543,29 @@ static int launch_hash_mma(const void *x, const void *A, int64_t n_rows, int64_t
     FM_CUDA_OK(cudaMemsetAsync(ws, 0, L.off_list, st));
     a_norm_max_kernel<T><<<(unsigned)ceil_div(total_buckets, 4), 128, 0, st>>>((const T *)A, (int)total_buckets, D, n_seg, seg_cb, amax);
     FM_LAUNCHED("a_norm_max_kernel");
-    const size_t smem = 2 * size_t(kTile) * D * 2;
-    FM_CUDA_OK(cudaFuncSetAttribute(hash_rows_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((unsigned)ceil_div(max_seg_rows, kTile), (unsigned)n_seg);
-    hash_rows_mma_kernel<T, D><<<grid, kHashThreads, smem, st>>>((const T *)x, (const T *)A, (int)n_rows, (int)total_buckets,
-                                                               seg_xb, seg_cb, amax, hash_out, list, count);
-    FM_LAUNCHED("hash_rows_mma_kernel");
-    const int blocks = (int)std::min<int64_t>(ceil_div(n_rows, 4), int64_t(sm_count()) * 4);
-    hash_recheck_kernel<T><<<blocks, 128, 0, st>>>((const T *)x, (const T *)A, D, (int)n_rows, (int)total_buckets, n_seg,
+    if (n_rows >= kTcHashMinRows && (D == 64 || D == 128)) {
+        CUtensorMap tmX, tmA;
+        int rc = make_tensor_map_2d(&tmX, x, Elem<T>::id, (uint64_t)n_rows, D, (uint64_t)D * 2, kThBM);
+        if (rc != FM_OK) return rc;
+        rc = make_tensor_map_2d(&tmA, A, Elem<T>::id, (uint64_t)total_buckets, D, (uint64_t)D * 2, kThBN);
+        if (rc != FM_OK) return rc;
+        const size_t smem = size_t(D / 64) * (kThBM * 128 + kThStages * kThBN * 128) + 1024;
+        FM_CUDA_OK(cudaFuncSetAttribute(hash_rows_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dim3 grid((unsigned)ceil_div(max_seg_rows, kThBM), (unsigned)n_seg);
+        hash_rows_tc_kernel<T, D><<<grid, kThThreads, smem, st>>>(tmX, tmA, (const T *)x, (const T *)A, (int)n_rows, (int)total_buckets,
+                                                                seg_xb, seg_cb, amax, hash_out, list, count,
+                                                                tc::instr_desc_f16(Elem<T>::id == FM_BF16, kThBM, kThBN));
+        FM_LAUNCHED("hash_rows_tc_kernel");
+    } else {
+        const size_t smem = 2 * size_t(kTile) * D * 2;
+        FM_CUDA_OK(cudaFuncSetAttribute(hash_rows_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dim3 grid((unsigned)ceil_div(max_seg_rows, kTile), (unsigned)n_seg);
+        hash_rows_mma_kernel<T, D><<<grid, kHashThreads, smem, st>>>((const T *)x, (const T *)A, (int)n_rows, (int)total_buckets,
+                                                                   seg_xb, seg_cb, amax, hash_out, list, count);
+        FM_LAUNCHED("hash_rows_mma_kernel");
+    }
+    const int blocks = (int)std::min<int64_t>(n_rows, int64_t(sm_count()) * 4);
+    hash_recheck_kernel<T><<<blocks, kRecheckThreads, 0, st>>>((const T *)x, (const T *)A, D, (int)n_rows, (int)total_buckets, n_seg,
                                                   seg_xb, seg_cb, list, count, hash_out);
     FM_LAUNCHED("hash_recheck_kernel");
     return FM_OK;
