@@ -32,6 +32,7 @@ struct AttnParams {
     int *counters;                         // [0] = number of items, [1] = next item to hand out
     int4 *items;                           // {bucket, first query position, key chunk, chunks of the bucket}
     int max_items;
+    int q_block;                            // queries per work item: 16 (CUDA-core kernel) or 32 (tensor-core kernel)
     int32_t *qparts;                       // per query position: number of partials to combine
     float *partials;                       // [query position][chunk][d + 2]
 };

@@ -25,12 +25,12 @@ __global__ void attn_plan_kernel(AttnParams p)
     if (nq <= 0) return;
     int64_t len = p.bucket_off[b + 1] - p.bucket_off[b];
     int nkc = len > 0 ? int((len + p.key_chunk - 1) / p.key_chunk) : 1;
-    int nqb = (nq + kQB - 1) / kQB;
+    int nqb = (nq + p.q_block - 1) / p.q_block;
     int base = atomicAdd(&p.counters[0], nqb * nkc);
     for (int qb = 0; qb < nqb; ++qb)
         for (int kc = 0; kc < nkc; ++kc) {
             int id = base + qb * nkc + kc;
-            if (id < p.max_items) p.items[id] = make_int4(b, q0 + qb * kQB, kc, nkc);
+            if (id < p.max_items) p.items[id] = make_int4(b, q0 + qb * p.q_block, kc, nkc);
         }
 }
 
@@ -347,14 +347,16 @@ extern "C" int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, i
     p.qparts = (int32_t *)(ws + L.off_qparts);
     p.partials = (float *)(ws + L.off_partials);
 
+    // the tensor-core kernel tracks the row maximum before scaling, which needs a positive scale
+    const bool use_mma = attn_mma_supported(dtype, d) && sm_scale > 0.f;
+    p.q_block = use_mma ? 32 : kQB;
+
     FM_CUDA_OK(cudaMemsetAsync(p.counters, 0, 8, st));
     if (L.nkc_max > 1) FM_CUDA_OK(cudaMemsetAsync(p.qparts, 0, size_t(n_q_rows) * 4, st));
     attn_plan_kernel<<<(unsigned)ceil_div(total_buckets, 256), 256, 0, st>>>(p);
     FM_LAUNCHED("attn_plan_kernel");
 
     int rc;
-    // the tensor-core kernel tracks the row maximum before scaling, which needs a positive scale
-    const bool use_mma = attn_mma_supported(dtype, d) && sm_scale > 0.f;
     int grid = (int)std::min<int64_t>(L.max_items, int64_t(sms) * (use_mma ? 2 : 4));
     if (use_mma) rc = launch_attn_mma(p, dtype, d, grid, st);
     else if (dtype == FM_F32) rc = dispatch_simt<float>(p, d, grid, st);
