@@ -21,6 +21,7 @@
 #include "topz_row.cuh"
 
 #include <cmath>
+#include <mutex>
 #include <vector>
 
 namespace fm {
@@ -785,6 +786,23 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
     return P;
 }
 
+// One extra stream per device for work that may run beside the main sequence of a build (nullptr if it cannot be made:
+// the work then stays on the caller's stream).
+static cudaStream_t side_stream()
+{
+    static std::mutex mu;
+    static cudaStream_t tab[64] = {};
+    static bool tried[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!tried[dev]) {
+        tried[dev] = true;
+        if (cudaStreamCreateWithFlags(&tab[dev], cudaStreamNonBlocking) != cudaSuccess) { tab[dev] = nullptr; cudaGetLastError(); }
+    }
+    return tab[dev];
+}
+
 // Builds the table rows of the listed segments.  status word (ws + 0): 0 = ok, 1-3 = a tensor-core pipeline
 // wait gave up, 4 = more buckets needed the fallback than it can take.
 template <typename T>
@@ -838,8 +856,19 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         uint2 *cand_mask = (uint2 *)(ws + P.off_mask);
         float *Yf = (float *)(ws + P.off_yf);
 
-        key_norm_max_kernel<T><<<dim3(std::max(1, 8 * sm_count() / ng), ng), 256, 0, st>>>((const T *)K, d, dsegs);
+        // The key norms are only needed by the selection: they are taken on a second stream, under the sample pass and
+        // the threshold selection (which leave most of the memory bandwidth idle), and joined before the selection.
+        cudaStream_t side = side_stream();
+        cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+        if (side) {
+            FM_CUDA_OK(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+            FM_CUDA_OK(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+            FM_CUDA_OK(cudaEventRecord(ev_fork, st));
+            FM_CUDA_OK(cudaStreamWaitEvent(side, ev_fork, 0));
+        }
+        key_norm_max_kernel<T><<<dim3(std::max(1, 8 * sm_count() / ng), ng), 256, 0, side ? side : st>>>((const T *)K, d, dsegs);
         FM_LAUNCHED("key_norm_max_kernel");
+        if (side) FM_CUDA_OK(cudaEventRecord(ev_join, side));
 
         const int sms = sm_count();
         TcParams tp = {};
@@ -866,6 +895,11 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         rc = tc_project_launch(tmA, tmK, tp, int(mtiles) * tp.n_ranges, d, false, dtype == FM_BF16, st);
         if (rc != FM_OK) return rc;
 
+        if (side) {
+            FM_CUDA_OK(cudaStreamWaitEvent(st, ev_join, 0));
+            cudaEventDestroy(ev_fork);                       // released once the work that uses them has run
+            cudaEventDestroy(ev_join);
+        }
         SelParams sp = {dsegs, ng, tp.n_ranges, P.cap, cand, cand_mask, P.group_buckets, counts, tau, A, K, d, table, fail_count, fail_list};
         {
             const size_t dyn = size_t(P.cap) * 8;
