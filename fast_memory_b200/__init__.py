@@ -4,11 +4,12 @@ The operators run in an in-tree CUDA library (``libfastmem_b200.so``, C ABI in `
 build it with ``python -m fast_memory_b200.build``.  There is no CPU or PyTorch fallback.
 """
 from ._lib import FastMemError, launch_count
-from .memory import Memory, kmeans_projection, merge
+from .memory import Memory, compute_centroids, kmeans_projection, merge
 from .ops import (attention_hash, attention_hash_varlen, group_rows, hash_rows, hashed_attention, lse_merge, project,
                   ring_attention_masked_forward, shard_filter, topz_select, unit_rows, update_out_and_lse)
 
 __all__ = [
+    "compute_centroids",
     "FastMemError", "Memory", "attention_hash", "attention_hash_varlen", "group_rows", "hash_rows", "hashed_attention",
     "kmeans_projection", "launch_count", "lse_merge", "merge", "project", "ring_attention_masked_forward", "shard_filter",
     "topz_select", "unit_rows", "update_out_and_lse",

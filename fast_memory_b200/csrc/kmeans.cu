@@ -173,6 +173,33 @@ extern "C" int fm_kmeans(const void *X, int dtype, int d, int n_seg, const int64
     }
 }
 
+namespace fm {
+// out[i, :] = mean_j U[rows[i * per_out + j], :], one CTA per output row (the rows are scattered: every thread owns a
+// few columns and walks the row list).
+__global__ void __launch_bounds__(128)
+gather_mean_kernel(const float *__restrict__ U, int d, const int32_t *__restrict__ rows, int per_out, float *__restrict__ out)
+{
+    const int32_t *list = rows + size_t(blockIdx.x) * per_out;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < per_out; ++j) acc += U[size_t(list[j]) * d + c];
+        out[size_t(blockIdx.x) * d + c] = acc / float(per_out);
+    }
+}
+}  // namespace fm
+
+extern "C" int fm_gather_mean(const float *U, int64_t n_rows, int d, const int32_t *rows, int64_t n_out, int64_t per_out, float *out,
+                              fm_stream_t stream)
+{
+    using namespace fm;
+    FM_REQUIRE(U && rows && out && n_rows > 0 && d > 0 && n_out >= 0 && per_out > 0, "fm_gather_mean: bad argument");
+    FM_REQUIRE(per_out < (int64_t(1) << 31) && n_out < (int64_t(1) << 31), "fm_gather_mean: sizes exceed int32");
+    if (n_out == 0) return FM_OK;
+    gather_mean_kernel<<<(unsigned)n_out, 128, 0, (cudaStream_t)stream>>>(U, d, rows, (int)per_out, out);
+    FM_LAUNCHED("gather_mean_kernel");
+    return FM_OK;
+}
+
 extern "C" int fm_unit_rows(const void *X, int dtype, int64_t n_rows, int d, float *U, fm_stream_t stream)
 {
     using namespace fm;

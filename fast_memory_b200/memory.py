@@ -55,6 +55,36 @@ def kmeans_projection(x: torch.Tensor, init: torch.Tensor, iters: int, seg_xb: S
     return A, cent
 
 
+def compute_centroids(kq: torch.Tensor, centroids: torch.Tensor, n_hashes: int, n_groups: int,
+                      centroid_topk: int) -> torch.Tensor:
+    """The projection-matrix construction of the reference's CODE (``compute_centroids``, mem:209-231; its README
+    describes k-means instead, see :func:`kmeans_projection`): rows are put on the unit sphere (in ``kq``'s dtype, as
+    mem:215-217 divides there), every centroid takes its ``centroid_topk`` nearest rows in each head, and the rows of
+    the ``n_groups`` heads that share a KV head are averaged.
+
+    ``kq`` ``[n_heads, ctx, d]``, ``centroids`` ``[n_hashes, d]`` -> ``[n_hashes, n_heads // n_groups, d]`` in ``kq``'s
+    dtype.  The top-k runs on the index-build kernels (a table with ``Z = centroid_topk``; exact fp32 ranking, lower row
+    wins a tie), the gather + mean in ``fm_gather_mean``."""
+    dev = L.require_cuda(kq, centroids)
+    H, ctx, d = kq.shape
+    if H % n_groups or centroids.shape != (n_hashes, d):
+        raise ValueError("compute_centroids: n_heads must be a multiple of n_groups and centroids [n_hashes, d]")
+    if centroid_topk > ctx:
+        raise ValueError("compute_centroids: centroid_topk exceeds the context length")
+    k_heads = H // n_groups
+    U = ops.unit_rows(kq.contiguous())                                   # fp32 [H, ctx, d]
+    x = U.to(kq.dtype)
+    A = centroids.to(kq.dtype).unsqueeze(0).expand(H, n_hashes, d).contiguous()
+    mem = Memory.build(x, x, A=A, bucket_size=centroid_topk)
+    # table rows of (head h, centroid z) -> the lists of (z, kv head): its n_groups heads back to back
+    t = mem.table.reshape(k_heads, n_groups, n_hashes, centroid_topk).permute(2, 0, 1, 3).contiguous()
+    xf = x.reshape(H * ctx, d) if x.dtype == torch.float32 else x.reshape(H * ctx, d).float()
+    out = torch.empty(n_hashes * k_heads, d, dtype=torch.float32, device=dev)
+    L.check(L.lib().fm_gather_mean(L.ptr(xf), xf.shape[0], d, L.ptr(t), out.shape[0], n_groups * centroid_topk, L.ptr(out),
+                                   L.stream_ptr(dev)), "fm_gather_mean")
+    return out.reshape(n_hashes, k_heads, d).to(kq.dtype)
+
+
 class Memory:
     """An indexed set of keys/values.  Create with :meth:`build`."""
 

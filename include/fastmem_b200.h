@@ -206,6 +206,12 @@ int fm_kmeans(const void *X, int dtype, int d, int n_seg, const int64_t *seg_xb,
 /* U[r, :] = X[r, :] / max(||X[r, :]||, 1e-6) in fp32 (unit-sphere projection, README.md:39; mem:215-217). */
 int fm_unit_rows(const void *X, int dtype, int64_t n_rows, int d, float *U, fm_stream_t stream);
 
+/* out[i, :] = mean over j < per_out of U[rows[i * per_out + j], :] (fp32, summed in list order): the averaging step of
+ * the reference's coded centroid construction (gather + mean, mem:222-229).  U [n_rows, d]; rows hold indices in
+ * [0, n_rows); out [n_out, d]. */
+int fm_gather_mean(const float *U, int64_t n_rows, int d, const int32_t *rows, int64_t n_out, int64_t per_out, float *out,
+                   fm_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,4 +1,6 @@
 """GPU parity of index build, query hashing, k-means and the Memory object against the CPU oracle."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -313,3 +315,22 @@ def test_state_dict_round_trip():
     m2 = fm.Memory.from_state_dict(mem.state_dict(), k.to(DEV), v.to(DEV))
     a, b = mem.query(q.to(DEV), 0.2), m2.query(q.to(DEV), 0.2)
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_compute_centroids_code_variant(golden_dir):
+    """mem:209-231 on the GPU path against the reference's own output (golden) and the oracle on a larger case."""
+    z = np.load(os.path.join(golden_dir, "compute_centroids.npz"))
+    kq, cent = torch.from_numpy(z["kq"]), torch.from_numpy(z["centroids"])
+    out = fm.compute_centroids(kq.to(DEV), cent.to(DEV), cent.shape[0], int(z["n_groups"]), int(z["centroid_topk"]))
+    assert out.shape == z["out"].shape
+    assert (out.cpu().float() - torch.from_numpy(z["out"])).abs().max() <= 2e-6
+    # larger, grouped heads, fp32 and bf16 (the unit rows are rounded to the input dtype first, as the reference does)
+    g = torch.Generator().manual_seed(9)
+    for dtype, tol in ((torch.float32, 2e-6), (torch.bfloat16, 1e-2)):
+        kq = torch.randn(8, 5000, 64, generator=g).to(dtype)
+        cent = torch.nn.functional.normalize(torch.randn(48, 64, generator=g), dim=-1).to(dtype)
+        out = fm.compute_centroids(kq.to(DEV), cent.to(DEV), 48, 4, 96)
+        x = fm.unit_rows(kq.to(DEV)).to(dtype).cpu()                     # what the top-k ranks
+        ref = O.compute_centroids(x, cent, 48, 4, 96)
+        assert out.shape == (48, 2, 64) and out.dtype == dtype
+        assert (out.cpu().float() - ref).abs().max() <= tol
