@@ -1,6 +1,6 @@
 """Benchmark of the LSH attention-memory hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg1|cfg3|cfg4|cfg5] [--impl ours|reference]
 
 One "step" = one pass of the query path over one batch of synthetic queries: query hashing, grouping by
 bucket, hashed attention over the indexed memory and (where the workload has a local window) the LSE merge
@@ -287,6 +287,133 @@ def run_ours(args, rank, world):
     return res
 
 
+def run_varlen(args, rank, world):
+    """cfg4: packed variable-length memories (16 sequences of 16 Ki .. 256 Ki keys per head, per-sequence C and Z,
+    1024 queries per sequence through cu_seqlens).  One memory per rank (weak scaling, no collective)."""
+    import fast_memory_b200 as fm
+    from fast_memory_b200 import ops, synth
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    cfg = synth.config("cfg4")
+    if args.kv_heads:
+        cfg.kv_heads = args.kv_heads
+    sm_scale = cfg.d ** -0.5
+    q, k, v, cu_q, cu_k = synth.make_varlen(cfg, seed=args.seed + rank, device=dev)
+    H, N_total, d = k.shape
+    S_total = q.shape[1]
+    n_queries = H * S_total
+    Cs = [synth.varlen_buckets(n) for n in cfg.seq_keys]
+    Zs = [synth.varlen_bucket_size(n) for n in cfg.seq_keys]
+    mem = fm.Memory.build(k, v, n_buckets=Cs, bucket_size=Zs, kmeans_iters=1, cu_seqlens_k=cu_k)     # k-means A once
+    A = mem.A
+    build_ms = []
+    for it in range(args.build_steps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        mem = fm.Memory.build(k, v, n_buckets=Cs, bucket_size=Zs, A=A, cu_seqlens_k=cu_k, check=False)
+        e1.record()
+        torch.cuda.synchronize()
+        mem.check_build()
+        if it > 0 or args.build_steps == 0:
+            build_ms.append(e0.elapsed_time(e1))
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    with ClockSampler(dev.index or 0) as clocks:
+        for _ in range(args.warmup):
+            mem.query(q, sm_scale, cu_seqlens_q=cu_q)
+        barrier()
+        launches0 = fm.launch_count()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            mem.query(q, sm_scale, cu_seqlens_q=cu_q)
+        t1.record()
+        barrier()
+        step_ms = t0.elapsed_time(t1) / args.steps
+    launches = fm.launch_count() - launches0
+
+    # the attention launch alone
+    qf = q.reshape(-1, d)
+    seg_xb, max_rows = mem._query_segments(H, S_total, cu_q, dev)
+    hashes = ops.hash_rows(qf, mem.A, seg_xb, mem._seg_cb_dev, max_rows)
+    group_off, perm = ops.group_rows(hashes, mem.total_buckets, seg_xb, mem._seg_cb_dev)
+    o_buf, l_buf = torch.empty_like(qf), torch.empty(qf.shape[0], dtype=torch.float32, device=dev)
+    kk, vv = k.reshape(-1, d), v.reshape(-1, d)
+    attn = lambda: ops.hashed_attention(qf, kk, vv, mem.table, mem.bucket_off, group_off, perm, sm_scale,
+                                        mem.max_bucket_len, out=o_buf, lse=l_buf)
+    for _ in range(3):
+        attn()
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for _ in range(args.steps):
+        attn()
+    a1.record()
+    torch.cuda.synchronize()
+    attn_ms = a0.elapsed_time(a1) / args.steps
+    attn_bytes, n_groups = algorithmic_attention_bytes(mem, group_off, d, 2)
+
+    # end to end: pinned host queries in, O and LSE out (packed memories are served by one call; no slicing)
+    q_host = q.cpu().pin_memory()
+    o_host = torch.empty(H, S_total, d, dtype=cfg.dtype).pin_memory()
+    l_host = torch.empty(H, S_total, dtype=torch.float32).pin_memory()
+    q_dev = torch.empty_like(q)
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        o, lse = mem.query(q_dev, sm_scale, cu_seqlens_q=cu_q)
+        o_host.copy_(o, non_blocking=True)
+        l_host.copy_(lse, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+
+    build_med = statistics.median(build_ms)
+    if world > 1:
+        t = torch.tensor([step_ms, e2e_ms, build_med], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        step_ms, e2e_ms, build_med = t.tolist()
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+    build_flops = sum(2.0 * c * n * d for c, n in zip(Cs, cfg.seq_keys)) * H
+    return {
+        "metric": METRIC, "value": world * n_queries / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": ("CUT-DOWN " if args.kv_heads else "") + f"cfg4: {H} heads x {len(cfg.seq_keys)} packed sequences of "
+                               f"{min(cfg.seq_keys)}..{max(cfg.seq_keys)} keys ({N_total} per head), d={d}, C=round(N^0.5) to 16 "
+                               f"({min(Cs)}..{max(Cs)}), Z=round(N^0.7) ({min(Zs)}..{max(Zs)}), {cfg.n_queries} queries per sequence",
+                   "parallelism": f"independent memories per GPU x{world}" if world > 1 else "single GPU",
+                   "l2": f"inputs larger than L2 ({attn_bytes / 1e9:.2f} GB gathered per step)", "non_empty_groups": n_groups},
+        "clocks": clocks.summary(),
+        "e2e": {"value": world * n_queries / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": o_host.numel() * 2 + l_host.numel() * 4,
+                "pipeline": "copy in, Memory.query with cu_seqlens, copy out, one stream"},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "hashed attention forward", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "traffic": None,
+                     "algorithmic_bytes": attn_bytes, "ms_per_launch": attn_ms},
+        "index_build": {"metric": "index_build_keys_per_s", "value": world * H * N_total / (build_med * 1e-3), "unit": "keys/s",
+                        "ms": build_med, "tflops": build_flops / (build_med * 1e-3) / 1e12,
+                        "frac_of_tensor_peak": build_flops / (build_med * 1e-3) / 1e12 / peaks["bf16_tflops"]},
+    }
+
+
 def run_ring(args, rank, world):
     """cfg5: keys sharded over the sequence into 8 logical shards (fixed, so the result does not depend on the
     GPU count), every rank indexes its own shards, all queries attend everywhere, partial (O, LSE) are merged
@@ -519,7 +646,7 @@ def main():
     else:
         if world > 1:
             torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
-        res = run_ring(args, rank, world) if args.workload == "cfg5" else run_ours(args, rank, world)
+        res = (run_ring if args.workload == "cfg5" else run_varlen if args.workload == "cfg4" else run_ours)(args, rank, world)
         if world > 1:
             torch.distributed.destroy_process_group()
     if res is not None:
