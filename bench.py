@@ -467,13 +467,13 @@ def run_ring(args, rank, world):
 
     with ClockSampler(dev.index or 0) as clocks:             # samples span the warm-up and the timed region (both under load)
         for _ in range(args.warmup):
-            mem.query(q, sm_scale)
+            mem.query(q, sm_scale, exchange=args.exchange)
         barrier()
         launches0 = fm.launch_count()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         for _ in range(args.steps):
-            mem.query(q, sm_scale)
+            mem.query(q, sm_scale, exchange=args.exchange)
         t1.record()
         barrier()
         step_ms = t0.elapsed_time(t1) / args.steps
@@ -500,7 +500,7 @@ def run_ring(args, rank, world):
 
     def e2e_step():
         q_dev.copy_(q_host, non_blocking=True)
-        o, lse = mem.query(q_dev, sm_scale)
+        o, lse = mem.query(q_dev, sm_scale, exchange=args.exchange)
         if rank == 0:
             o_host.copy_(o, non_blocking=True)
             l_host.copy_(lse, non_blocking=True)
@@ -626,6 +626,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--exchange", default="ring", choices=["ring", "allreduce"],
+                    help="cfg5: how the ranks' partial (O, LSE) are merged (ring of send/recv + merge steps, or MAX + SUM all-reduce)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--build-steps", type=int, default=2)
     ap.add_argument("--cpu-seconds", type=float, default=15.0)

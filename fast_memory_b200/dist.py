@@ -100,6 +100,30 @@ def ring_reduce_scatter_partials(out: torch.Tensor, lse: torch.Tensor, group: Op
     return out[own * n:(own + 1) * n], lse[own * n:(own + 1) * n], own
 
 
+def allreduce_merge_partials(o: torch.Tensor, lse: torch.Tensor, group: Optional[dist.ProcessGroup] = None
+                             ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The same merge as a sum: with M = the maximum LSE of a row over the ranks (one MAX all-reduce of the LSEs), the
+    complete result is ``sum_r w_r o_r / sum_r w_r`` and ``M + log sum_r w_r`` with ``w_r = exp(lse_r - M)``, so one
+    SUM all-reduce of ``[w o | w]`` finishes the job and the library is free to use its fastest algorithm (in-switch
+    reduction on NVSwitch) instead of W - 1 dependent send/recv + merge steps.
+
+    ``o`` ``[rows, d]`` (any float dtype) and ``lse`` fp32 ``[rows]``: this rank's partial result over its keys for all
+    queries.  Returns fp32 ``(out [rows, d], lse [rows])``, complete and identical on every rank; rows no rank has a
+    key for come back as zeros and ``-inf``."""
+    rows, d = o.shape
+    M = lse.clone()
+    dist.all_reduce(M, op=dist.ReduceOp.MAX, group=group)
+    M = torch.where(torch.isinf(M), torch.zeros_like(M), M)              # all ranks empty: any finite shift
+    acc = torch.empty(rows, d + 1, dtype=torch.float32, device=o.device)
+    w = torch.exp(lse - M)                                               # exp(-inf) = 0 for a rank without keys
+    torch.mul(o, w[:, None], out=acc[:, :d]) if o.dtype == torch.float32 else acc[:, :d].copy_(o.float() * w[:, None])
+    acc[:, d] = w
+    dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=group)
+    den = acc[:, d]
+    out = acc[:, :d] / den.clamp_min(torch.finfo(torch.float32).tiny)[:, None]
+    return out, M + torch.log(den)
+
+
 def all_gather_chunks(chunk: torch.Tensor, own: int, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """Rank r contributes the chunk it owns (index ``own = (r + 1) % W``); returns all chunks in row order."""
     W = dist.get_world_size(group)
@@ -166,16 +190,27 @@ class ShardedMemory:
         """This rank's partial result over its own shards: o in q's dtype, fp32 lse."""
         return self.local.query(q, sm_scale)
 
-    def query(self, q: torch.Tensor, sm_scale: float, gather: bool = True, merge_fn: MergeFn = _default_merge
-              ) -> Tuple[torch.Tensor, torch.Tensor]:
+    def query(self, q: torch.Tensor, sm_scale: float, gather: bool = True, merge_fn: MergeFn = _default_merge,
+              exchange: str = "ring") -> Tuple[torch.Tensor, torch.Tensor]:
         """q ``[Hq, S, d]``, the same on every rank.  Returns fp32 ``(out [Hq, S, d], lse [Hq, S])`` over all
-        shards of all ranks (``gather=False``: only the rows this rank ends up owning, plus their range)."""
+        shards of all ranks (``gather=False``: only the rows this rank ends up owning, plus their range).
+
+        ``exchange="ring"``: the partial results go around the ring (send/recv + merge per step, then an all-gather),
+        as the reference moves its blocks (mem:307-338).  ``exchange="allreduce"``: the merge written as one MAX and
+        one SUM all-reduce (:func:`allreduce_merge_partials`)."""
         Hq, S, d = q.shape
         o, lse = self.local.query(q, sm_scale)
         W = dist.get_world_size(self.group) if dist.is_initialized() else 1
         rows = Hq * S
         if W == 1:
             return o.float(), lse
+        if exchange == "allreduce":
+            if not gather:
+                raise ValueError("exchange='allreduce' returns the complete result on every rank")
+            out, l = allreduce_merge_partials(o.reshape(rows, d), lse.reshape(rows), self.group)
+            return out.reshape(Hq, S, d), l.reshape(Hq, S)
+        if exchange != "ring":
+            raise ValueError(f"unknown exchange {exchange!r}")
         pad = (-rows) % W
         out = torch.empty(rows + pad, d, dtype=torch.float32, device=q.device)
         out[:rows].copy_(o.reshape(rows, d))

@@ -60,7 +60,9 @@ def _rank_main(rank, world, port, n_shards, H, L, S, C, Z, result):
     dev = f"cuda:{rank}"
     mem = ShardedMemory.build(k[:, lo:hi].contiguous().to(dev), v[:, lo:hi].contiguous().to(dev), L, A=A.to(dev), bucket_size=Z)
     o, lse = mem.query(q.to(dev), cfg.d ** -0.5)
+    o2, lse2 = mem.query(q.to(dev), cfg.d ** -0.5, exchange="allreduce")
     torch.cuda.synchronize()
+    assert (o2 - o).abs().max() <= 1e-4 and (lse2 - lse).abs().max() <= 1e-4       # two ways to merge the same partials
     if rank == 0:
         result["o"], result["lse"] = o.cpu(), lse.cpu()
     dist.destroy_process_group()

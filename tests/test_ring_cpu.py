@@ -46,6 +46,12 @@ def _worker(rank, world, port, rows, d, result):
     full_l = fmd.all_gather_chunks(lc, own)
     if rank == 0:
         result["o"], result["l"] = full_o, full_l
+    # the same merge written as a MAX and a SUM all-reduce
+    ao, al = fmd.allreduce_merge_partials(o.clone(), l.clone())
+    fin = torch.isfinite(full_l)
+    assert torch.equal(torch.isfinite(al), fin)
+    assert torch.allclose(al[fin], full_l[fin], atol=1e-5) and torch.allclose(ao[fin], full_o[fin], atol=1e-5)
+    assert (ao[~fin] == 0).all()
     # SendRecv misuse raises like the reference (mem:39-40, 45-46)
     c = fmd.SendRecv()
     with pytest.raises(RuntimeError, match="Wait called before commit"):
