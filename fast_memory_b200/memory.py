@@ -17,6 +17,8 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence, Tuple, Union
 
+import warnings
+
 import numpy as np
 import torch
 
@@ -105,7 +107,8 @@ class Memory:
     def build(cls, k: torch.Tensor, v: torch.Tensor, *, n_buckets: Optional[IntOrSeq] = None,
               bucket_size: IntOrSeq, A: Optional[torch.Tensor] = None, kmeans_iters: int = 2,
               kmeans_init: Optional[torch.Tensor] = None, cu_seqlens_k: Optional[Sequence[int]] = None,
-              key_range: Optional[Tuple[int, int]] = None, check: bool = True, exact_only: bool = False) -> "Memory":
+              key_range: Optional[Tuple[int, int]] = None, check: bool = True, exact_only: bool = False,
+              fallback_exact: bool = True) -> "Memory":
         """Index ``k`` / ``v``.
 
         :param k, v: ``[H, N, d]`` (or ``[H, N_total, d]`` with ``cu_seqlens_k``)
@@ -119,6 +122,9 @@ class Memory:
         :param check: read the build's status word back (one device sync) and raise if the tensor-core path
             gave up; pass False to stay asynchronous and call :meth:`check_build` later
         :param exact_only: score every key with the fp32 chain instead of the tensor-core filter
+        :param fallback_exact: with ``check``, when the tensor-core filter reports that too many buckets need the exact
+            fallback (status 4: masses of equal scores, key order far from stationary) the table is rebuilt with
+            ``exact_only`` and a warning instead of raising
         :param key_range: keep only table entries whose per-head key index lies in ``[lo, hi)`` (the
             filter the reference hard-codes at tk:283); uniform memories only
         """
@@ -187,9 +193,12 @@ class Memory:
         flags = 1 if exact_only else 0
         need = L.lib().fm_index_build_workspace_bytes(n_seg, kb, cb, zz, d, L.dtype_id(k.dtype), flags)
         ws = ops._ws.get("build", need, dev)
-        L.check(L.lib().fm_index_build(L.ptr(kf), L.ptr(A2), L.dtype_id(k.dtype), d, n_seg, kb, cb, zz, to,
-                                       L.ptr(table), flags, L.ptr(ws), ws.numel(), L.stream_ptr(dev)), "fm_index_build")
-        self.build_status = ws[:4].view(torch.int32)[0].clone()  # device scalar: 0 = ok (see check_build)
+        def launch(fl):
+            L.check(L.lib().fm_index_build(L.ptr(kf), L.ptr(A2), L.dtype_id(k.dtype), d, n_seg, kb, cb, zz, to,
+                                           L.ptr(table), fl, L.ptr(ws), ws.numel(), L.stream_ptr(dev)), "fm_index_build")
+            return ws[:4].view(torch.int32)[0].clone()           # device scalar: 0 = ok (see check_build)
+
+        self.build_status = launch(flags)
         self.table = table
         # the host-side prefix arrays are made while the device builds the table
         bucket_off = np.zeros(total_c + 1, dtype=np.int64)
@@ -198,6 +207,12 @@ class Memory:
         self.max_bucket_len = int(seg_zc.max()) if total_c else 0
         self._seg_cb_dev = torch.tensor(seg_cb, dtype=torch.int32).to(dev, non_blocking=True)
         if check:
+            if fallback_exact and not exact_only and int(self.build_status.item()) == 4:
+                warnings.warn("index build: the tensor-core filter handed too many buckets to its fallback; "
+                              "rebuilding the table with the exact fp32 path", RuntimeWarning)
+                need_exact = L.lib().fm_index_build_workspace_bytes(n_seg, kb, cb, zz, d, L.dtype_id(k.dtype), 1)
+                ws = ops._ws.get("build", need_exact, dev)
+                self.build_status = launch(1)
             self.check_build()
         if key_range is not None:
             self._apply_key_range(key_range)

@@ -202,7 +202,11 @@ def test_fused_build_with_massive_ties_uses_the_fallback():
     # with more such buckets than the fallback takes, the build reports it and the exact path still works
     A2 = torch.randn(1, 128, d, generator=g).bfloat16()
     with pytest.raises(fm.FastMemError):
-        fm.Memory.build(k.to(DEV), k.to(DEV), A=A2.to(DEV), bucket_size=Z)
+        fm.Memory.build(k.to(DEV), k.to(DEV), A=A2.to(DEV), bucket_size=Z, fallback_exact=False)
+    with pytest.warns(RuntimeWarning, match="exact fp32 path"):
+        mem2 = fm.Memory.build(k.to(DEV), k.to(DEV), A=A2.to(DEV), bucket_size=Z)        # rebuilds by itself
+    ok, why = tables_equal_as_sets(mem2.table_of(0).cpu().numpy(), O.topz(O.project(A2[0], k[0]), Z))
+    assert ok, why
     mem2 = fm.Memory.build(k.to(DEV), k.to(DEV), A=A2.to(DEV), bucket_size=Z, exact_only=True)
     ok, why = tables_equal_as_sets(mem2.table_of(0).cpu().numpy(), O.topz(O.project(A2[0], k[0]), Z))
     assert ok, why
