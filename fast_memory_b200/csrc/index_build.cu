@@ -176,7 +176,7 @@ extern "C" int fm_index_build(const void *K, const void *A, int dtype, int d, in
     if (!F.seg.empty()) {
         FM_REQUIRE(((uintptr_t)K | (uintptr_t)A) % 16 == 0, "fm_index_build: K and A must be 16-byte aligned");
         rc = fused_index_build(K, A, dtype, d, seg_kb[n_seg], seg_cb[n_seg], (int)F.seg.size(), F.kb.data(), F.nk.data(),
-                               F.cb.data(), F.nbk.data(), F.zc.data(), F.toff.data(), table, workspace, st);
+                               F.cb.data(), F.nbk.data(), F.zc.data(), F.toff.data(), table, workspace, (flags & FM_BUILD_SINGLE_RANGE) != 0, st);
         if (rc != FM_OK) return rc;
     }
     float *Y = (float *)((char *)workspace + 256);

@@ -808,7 +808,7 @@ static cudaStream_t side_stream()
 template <typename T>
 static int fused_build_impl(const void *K, const void *A, int d, int64_t total_key_rows, int64_t total_buckets, int n,
                             const int64_t *kb, const int64_t *nk, const int64_t *cb, const int64_t *nbk, const int64_t *zc,
-                            const int64_t *table_off, int32_t *table, char *ws, cudaStream_t st)
+                            const int64_t *table_off, int32_t *table, char *ws, bool single_range, cudaStream_t st)
 {
     const int dtype = Elem<T>::id;
     FusedPlan P = fused_plan(n, nk, nbk, zc);
@@ -890,7 +890,7 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         {
             int64_t min_tiles = INT64_MAX;
             for (int i = g0; i < g1; ++i) min_tiles = std::min(min_tiles, ceil_div(nk[i], kTcBN));
-            tp.n_ranges = choose_ranges(mtiles, min_tiles, sms);
+            tp.n_ranges = single_range ? 1 : choose_ranges(mtiles, min_tiles, sms);
         }
         rc = tc_project_launch(tmA, tmK, tp, int(mtiles) * tp.n_ranges, d, false, dtype == FM_BF16, st);
         if (rc != FM_OK) return rc;
@@ -921,11 +921,11 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
 
 int fused_index_build(const void *K, const void *A, int dtype, int d, int64_t total_key_rows, int64_t total_buckets, int n,
                       const int64_t *kb, const int64_t *nk, const int64_t *cb, const int64_t *nbk, const int64_t *zc,
-                      const int64_t *table_off, int32_t *table, void *ws, cudaStream_t st)
+                      const int64_t *table_off, int32_t *table, void *ws, bool single_range, cudaStream_t st)
 {
     if (dtype == FM_BF16)
-        return fused_build_impl<__nv_bfloat16>(K, A, d, total_key_rows, total_buckets, n, kb, nk, cb, nbk, zc, table_off, table, (char *)ws, st);
-    return fused_build_impl<__half>(K, A, d, total_key_rows, total_buckets, n, kb, nk, cb, nbk, zc, table_off, table, (char *)ws, st);
+        return fused_build_impl<__nv_bfloat16>(K, A, d, total_key_rows, total_buckets, n, kb, nk, cb, nbk, zc, table_off, table, (char *)ws, single_range, st);
+    return fused_build_impl<__half>(K, A, d, total_key_rows, total_buckets, n, kb, nk, cb, nbk, zc, table_off, table, (char *)ws, single_range, st);
 }
 
 }  // namespace fm

@@ -23,6 +23,6 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
 // Table rows of the listed segments; status word at ws + 0 (0 = ok).
 int fused_index_build(const void *K, const void *A, int dtype, int d, int64_t total_key_rows, int64_t total_buckets, int n,
                       const int64_t *kb, const int64_t *nk, const int64_t *cb, const int64_t *nbk, const int64_t *zc,
-                      const int64_t *table_off, int32_t *table, void *ws, cudaStream_t st);
+                      const int64_t *table_off, int32_t *table, void *ws, bool single_range, cudaStream_t st);
 
 }  // namespace fm

@@ -208,6 +208,10 @@ class Memory:
         self._seg_cb_dev = torch.tensor(seg_cb, dtype=torch.int32).to(dev, non_blocking=True)
         if check:
             if fallback_exact and not exact_only and int(self.build_status.item()) == 4:
+                # first with one candidate buffer per bucket (key positions far from stationary overflow the per-range
+                # buffers), then without the filter
+                self.build_status = launch(2)
+            if fallback_exact and not exact_only and int(self.build_status.item()) == 4:
                 warnings.warn("index build: the tensor-core filter handed too many buckets to its fallback; "
                               "rebuilding the table with the exact fp32 path", RuntimeWarning)
                 need_exact = L.lib().fm_index_build_workspace_bytes(n_seg, kb, cb, zz, d, L.dtype_id(k.dtype), 1)

@@ -184,6 +184,8 @@ int fm_topz_select(const float *Y, int64_t n_rows, int64_t N, int64_t ldy, int64
  * table + table_off[s] + (b - seg_cb[s]) * min(seg_z[s], N_s)  (table_off: HOST, n_seg entries).
  * ------------------------------------------------------------------------------------------- */
 #define FM_BUILD_EXACT_ONLY 1 /* flags: skip the tensor-core path, score every key with the fp32 chain */
+#define FM_BUILD_SINGLE_RANGE 2 /* flags: tensor-core path with ONE key range per bucket tile: a bucket's candidate list is one
+                                  buffer whatever the positions of its keys (slower when bucket tiles are fewer than SMs) */
 size_t fm_index_build_workspace_bytes(int n_seg, const int64_t *seg_kb, const int64_t *seg_cb, const int64_t *seg_z,
                                       int d, int dtype, int flags);
 int fm_index_build(const void *K, const void *A, int dtype, int d, int n_seg, const int64_t *seg_kb,

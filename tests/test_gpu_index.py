@@ -338,3 +338,21 @@ def test_compute_centroids_code_variant(golden_dir):
         ref = O.compute_centroids(x, cent, 48, 4, 96)
         assert out.shape == (48, 2, 64) and out.dtype == dtype
         assert (out.cpu().float() - ref).abs().max() <= tol
+
+
+def test_fused_build_with_keys_clustered_by_position():
+    """Keys sorted by cluster: every bucket's best keys sit in one stretch of positions, which overflows the per-range
+    candidate buffers; the build retries with one buffer per bucket and still needs no exact rebuild."""
+    import warnings
+    g = torch.Generator().manual_seed(31)
+    N, C, Z, d = 65536, 128, 1024, 128
+    cent = torch.nn.functional.normalize(torch.randn(C, d, generator=g), dim=-1)
+    cid = torch.sort(torch.randint(C, (N,), generator=g)).values
+    k = torch.nn.functional.normalize(cent[cid] + 0.1 * torch.randn(N, d, generator=g), dim=-1).bfloat16()[None].contiguous()
+    A = cent.bfloat16()[None].contiguous()
+    with warnings.catch_warnings(record=True) as rec:
+        warnings.simplefilter("always")
+        mem = fm.Memory.build(k.to(DEV), k.to(DEV), A=A.to(DEV), bucket_size=Z)
+    assert not [w for w in rec if issubclass(w.category, RuntimeWarning)], "fell back to the exact path"
+    ok, why = tables_equal_as_sets(mem.table_of(0).cpu().numpy(), O.topz(O.project(A[0], k[0]), Z))
+    assert ok, why
