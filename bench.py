@@ -626,7 +626,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
-    ap.add_argument("--exchange", default="ring", choices=["ring", "allreduce"],
+    ap.add_argument("--exchange", default="allreduce", choices=["ring", "allreduce"],
                     help="cfg5: how the ranks' partial (O, LSE) are merged (ring of send/recv + merge steps, or MAX + SUM all-reduce)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--build-steps", type=int, default=2)
