@@ -6,8 +6,9 @@
 //   3. thresholds:     tau_b = the r-th largest sample score of bucket b, r chosen so that about
 //                      (r / z) Z keys pass and fewer than Z pass with probability ~1e-6 per bucket (z = Z / step;
 //                      such a bucket goes to the fallback).
-//   4. candidates:     tensor-core projection of ALL keys; the epilogue appends (score, key) for score >= tau_b
-//                      to the bucket's candidate list, in key order.
+//   4. candidates:     tensor-core projection of ALL keys; the epilogue appends every group of four consecutive
+//                      keys with a score >= tau_b (the four scores) to the bucket's candidate list, in key order,
+//                      and records the group in a bit mask per (bucket, key tile).
 //   5. selection:      per bucket, theta = Z-th largest candidate score.  Scores come from the tensor cores
 //                      (hardware summation order), so only candidates whose score is outside
 //                      [theta - eps, theta + eps] are decided by them; the band in between is re-scored

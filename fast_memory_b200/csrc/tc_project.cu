@@ -1,7 +1,7 @@
 // Projection Y = A K^T on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operands staged
 // by TMA), with the epilogue that makes the index build a single pass over the keys: instead of writing
 // Y (C x N fp32, several GB) each epilogue thread owns one bucket row, compares its scores with the bucket's
-// threshold and appends the survivors (score, key) to the bucket's candidate list.  A dense-store epilogue of
+// threshold and appends the groups of four keys that hold a survivor to the bucket's candidate list.  A dense-store epilogue of
 // the same kernel produces the small score matrix of the key sample from which the thresholds are estimated.
 //
 // CTA = 320 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and TMEM owner,
