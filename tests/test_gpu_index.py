@@ -356,3 +356,21 @@ def test_fused_build_with_keys_clustered_by_position():
     assert not [w for w in rec if issubclass(w.category, RuntimeWarning)], "fell back to the exact path"
     ok, why = tables_equal_as_sets(mem.table_of(0).cpu().numpy(), O.topz(O.project(A[0], k[0]), Z))
     assert ok, why
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [64, 128])
+def test_hash_rows_large_batch_ragged_segments(dtype, d):
+    """Batches of 2048 rows or more take the tcgen05 kernel: segments whose bucket counts are not multiples of the
+    128-bucket tile (columns of the next segment must not leak in), a one-row segment, row tiles that straddle
+    segment ends."""
+    g = torch.Generator().manual_seed(5 + d)
+    Cs, Ss = [5, 64, 130, 300], [2500, 1, 3000, 129]
+    A = torch.randn(sum(Cs), d, generator=g).to(dtype)
+    X = torch.randn(sum(Ss), d, generator=g).to(dtype)
+    xb = torch.tensor([0] + list(np.cumsum(Ss)), dtype=torch.int32)
+    cb = torch.tensor([0] + list(np.cumsum(Cs)), dtype=torch.int32)
+    h = fm.hash_rows(X.to(DEV), A.to(DEV), xb.to(DEV), cb.to(DEV), max(Ss)).cpu().numpy()
+    for s in range(len(Cs)):
+        ref = O.query_hash(A[cb[s]:cb[s + 1]][None], X[xb[s]:xb[s + 1]][None])[0]
+        assert np.array_equal(h[xb[s]:xb[s + 1]], ref), f"segment {s}"
