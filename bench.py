@@ -175,10 +175,7 @@ def run_ours(args, rank, world):
     def step(qd):
         o, lse = mem.query(qd, sm_scale)
         if local is not None:
-            out_acc.copy_(local[0])
-            lse_acc.copy_(local[1])
-            ops.lse_merge(out_acc, lse_acc, o, lse)
-            return out_acc, lse_acc
+            return ops.lse_merge_out(local[0], local[1], o, lse, out=out_acc, lse_out=lse_acc)
         return o, lse
 
     def barrier():

@@ -63,6 +63,69 @@ lse_merge_kernel(float *__restrict__ out, float *__restrict__ lse, const T *__re
     }
 }
 
+// The same merge out of place: (acc_out fp32, acc_lse) and (blk_out T, blk_lse fp32) are read, the merged rows are written
+// to `dst` in TO (fp32 or T) and `dst_lse`; per row it moves d * (4 + sizeof(T) + sizeof(TO)) + 12 bytes instead of the
+// copy + in-place merge + cast a caller that must keep its accumulator would otherwise run.
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+lse_merge_out_kernel(const float *__restrict__ acc_out, const float *__restrict__ acc_lse, const T *__restrict__ blk_out,
+                     const float *__restrict__ blk_lse, TO *__restrict__ dst, float *__restrict__ dst_lse, int64_t n_rows, int d)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = int64_t(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t r = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < n_rows; r += warps) {
+        const float a = acc_lse[r], b = blk_lse[r];
+        float w, nl;
+        if (b == -INFINITY) { w = 0.f; nl = a; }
+        else if (a == -INFINITY) { w = 1.f; nl = b; }
+        else {
+            const float dlt = b - a;
+            w = 1.f / (1.f + expf(-dlt));
+            nl = a + (dlt > 0.f ? dlt + log1pf(expf(-dlt)) : log1pf(expf(dlt)));
+        }
+        const float *arow = acc_out + r * d;
+        const T *brow = blk_out + r * d;
+        TO *orow = dst + r * d;
+        for (int c = lane * 4; c < d; c += 128) {
+            float4 o4 = *reinterpret_cast<const float4 *>(arow + c);
+            float b0, b1, b2, b3;
+            if constexpr (sizeof(T) == 4) {
+                float4 b4 = *reinterpret_cast<const float4 *>(brow + c);
+                b0 = b4.x; b1 = b4.y; b2 = b4.z; b3 = b4.w;
+            } else {
+                uint2 raw = *reinterpret_cast<const uint2 *>(brow + c);
+                const T *h = reinterpret_cast<const T *>(&raw);
+                b0 = Elem<T>::to_f32(h[0]); b1 = Elem<T>::to_f32(h[1]);
+                b2 = Elem<T>::to_f32(h[2]); b3 = Elem<T>::to_f32(h[3]);
+            }
+            o4.x -= w * (o4.x - b0);
+            o4.y -= w * (o4.y - b1);
+            o4.z -= w * (o4.z - b2);
+            o4.w -= w * (o4.w - b3);
+            if constexpr (sizeof(TO) == 4) {
+                *reinterpret_cast<float4 *>(orow + c) = o4;
+            } else {
+                TO h[4] = {Elem<TO>::from_f32(o4.x), Elem<TO>::from_f32(o4.y), Elem<TO>::from_f32(o4.z), Elem<TO>::from_f32(o4.w)};
+                *reinterpret_cast<uint2 *>(orow + c) = *reinterpret_cast<const uint2 *>(h);
+            }
+        }
+        if (lane == 0) dst_lse[r] = nl;
+    }
+}
+
+template <typename T>
+static int launch_merge_out(const float *acc_out, const float *acc_lse, const void *blk_out, const float *blk_lse, void *dst,
+                            int dst_dtype, float *dst_lse, int64_t n_rows, int d, cudaStream_t st)
+{
+    const int blocks = (int)std::min<int64_t>(ceil_div(n_rows, 8), int64_t(sm_count()) * 8);
+    if (dst_dtype == FM_F32)
+        lse_merge_out_kernel<T, float><<<blocks, 256, 0, st>>>(acc_out, acc_lse, (const T *)blk_out, blk_lse, (float *)dst, dst_lse, n_rows, d);
+    else
+        lse_merge_out_kernel<T, T><<<blocks, 256, 0, st>>>(acc_out, acc_lse, (const T *)blk_out, blk_lse, (T *)dst, dst_lse, n_rows, d);
+    FM_LAUNCHED("lse_merge_out_kernel");
+    return FM_OK;
+}
+
 }  // namespace fm
 
 extern "C" int fm_lse_merge(float *out, float *lse, const void *blk_out, int blk_dtype, const void *blk_lse,
@@ -94,4 +157,25 @@ extern "C" int fm_lse_merge(float *out, float *lse, const void *blk_out, int blk
     }
     FM_LAUNCHED("lse_merge_kernel");
     return FM_OK;
+}
+
+extern "C" int fm_lse_merge_out(const float *acc_out, const float *acc_lse, const void *blk_out, int blk_dtype, const float *blk_lse,
+                                void *dst, int dst_dtype, float *dst_lse, int64_t n_rows, int d, fm_stream_t stream)
+{
+    using namespace fm;
+    FM_REQUIRE(n_rows >= 0 && d > 0, "fm_lse_merge_out: bad sizes");
+    if (n_rows == 0) return FM_OK;
+    FM_REQUIRE(acc_out && acc_lse && blk_out && blk_lse && dst && dst_lse, "fm_lse_merge_out: null pointer");
+    FM_REQUIRE(d % 4 == 0, "fm_lse_merge_out: head dim must be a multiple of 4");
+    FM_REQUIRE(((uintptr_t)acc_out) % 16 == 0 && ((uintptr_t)blk_out) % 8 == 0 && ((uintptr_t)dst) % 8 == 0,
+               "fm_lse_merge_out: misaligned buffer");
+    FM_REQUIRE(dst_dtype == FM_F32 || dst_dtype == blk_dtype, "fm_lse_merge_out: the result is fp32 or in the block's dtype");
+    FM_REQUIRE(dst_dtype != FM_F32 || ((uintptr_t)dst) % 16 == 0, "fm_lse_merge_out: misaligned buffer");
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (blk_dtype) {
+    case FM_F32: return launch_merge_out<float>(acc_out, acc_lse, blk_out, blk_lse, dst, dst_dtype, dst_lse, n_rows, d, st);
+    case FM_BF16: return launch_merge_out<__nv_bfloat16>(acc_out, acc_lse, blk_out, blk_lse, dst, dst_dtype, dst_lse, n_rows, d, st);
+    case FM_F16: return launch_merge_out<__half>(acc_out, acc_lse, blk_out, blk_lse, dst, dst_dtype, dst_lse, n_rows, d, st);
+    default: set_error("fm_lse_merge_out: unknown dtype %d", blk_dtype); return FM_ERR_UNSUPPORTED;
+    }
 }

@@ -388,10 +388,7 @@ class Memory:
             main.wait_event(ev_in[i])
             o, lse = self.query(q_dev[a:b], sm_scale, head_range=(bounds[i], bounds[i + 1]))
             if local is not None:
-                acc_o = local[0][a:b].clone()
-                acc_l = local[1][a:b].clone()
-                ops.lse_merge(acc_o, acc_l, o, lse)
-                o, lse = acc_o.to(q_host.dtype), acc_l
+                o, lse = ops.lse_merge_out(local[0][a:b], local[1][a:b], o, lse, out_dtype=q_host.dtype)
             done = torch.cuda.Event()
             done.record(main)
             with torch.cuda.stream(s_out):

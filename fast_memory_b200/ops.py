@@ -121,6 +121,31 @@ def lse_merge(out: torch.Tensor, lse: torch.Tensor, block_out: torch.Tensor, blo
             "fm_lse_merge")
 
 
+def lse_merge_out(acc_out: torch.Tensor, acc_lse: torch.Tensor, block_out: torch.Tensor, block_lse: torch.Tensor,
+                  out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
+                  lse_out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The merge of :func:`lse_merge` out of place: fp32 ``acc_out`` / ``acc_lse`` stay untouched, the result comes back
+    in ``out_dtype`` (fp32, the default, or ``block_out``'s dtype) with its fp32 LSE - one pass instead of copy + merge
+    + cast."""
+    dev = L.require_cuda(acc_out, acc_lse, block_out, block_lse)
+    if acc_out.dtype != torch.float32 or acc_lse.dtype != torch.float32 or block_lse.dtype != torch.float32:
+        raise TypeError("the accumulator and both LSEs must be float32")
+    assert acc_out.is_contiguous() and acc_lse.is_contiguous() and block_out.is_contiguous() and block_lse.is_contiguous()
+    d = acc_out.shape[-1]
+    rows = acc_out.numel() // d
+    assert block_out.numel() == acc_out.numel() and acc_lse.numel() == rows and block_lse.numel() == rows
+    out_dtype = out_dtype or torch.float32
+    if out is None:
+        out = torch.empty(acc_out.shape, dtype=out_dtype, device=dev)
+    if lse_out is None:
+        lse_out = torch.empty(acc_lse.shape, dtype=torch.float32, device=dev)
+    assert out.dtype == out_dtype and out.is_contiguous() and lse_out.is_contiguous() and lse_out.dtype == torch.float32
+    L.check(L.lib().fm_lse_merge_out(L.ptr(acc_out), L.ptr(acc_lse), L.ptr(block_out), L.dtype_id(block_out.dtype),
+                                     L.ptr(block_lse), L.ptr(out), L.dtype_id(out_dtype), L.ptr(lse_out), rows, d,
+                                     L.stream_ptr(dev)), "fm_lse_merge_out")
+    return out, lse_out
+
+
 def project(A: torch.Tensor, K: torch.Tensor) -> torch.Tensor:
     """fp32 ``Y[c, j] = A[c] . K[j]`` in the library's fixed summation order."""
     dev = L.require_cuda(A, K)

@@ -142,6 +142,12 @@ int fm_shard_filter(const int64_t *k_hashes, int64_t C, int64_t H, int64_t Z, in
 int fm_lse_merge(float *out, float *lse, const void *blk_out, int blk_dtype, const void *blk_lse, int lse_dtype,
                  int64_t n_rows, int d, fm_stream_t stream);
 
+/* The same merge out of place, for a caller that keeps its accumulator (e.g. a local-window result merged with a new
+ * memory result per request, mem:332): reads (acc_out fp32, acc_lse fp32) and (blk_out in `blk_dtype`, blk_lse fp32),
+ * writes the merged rows to `dst` in `dst_dtype` (FM_F32 or `blk_dtype`) and their LSE to `dst_lse`. */
+int fm_lse_merge_out(const float *acc_out, const float *acc_lse, const void *blk_out, int blk_dtype, const float *blk_lse,
+                     void *dst, int dst_dtype, float *dst_lse, int64_t n_rows, int d, fm_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Projection Y[c, j] = A[c, :] . K[j, :] in fp32 (sequential FMA over the head dim), row stride ldy.
  * Replaces: the einsum at mem:261 / tk:277 (README.md:25).  Stand-alone form, for tests and for

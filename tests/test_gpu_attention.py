@@ -157,3 +157,22 @@ def test_merge_handles_empty_sides():
     assert torch.allclose(out.cpu()[keep], ro[keep], atol=1e-6)
     assert torch.equal(torch.isinf(lse.cpu()), torch.isinf(rl)) and torch.allclose(lse.cpu()[keep], rl[keep], atol=1e-6)
     assert torch.equal(o1, o1) and out.data_ptr() != o1.data_ptr()      # merge() leaves its inputs alone
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_merge_out_of_place_equals_in_place(dtype):
+    g = torch.Generator().manual_seed(4)
+    rows, d = 1000, 128
+    a = torch.randn(rows, d, generator=g).to(DEV)
+    al = (torch.randn(rows, generator=g) * 3).to(DEV)
+    b = torch.randn(rows, d, generator=g).to(dtype).to(DEV)
+    bl = (torch.randn(rows, generator=g) * 3).to(DEV)
+    al[::7] = -math.inf
+    bl[::5] = -math.inf
+    ref_o, ref_l = a.clone(), al.clone()
+    fm.lse_merge(ref_o, ref_l, b, bl)
+    o, l = fm.lse_merge_out(a, al, b, bl)
+    assert torch.equal(o, ref_o) and torch.equal(l, ref_l)
+    o2, l2 = fm.lse_merge_out(a, al, b, bl, out_dtype=dtype)
+    assert o2.dtype == dtype and torch.equal(o2, ref_o.to(dtype)) and torch.equal(l2, ref_l)
+
