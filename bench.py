@@ -616,6 +616,30 @@ def run_reference(args, rank, world):
             "gpu_launches": 0}
 
 
+def bind_to_gpu_numa_node(local_rank: int) -> str:
+    """Run this rank (and so first-touch its pinned host buffers) on the CPU cores of its GPU's NUMA node: with several
+    ranks copying at once, buffers on the far socket halve the host<->device bandwidth.  Best effort; returns a note."""
+    try:
+        props = torch.cuda.get_device_properties(local_rank)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return "numa: no node reported"
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if not allowed:
+            return f"numa: node {node} has no allowed cpu"
+        os.sched_setaffinity(0, allowed)
+        return f"numa: node {node}, {len(allowed)} cpus"
+    except (OSError, ValueError, AttributeError) as e:
+        return f"numa: not bound ({type(e).__name__})"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -644,6 +668,9 @@ def main():
         res = run_reference(args, rank, world)
     else:
         if world > 1:
+            note = bind_to_gpu_numa_node(int(os.environ.get("LOCAL_RANK", 0)))
+            if rank == 0:
+                print(note, file=sys.stderr)
             torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
         res = (run_ring if args.workload == "cfg5" else run_varlen if args.workload == "cfg4" else run_ours)(args, rank, world)
         if world > 1:
