@@ -152,6 +152,7 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
             for (int n = 0; n < 2; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[mt][n][e] = 0.f;
+        float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
             // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
@@ -162,8 +163,14 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 if constexpr (MT == 1) {
-                    mma16816<T>(s[mt][0], qf[ks], b[0], b[1]);
-                    mma16816<T>(s[mt][1], qf[ks], b[2], b[3]);
+                    // even and odd k-steps accumulate separately: four independent MMA chains instead of two
+                    if (ks & 1) {
+                        mma16816<T>(s_odd[0], qf[ks], b[0], b[1]);
+                        mma16816<T>(s_odd[1], qf[ks], b[2], b[3]);
+                    } else {
+                        mma16816<T>(s[mt][0], qf[ks], b[0], b[1]);
+                        mma16816<T>(s[mt][1], qf[ks], b[2], b[3]);
+                    }
                 } else {
                     // matrices: (rows 0-7, d lo), (rows 8-15, d lo), (rows 0-7, d hi), (rows 8-15, d hi) of the row tile
                     uint32_t qa[4];
@@ -172,6 +179,12 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
                     mma16816<T>(s[mt][1], qa, b[2], b[3]);
                 }
             }
+        }
+        if constexpr (MT == 1) {
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[0][n][e] += s_odd[n][e];
         }
         // mask (only the last tile can be partial), online softmax in the scaled base-2 domain
         // (rows g and g + 8 of each row tile; this thread's keys: wk + 8 n + 2 tq + {0, 1})
