@@ -135,3 +135,19 @@ def test_config4_full_size_varlen():
     g = torch.Generator().manual_seed(3)
     rows = torch.randint(H * Qt, (32,), generator=g).tolist()
     check_sampled_queries(mem, qf, of, lf, hf, seg_of, rows, sm, cfg.dtype)
+
+
+def test_config5_shards_several_workspace_groups():
+    """Two heads of the ring config, all 8 key shards of a head on one device (16 segments of 524288 keys, C = 1024,
+    Z = 8192): more buckets than one workspace group of the fused build holds, so the segments are built in several
+    groups; properties everywhere, oracle rows in the first and in a later group."""
+    cfg = synth.config("cfg5")
+    q, k, v = synth.make(cfg, seed=4, device=DEV, kv_heads=2)
+    H, N, d = k.shape
+    L = N // cfg.shards
+    cu_k = [i * L for i in range(cfg.shards + 1)]
+    mem = fm.Memory.build(k, v, n_buckets=[cfg.n_buckets] * cfg.shards, bucket_size=[cfg.bucket_size] * cfg.shards,
+                          kmeans_iters=1, cu_seqlens_k=cu_k)
+    check_table_properties(mem)
+    check_buckets_against_oracle(mem, 1, [0, 500, 1023])
+    check_buckets_against_oracle(mem, 14, [3, 777])
