@@ -65,6 +65,7 @@ _SIGNATURES = {
     "fm_kmeans": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                           c_size_t, c_void_p]),
     "fm_unit_rows": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p]),
+    "fm_table_scores": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "fm_gather_mean": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
 }
 

@@ -97,6 +97,40 @@ extern "C" int fm_project(const void *A, const void *K, int dtype, int64_t C, in
     }
 }
 
+namespace fm {
+// scores[e] = canonical A[b] . K[table[e]] for the entries e of bucket b: what a table's keys scored, in the fixed fp32
+// order, so that tables of different key shards can be merged exactly.
+template <typename T>
+__global__ void __launch_bounds__(128)
+table_scores_kernel(const T *__restrict__ K, const T *__restrict__ A, int d, const int32_t *__restrict__ table,
+                    const int64_t *__restrict__ bucket_off, float *__restrict__ scores)
+{
+    const int b = blockIdx.x;
+    const T *a_row = A + size_t(b) * d;
+    for (int64_t e = bucket_off[b] + threadIdx.x; e < bucket_off[b + 1]; e += blockDim.x)
+        scores[e] = canonical_dot(a_row, K + size_t(table[e]) * d, d);
+}
+}  // namespace fm
+
+extern "C" int fm_table_scores(const void *K, const void *A, int dtype, int d, int64_t total_buckets, const int32_t *table,
+                               const int64_t *bucket_off, float *scores, fm_stream_t stream)
+{
+    using namespace fm;
+    FM_REQUIRE(K && A && table && bucket_off && scores, "fm_table_scores: null pointer");
+    FM_REQUIRE(total_buckets > 0 && total_buckets < (int64_t(1) << 31), "fm_table_scores: bad bucket count");
+    int rc = check_dim("fm_table_scores", d);
+    if (rc != FM_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (dtype) {
+    case FM_F32: table_scores_kernel<float><<<(unsigned)total_buckets, 128, 0, st>>>((const float *)K, (const float *)A, d, table, bucket_off, scores); break;
+    case FM_BF16: table_scores_kernel<__nv_bfloat16><<<(unsigned)total_buckets, 128, 0, st>>>((const __nv_bfloat16 *)K, (const __nv_bfloat16 *)A, d, table, bucket_off, scores); break;
+    case FM_F16: table_scores_kernel<__half><<<(unsigned)total_buckets, 128, 0, st>>>((const __half *)K, (const __half *)A, d, table, bucket_off, scores); break;
+    default: set_error("fm_table_scores: unknown dtype %d", dtype); return FM_ERR_UNSUPPORTED;
+    }
+    FM_LAUNCHED("table_scores_kernel");
+    return FM_OK;
+}
+
 extern "C" int fm_topz_select(const float *Y, int64_t n_rows, int64_t N, int64_t ldy, int64_t Z, int32_t index_base,
                               int32_t *table, int64_t ld_table, fm_stream_t stream)
 {

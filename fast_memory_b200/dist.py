@@ -20,6 +20,7 @@ from typing import Callable, List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
+from . import _lib as L
 from . import ops
 from .memory import Memory, kmeans_projection
 
@@ -225,3 +226,81 @@ class ShardedMemory:
         full_o = all_gather_chunks(oc, own, self.group)[:rows].reshape(Hq, S, d)
         full_l = all_gather_chunks(lc, own, self.group)[:rows].reshape(Hq, S)
         return full_o, full_l
+
+
+# ---------------------------------------------------------------------------------------------------
+# The reference's GLOBAL index over sharded keys (mem:260-278): top-Z of a bucket over the keys of ALL ranks
+# ---------------------------------------------------------------------------------------------------
+def shard_candidates(k_local: torch.Tensor, A: torch.Tensor, bucket_size: int, key_offset: int
+                     ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """This shard's candidates for the global table: its own top-Z per bucket with their canonical fp32 scores.
+
+    ``k_local`` ``[H, L, d]``, ``A`` ``[H, C, d]`` (the same on every rank).  Returns ``(scores [H, C, Zc] fp32,
+    ids [H, C, Zc] int64)``, ``Zc = min(Z, L)``, ids = ``key_offset`` + index inside the shard, ascending per bucket.
+    A key of the global top-Z is in the top-Z of its own shard, so the union of these candidates holds the answer."""
+    H, Lk, d = k_local.shape
+    C = A.shape[1]
+    mem = Memory.build(k_local, k_local, A=A, bucket_size=bucket_size)
+    zc = min(bucket_size, Lk)
+    scores = torch.empty(H * C * zc, dtype=torch.float32, device=k_local.device)
+    L.check(L.lib().fm_table_scores(L.ptr(mem.k), L.ptr(mem.A), L.dtype_id(k_local.dtype), d, H * C, L.ptr(mem.table),
+                                    L.ptr(mem.bucket_off), L.ptr(scores), L.stream_ptr(k_local.device)), "fm_table_scores")
+    local = mem.table.reshape(H, C, zc).long() - (torch.arange(H, device=k_local.device) * Lk)[:, None, None]
+    return scores.reshape(H, C, zc), local + key_offset
+
+
+def merge_shard_candidates(scores: Sequence[torch.Tensor], ids: Sequence[torch.Tensor], bucket_size: int) -> torch.Tensor:
+    """Global table from the candidates of all shards, given in shard order (ascending key offsets): per bucket the
+    ``bucket_size`` best of the concatenated candidates, exact fp32 comparison, the lower key index winning a tie - the
+    table a single device would build over all the keys.  Returns ``k_hashes`` ``[C, H, Z]`` int64 global key indices,
+    ascending per bucket (the layout mem:128 expects)."""
+    Y = torch.cat(list(scores), dim=-1)                                  # [H, C, sum Zc]
+    I = torch.cat(list(ids), dim=-1)
+    H, C, n = Y.shape
+    pos = ops.topz_select(Y.reshape(H * C, n).contiguous(), bucket_size).long()      # positions, ascending = ids ascending
+    table = torch.gather(I.reshape(H * C, n), 1, pos).reshape(H, C, -1)
+    return table.permute(1, 0, 2).contiguous()
+
+
+def build_global_table(k_local: torch.Tensor, A: torch.Tensor, bucket_size: int,
+                       group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """The index build of the reference's distributed path (mem:260-278) without moving the score matrix: every rank
+    selects inside its own key shard on the index-build kernels, the ``(score, key)`` candidates - Z per bucket and rank
+    instead of the shard's whole row of Y - are all-gathered, and one exact row select finishes the table on every rank.
+    ``k_local`` ``[H, L, d]`` is rank r's contiguous shard ``[r L, (r + 1) L)`` of the keys."""
+    W = dist.get_world_size(group) if dist.is_initialized() else 1
+    r = dist.get_rank(group) if dist.is_initialized() else 0
+    sc, idx = shard_candidates(k_local, A, bucket_size, r * k_local.shape[1])
+    if W == 1:
+        return merge_shard_candidates([sc], [idx], bucket_size)
+    all_sc = torch.empty((W,) + tuple(sc.shape), dtype=sc.dtype, device=sc.device)
+    all_id = torch.empty((W,) + tuple(idx.shape), dtype=idx.dtype, device=idx.device)
+    dist.all_gather_into_tensor(all_sc, sc.contiguous(), group=group)
+    dist.all_gather_into_tensor(all_id, idx.contiguous(), group=group)
+    return merge_shard_candidates(list(all_sc), list(all_id), bucket_size)
+
+
+def query_global_table(k_hashes: torch.Tensor, A: torch.Tensor, q: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor,
+                       sm_scale: float, group: Optional[dist.ProcessGroup] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """All queries against a globally indexed, key-sharded memory (the forward of mem:291-338 with the key blocks staying
+    where they are): hash with the shared ``A``, attend to the table entries that fall into this rank's shard
+    (:func:`fast_memory_b200.ops.ring_attention_masked_forward`), merge the ranks' partial results.
+    ``q`` ``[Hq, S, d]``, ``k_local`` / ``v_local`` ``[H, L, d]``; returns fp32 ``(out [Hq, S, d], lse [Hq, S])``."""
+    W = dist.get_world_size(group) if dist.is_initialized() else 1
+    r = dist.get_rank(group) if dist.is_initialized() else 0
+    Hq, S, d = q.shape
+    H = k_local.shape[0]
+    C = A.shape[1]
+    seg_xb = torch.arange(0, (H + 1) * (Hq // H) * S, (Hq // H) * S, dtype=torch.int32, device=q.device)
+    seg_cb = torch.arange(0, (H + 1) * C, C, dtype=torch.int32, device=q.device)
+    hashes = ops.hash_rows(q.reshape(Hq * S, d), A.reshape(H * C, d).contiguous(), seg_xb, seg_cb, (Hq // H) * S)
+    o, lse = ops.ring_attention_masked_forward(k_hashes, hashes.reshape(H, Hq // H, S).long(), q[None], k_local[None],
+                                               v_local[None], sm_scale, r)
+    # the drop-in returns the reference's convention (lse in q's dtype, finfo.min for an empty bucket): back to fp32 / -inf
+    lse = lse[0].float()
+    lse = torch.where(lse <= torch.finfo(q.dtype).min, torch.full_like(lse, float("-inf")), lse)
+    if W == 1:
+        return o[0].float(), lse
+    out, l = allreduce_merge_partials(o[0].reshape(Hq * S, d), lse.reshape(Hq * S), group)
+    return out.reshape(Hq, S, d), l.reshape(Hq, S)
+

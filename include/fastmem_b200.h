@@ -198,6 +198,14 @@ int fm_index_build(const void *K, const void *A, int dtype, int d, int n_seg, co
                    const int64_t *seg_cb, const int64_t *seg_z, const int64_t *table_off, int32_t *table, int flags,
                    void *workspace, size_t workspace_bytes, fm_stream_t stream);
 
+/* scores[e] = A[b, :] . K[table[e], :] (canonical fp32 chain) for every entry e of every bucket b of a table built by
+ * fm_index_build (table / bucket_off as produced there, total_buckets rows of A).  With the scores, the tables of
+ * several key shards merge into the reference's GLOBAL table (top-Z over all shards' keys, mem:260-278) by one exact
+ * row select over the shards' candidates instead of an all_to_all of the score matrix. */
+int fm_table_scores(const void *K, const void *A, int dtype, int d, int64_t total_buckets, const int32_t *table,
+                    const int64_t *bucket_off, float *scores, fm_stream_t stream);
+
+
 /* ---------------------------------------------------------------------------------------------
  * Projection matrix by spherical k-means (distance 1 - c.x, README.md:37-45): `iters` rounds of
  * assignment (fm_hash_rows on the raw rows) and centroid update (exact integer sums of the unit rows

@@ -63,9 +63,42 @@ def _rank_main(rank, world, port, n_shards, H, L, S, C, Z, result):
     o2, lse2 = mem.query(q.to(dev), cfg.d ** -0.5, exchange="allreduce")
     torch.cuda.synchronize()
     assert (o2 - o).abs().max() <= 1e-4 and (lse2 - lse).abs().max() <= 1e-4       # two ways to merge the same partials
+    # the reference's global index over the two ranks' keys, and all queries through it
+    from fast_memory_b200 import dist as fmd
+    k_hashes = fmd.build_global_table(k[:, lo:hi].contiguous().to(dev), A.to(dev), Z)
+    go, gl = fmd.query_global_table(k_hashes, A.to(dev), q.to(dev), k[:, lo:hi].contiguous().to(dev),
+                                    v[:, lo:hi].contiguous().to(dev), cfg.d ** -0.5)
+    torch.cuda.synchronize()
     if rank == 0:
         result["o"], result["lse"] = o.cpu(), lse.cpu()
+        result["k_hashes"], result["go"], result["gl"] = k_hashes.cpu(), go.cpu(), gl.cpu()
     dist.destroy_process_group()
+
+
+def test_global_table_from_shard_candidates_equals_single_device_build():
+    """mem:260-278 without the all_to_all of Y: per-shard top-Z with canonical scores, one exact select over the union."""
+    from fast_memory_b200 import dist as fmd
+    n_shards, H, L, S, C, Z = 4, 2, 8192, 300, 32, 700
+    cfg, q, k, v, A = _case(n_shards, H, L, S, C)
+    kd, vd, Ad = k.to(DEV), v.to(DEV), A.to(DEV)
+    cands = [fmd.shard_candidates(kd[:, s * L:(s + 1) * L].contiguous(), Ad, Z, s * L) for s in range(n_shards)]
+    k_hashes = fmd.merge_shard_candidates([c[0] for c in cands], [c[1] for c in cands], Z)        # [C, H, Z]
+    assert k_hashes.shape == (C, H, Z) and k_hashes.dtype == torch.int64
+    ref = fm.Memory.build(kd, vd, A=Ad, bucket_size=Z)
+    for h in range(H):
+        assert torch.equal(k_hashes[:, h].cpu(), ref.table_of(h).long().cpu()), f"head {h}"
+    # attending through the global table, shard by shard, equals the single memory
+    sm = cfg.d ** -0.5
+    o_ref, l_ref = ref.query(q.to(DEV), sm)
+    out, acc_l = None, None
+    for s in range(n_shards):
+        hashes = ref.hash_queries(q.to(DEV)).long()[:, None, :]
+        bo, bl = fm.ring_attention_masked_forward(k_hashes, hashes, q.to(DEV)[None], kd[None, :, s * L:(s + 1) * L].contiguous(),
+                                                  vd[None, :, s * L:(s + 1) * L].contiguous(), sm, s)
+        bl = torch.where(bl.float() <= torch.finfo(q.dtype).min, torch.full_like(bl.float(), float("-inf")), bl.float())
+        out, acc_l = fm.update_out_and_lse(out, acc_l, bo, bl)
+    assert (out[0].cpu() - o_ref.float().cpu()).abs().max() <= 2e-2
+    assert (acc_l[0].squeeze(-1).cpu() - l_ref.cpu()).abs().max() <= 3e-2        # the drop-in rounds each shard's LSE to bf16
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -79,8 +112,15 @@ def test_two_ranks_equal_single_device():
         result = mgr.dict()
         mp.spawn(_rank_main, args=(2, port, n_shards, H, L, S, C, Z, result), nprocs=2, join=True)
         o2, l2 = result["o"], result["lse"]
+        kh, go, gl = result["k_hashes"], result["go"], result["gl"]
     cfg, q, k, v, A = _case(n_shards, H, L, S, C)
     single = ShardedMemory.build(k.to(DEV), v.to(DEV), L, A=A.to(DEV), bucket_size=Z)
     o1, l1 = single.query(q.to(DEV), cfg.d ** -0.5)
     assert (o1.float().cpu() - o2).abs().max() <= 2e-2          # bf16 partials merged in fp32 vs one bf16 pass
     assert (l1.cpu() - l2).abs().max() <= 1e-3
+    # global table built by the two ranks = the table one device builds over all the keys; queries through it
+    whole = fm.Memory.build(k.to(DEV), v.to(DEV), A=A.to(DEV), bucket_size=Z)
+    for h in range(H):
+        assert torch.equal(kh[:, h], whole.table_of(h).long().cpu())
+    ow, lw = whole.query(q.to(DEV), cfg.d ** -0.5)
+    assert (ow.float().cpu() - go).abs().max() <= 2e-2 and (lw.cpu() - gl).abs().max() <= 3e-2
