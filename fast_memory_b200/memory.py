@@ -415,6 +415,45 @@ class Memory:
                     max_bucket_len=self.max_bucket_len, seq_buckets=self.seq_buckets,
                     cu_seqlens_k=self.cu_seqlens_k)
 
+    def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> "Memory":
+        """A memory over the old keys followed by ``k_new`` / ``v_new`` (``[H, N_new, d]``; uniform memories), with the
+        same projection and bucket size, WITHOUT indexing the old keys again: a key of the new top-Z is either in the old
+        table or in the top-Z of the new block, so the old entries (re-scored with the canonical chain,
+        ``fm_table_scores``) and the new block's own top-Z are merged by one exact row select.  The table equals the one
+        a full build over all the keys gives.  Returns a new ``Memory``; this one stays valid."""
+        from .dist import merge_shard_candidates, shard_candidates
+        if self.n_seq != 1:
+            raise ValueError("append serves uniform memories")
+        dev = L.require_cuda(k_new, v_new)
+        H, N, d = self.k.shape
+        if k_new.dim() != 3 or k_new.shape[0] != H or k_new.shape[2] != d or v_new.shape != k_new.shape or k_new.dtype != self.k.dtype:
+            raise ValueError("append: k_new / v_new must be [H, N_new, d] in the memory's dtype")
+        C, Z = self.seq_buckets[0], self.seg_z[0]
+        zc_old = min(Z, N)
+        A3 = self.A.reshape(H, C, d)
+        old_scores = torch.empty(H * C * zc_old, dtype=torch.float32, device=dev)
+        L.check(L.lib().fm_table_scores(L.ptr(self.k), L.ptr(self.A), L.dtype_id(self.k.dtype), d, H * C, L.ptr(self.table),
+                                        L.ptr(self.bucket_off), L.ptr(old_scores), L.stream_ptr(dev)), "fm_table_scores")
+        old_ids = self.table.reshape(H, C, zc_old).long() - (torch.arange(H, device=dev) * N)[:, None, None]
+        new_scores, new_ids = shard_candidates(k_new.contiguous(), A3, Z, N)
+        k_hashes = merge_shard_candidates([old_scores.reshape(H, C, zc_old), new_scores], [old_ids, new_ids], Z)   # [C, H, Z']
+        N2 = N + k_new.shape[1]
+        zc = k_hashes.shape[2]
+        out = Memory()
+        out.k, out.v = torch.cat([self.k, k_new], 1), torch.cat([self.v, v_new], 1)
+        out.n_heads, out.n_seq, out.d = H, 1, d
+        out.cu_seqlens_k = [0, N2]
+        out.seg_kb = [h * N2 for h in range(H + 1)]
+        out.seg_cb, out.seg_z, out.seq_buckets = list(self.seg_cb), list(self.seg_z), list(self.seq_buckets)
+        out.table_off = [h * C * zc for h in range(H + 1)]
+        out.A, out.centroids_f32 = self.A, self.centroids_f32
+        out.table = (k_hashes.permute(1, 0, 2) + (torch.arange(H, device=dev) * N2)[:, None, None]).to(torch.int32).reshape(-1).contiguous()
+        out.bucket_off = torch.arange(0, (H * C + 1) * zc, zc, dtype=torch.int64, device=dev)
+        out.max_bucket_len = zc
+        out.build_status = torch.zeros((), dtype=torch.int32, device=dev)
+        out._seg_cb_dev = self._seg_cb_dev
+        return out
+
     @classmethod
     def from_state_dict(cls, state: dict, k: torch.Tensor, v: torch.Tensor) -> "Memory":
         self = cls()

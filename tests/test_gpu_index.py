@@ -374,3 +374,28 @@ def test_hash_rows_large_batch_ragged_segments(dtype, d):
     for s in range(len(Cs)):
         ref = O.query_hash(A[cb[s]:cb[s + 1]][None], X[xb[s]:xb[s + 1]][None])[0]
         assert np.array_equal(h[xb[s]:xb[s + 1]], ref), f"segment {s}"
+
+
+def test_append_equals_full_build():
+    """Incremental growth of a memory: old table entries re-scored + the new block's own top-Z, merged exactly."""
+    cfg = synth.config("cfg2")
+    q, k, v = synth.make(cfg, seed=8, kv_heads=2, n_keys=24576, n_queries=500)
+    C, Z = 48, 600
+    kd, vd = k.to(DEV), v.to(DEV)
+    full = fm.Memory.build(kd, vd, n_buckets=C, bucket_size=Z, kmeans_iters=1)
+    A = full.A.reshape(2, C, cfg.d)
+    mem = fm.Memory.build(kd[:, :16384].contiguous(), vd[:, :16384].contiguous(), A=A, bucket_size=Z)
+    mem = mem.append(kd[:, 16384:20000].contiguous(), vd[:, 16384:20000].contiguous())
+    mem = mem.append(kd[:, 20000:].contiguous(), vd[:, 20000:].contiguous())          # twice, ragged block sizes
+    assert torch.equal(mem.k, kd) and torch.equal(mem.v, vd)
+    for h in range(2):
+        assert torch.equal(mem.table_of(h), full.table_of(h)), f"head {h}"
+    o1, l1 = mem.query(q.to(DEV), 0.1)
+    o2, l2 = full.query(q.to(DEV), 0.1)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    # a memory smaller than its bucket size grows into it
+    small = fm.Memory.build(kd[:, :300].contiguous(), vd[:, :300].contiguous(), A=A, bucket_size=Z)
+    small = small.append(kd[:, 300:900].contiguous(), vd[:, 300:900].contiguous())
+    ref = fm.Memory.build(kd[:, :900].contiguous(), vd[:, :900].contiguous(), A=A, bucket_size=Z)
+    for h in range(2):
+        assert torch.equal(small.table_of(h), ref.table_of(h))
