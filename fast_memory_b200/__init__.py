@@ -5,10 +5,11 @@ build it with ``python -m fast_memory_b200.build``.  There is no CPU or PyTorch 
 """
 from ._lib import FastMemError, launch_count
 from .memory import Memory, compute_centroids, kmeans_projection, merge
-from .ops import (attention_hash, attention_hash_varlen, group_rows, hash_rows, hashed_attention, lse_merge, lse_merge_out, project,
+from .ops import (attention_hash, attention_hash_varlen, group_rows, hash_rows, hashed_attention, hashed_attention_backward, lse_merge, lse_merge_out, project,
                   ring_attention_masked_forward, shard_filter, topz_select, unit_rows, update_out_and_lse)
 
 __all__ = [
+    "hashed_attention_backward",
     "lse_merge_out",
     "compute_centroids",
     "FastMemError", "Memory", "attention_hash", "attention_hash_varlen", "group_rows", "hash_rows", "hashed_attention",

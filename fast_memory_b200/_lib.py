@@ -50,6 +50,9 @@ _SIGNATURES = {
     "fm_shard_filter_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "fm_shard_filter": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                 c_size_t, c_void_p]),
+    "fm_hashed_attn_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p]),
     "fm_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_void_p]),
     "fm_lse_merge_out": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int,
                                  c_void_p]),

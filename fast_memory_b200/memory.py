@@ -331,6 +331,28 @@ class Memory:
                                       group_off, perm, sm_scale, self.max_bucket_len, key_chunk=key_chunk)
         return o.reshape(Hq, S, d), lse.reshape(Hq, S)
 
+    def query_backward(self, q: torch.Tensor, sm_scale: float, out: torch.Tensor, lse: torch.Tensor, d_out: torch.Tensor,
+                       cu_seqlens_q: Optional[Sequence[int]] = None, q_hashes: Optional[torch.Tensor] = None,
+                       dk: Optional[torch.Tensor] = None, dv: Optional[torch.Tensor] = None
+                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Gradients of :meth:`query` w.r.t. q, k and v for the output gradient ``d_out`` (mem:166-206): ``out`` and
+        ``lse`` are the forward result the caller ended up with (of this memory alone, or merged with other attention:
+        mem:332, 354-378 pass the merged pair).  Returns fp32 ``(dq [Hq, S, d], dk [H, N, d], dv [H, N, d])``; ``dk`` /
+        ``dv`` given are accumulated into.  The projection (hashing) is not differentiated, as in the reference."""
+        dev = L.require_cuda(q, out, lse, d_out)
+        q = q.contiguous()
+        Hq, S, d = q.shape
+        seg_xb, max_rows = self._query_segments(Hq, S, cu_seqlens_q, dev)
+        qf = q.reshape(Hq * S, d)
+        hashes = ops.hash_rows(qf, self.A, seg_xb, self._seg_cb_dev, max_rows) if q_hashes is None else \
+            q_hashes.reshape(-1).to(torch.int32).contiguous()
+        group_off, perm = ops.group_rows(hashes, self.total_buckets, seg_xb, self._seg_cb_dev)
+        dq, dk, dv = ops.hashed_attention_backward(
+            qf, self.k.reshape(-1, d), self.v.reshape(-1, d), self.table, self.bucket_off, group_off, perm, sm_scale,
+            out.reshape(Hq * S, d).contiguous(), lse.reshape(Hq * S).float().contiguous(), d_out.reshape(Hq * S, d).contiguous(),
+            dk=None if dk is None else dk.reshape(-1, d), dv=None if dv is None else dv.reshape(-1, d))
+        return dq.reshape(Hq, S, d), dk.reshape(self.k.shape), dv.reshape(self.k.shape)
+
     def query_from_host(self, q_host: torch.Tensor, sm_scale: float, o_host: torch.Tensor, lse_host: torch.Tensor,
                         n_chunks: int = 4, local: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
                         overlap_calls: bool = False) -> None:

@@ -107,6 +107,41 @@ def hashed_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: t
     return out, lse
 
 
+def hashed_attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: torch.Tensor, bucket_off: torch.Tensor,
+                              group_off: torch.Tensor, perm: torch.Tensor, sm_scale: float, out: torch.Tensor, lse: torch.Tensor,
+                              d_out: torch.Tensor, bucket_kbase: Optional[torch.Tensor] = None,
+                              dk: Optional[torch.Tensor] = None, dv: Optional[torch.Tensor] = None
+                              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of the hashed attention over the gathered rows (mem:166-206 without the dense mask).  Same layouts as
+    :func:`hashed_attention`; ``out`` / ``d_out`` ``[n_q, d]`` in q's dtype, ``lse`` fp32 ``[n_q]`` natural log (the LSE the
+    forward result was normalised with).  Returns fp32 ``(dq [n_q, d], dk [n_k, d], dv [n_k, d])``; pass ``dk`` / ``dv``
+    to accumulate into existing buffers (several shards or memories taking turns)."""
+    dev = L.require_cuda(q, k, v, table, bucket_off, group_off, perm, out, lse, d_out, bucket_kbase, dk, dv)
+    if not (q.dtype == k.dtype == v.dtype == out.dtype == d_out.dtype):
+        raise TypeError("q, k, v, out and d_out must share a dtype")
+    if lse.dtype != torch.float32:
+        raise TypeError("lse must be float32 (natural log)")
+    assert q.dim() == 2 and k.dim() == 2 and v.shape == k.shape and out.shape == q.shape and d_out.shape == q.shape
+    for t in (q, k, v, table, out, lse, d_out):
+        assert t.is_contiguous()
+    assert table.dtype in (torch.int32, torch.int64) and bucket_off.dtype == torch.int64
+    assert group_off.dtype == torch.int32 and perm.dtype == torch.int32
+    n_q, d = q.shape
+    dq = torch.empty(n_q, d, dtype=torch.float32, device=dev)
+    if dk is None:
+        dk = torch.zeros(k.shape, dtype=torch.float32, device=dev)
+    if dv is None:
+        dv = torch.zeros(k.shape, dtype=torch.float32, device=dev)
+    assert dk.dtype == torch.float32 and dv.dtype == torch.float32 and dk.shape == k.shape and dv.shape == k.shape
+    assert dk.is_contiguous() and dv.is_contiguous()
+    L.check(L.lib().fm_hashed_attn_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.dtype_id(q.dtype), d, n_q, k.shape[0],
+                                       bucket_off.numel() - 1, L.ptr(table), table.element_size(), L.ptr(bucket_off),
+                                       L.ptr(bucket_kbase), L.ptr(group_off), L.ptr(perm), float(sm_scale), L.ptr(out),
+                                       L.ptr(lse), L.ptr(d_out), L.ptr(dq), L.ptr(dk), L.ptr(dv), L.stream_ptr(dev)),
+            "fm_hashed_attn_bwd")
+    return dq, dk, dv
+
+
 def lse_merge(out: torch.Tensor, lse: torch.Tensor, block_out: torch.Tensor, block_lse: torch.Tensor) -> None:
     """In place on fp32 ``out`` ``[rows, d]`` / ``lse`` ``[rows]``."""
     dev = L.require_cuda(out, lse, block_out, block_lse)

@@ -124,6 +124,21 @@ int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, int dtype, i
                        int64_t key_chunk, void *workspace, size_t workspace_bytes, fm_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Hashed attention backward over the gathered rows: dq = dS K * sm_scale, dk += dS^T Q * sm_scale, dv += P^T dO with
+ * P = exp(q.k * sm_scale - lse), dS = P * (dO V^T - rowsum(dO * o)).
+ * Replaces: ring_attention_masked_backward, mem:166-206 (dense mask + five einsums), for the key shard described by
+ * k, v, table.  q, o, d_o [n_q_rows, d] and k, v [n_k_rows, d] in `dtype`; table / bucket_off / bucket_kbase /
+ * group_off / perm as in fm_hashed_attn_fwd; lse [n_q_rows] fp32 natural log: the LSE the forward result was
+ * normalised with (it may cover more keys than this shard, e.g. after a merge).  dq [n_q_rows, d] fp32 is written
+ * (zero where the bucket is empty); dk, dv [n_k_rows, d] fp32 are ACCUMULATED (a key sits in several buckets and in
+ * several calls when shards take turns): the caller zeroes them first.
+ * ------------------------------------------------------------------------------------------- */
+int fm_hashed_attn_bwd(const void *q, const void *k, const void *v, int dtype, int d, int64_t n_q_rows, int64_t n_k_rows,
+                       int64_t total_buckets, const void *table, int idx_bytes, const int64_t *bucket_off,
+                       const int32_t *bucket_kbase, const int32_t *group_off, const int32_t *perm, float sm_scale,
+                       const void *o, const float *lse, const void *d_o, float *dq, float *dk, float *dv, fm_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Shard filter of a globally indexed table: for every (head, bucket) row of k_hashes [C, H, Z] (int64
  * GLOBAL key indices) keep the entries in [lo, hi), rebased to the shard (index - lo), slot order kept,
  * packed (head, bucket, slot) into flat_out (room for C*H*Z entries); counts_out [H, C] int64.

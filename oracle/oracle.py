@@ -332,6 +332,35 @@ def compute_centroids(kq: torch.Tensor, centroids: torch.Tensor, n_hashes: int, 
 
 
 # --------------------------------------------------------------------------------------------------
+# Backward of the hashed attention (mem:166-206)
+# --------------------------------------------------------------------------------------------------
+def hashed_attention_backward_dense(q, k, v, table, counts, q_hashes, sm_scale: float, out, lse, d_out):
+    """The reference's backward (``ring_attention_masked_backward``, mem:166-206) for one key shard, in fp64: rebuild
+    the dense mask from the table (mem:174-180), P = exp(S - lse) (mem:190-194), dV, dP, D, dS, dQ, dK (mem:195-205).
+
+    q, out, d_out ``[H, S, d]``; k, v ``[H, N, d]``; table ``[H, C, Zmax]`` key indices with ``counts [H, C]`` valid slots
+    per bucket; q_hashes ``[H, S]``; lse ``[H, S]`` natural log.  Returns float64 ``(dq, dk, dv)``."""
+    H, S, d = q.shape
+    N = k.shape[1]
+    mask = torch.zeros(H, S, N, dtype=torch.bool)
+    for h in range(H):
+        for s_ in range(S):
+            b = int(q_hashes[h, s_])
+            mask[h, s_, table[h, b, :int(counts[h, b])].long()] = True
+    qd, kd, vd, od, gd = q.double(), k.double(), v.double(), out.double(), d_out.double()
+    scores = torch.einsum("hid,hjd->hij", qd, kd) * sm_scale
+    P = torch.exp(scores - lse.double()[..., None])
+    P = torch.where(mask & torch.isfinite(lse)[..., None], P, torch.zeros_like(P))
+    dV = torch.einsum("hij,hid->hjd", P, gd)
+    dP = torch.einsum("hid,hjd->hij", gd, vd)
+    D = (gd * od).sum(-1, keepdim=True)
+    dS = P * (dP - D)
+    dQ = torch.einsum("hij,hjd->hid", dS, kd) * sm_scale
+    dK = torch.einsum("hij,hid->hjd", dS, qd) * sm_scale
+    return dQ, dK, dV
+
+
+# --------------------------------------------------------------------------------------------------
 # Dense local-window attention with LSE (stands in for the undefined ``attention_forward``, mem:302)
 # --------------------------------------------------------------------------------------------------
 def local_window_attention(q, k, v, sm_scale: float, window: int):

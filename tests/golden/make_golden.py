@@ -152,6 +152,34 @@ def dense_ref_case(mem, name, seed):
     print(name, "ok")
 
 
+def backward_case(mem, name, seed):
+    """mem:166-206 (the function under its ``torch.compile`` wrapper, run eagerly) on two key shards of a GLOBAL table
+    with the MERGED forward result of both shards, GQA with 2 groups."""
+    g = torch.Generator().manual_seed(seed)
+    k_heads, n_groups, S, ctx, d, C, Z, W = 2, 2, 24, 128, 32, 8, 40, 2
+    q = torch.randn(1, k_heads * n_groups, S, d, generator=g) * 0.5
+    k = torch.randn(W, 1, k_heads, ctx, d, generator=g) * 0.5
+    v = torch.randn(W, 1, k_heads, ctx, d, generator=g) * 0.5
+    d_out = torch.randn(1, k_heads * n_groups, S, d, generator=g)
+    k_hashes = torch.topk(torch.rand(C, k_heads, W * ctx, generator=g), dim=-1, k=Z)[1]    # global indices
+    q_hashes = torch.randint(C, (k_heads, n_groups, S), generator=g)
+    h_idx = torch.arange(k_heads)
+    sm_scale = d ** -0.5
+    out, lse = None, None
+    for r in range(W):
+        bo, bl = mem.ring_attention_masked_forward_ref(k_hashes, q_hashes, h_idx, q, k[r], v[r], sm_scale, r)
+        out, lse = mem.update_out_and_lse(out, lse, bo, bl)
+    bwd = mem.ring_attention_masked_backward
+    bwd = getattr(bwd, "_torchdynamo_orig_callable", bwd)
+    res = dict(q=q.numpy(), k=k.numpy(), v=v.numpy(), d_out=d_out.numpy(), k_hashes=k_hashes.numpy(), q_hashes=q_hashes.numpy(),
+               sm_scale=np.float64(sm_scale), out=_np(out), lse=_np(lse.squeeze(-1)))
+    for r in range(W):
+        dq, dk, dv = bwd(k_hashes, q_hashes, h_idx, d_out, q, k[r], v[r], out, lse.squeeze(-1), sm_scale, r)
+        res[f"dq_rank{r}"], res[f"dk_rank{r}"], res[f"dv_rank{r}"] = _np(dq), _np(dk), _np(dv)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **res)
+    print(name, "ok")
+
+
 def centroids_case(mem, name, seed):
     g = torch.Generator().manual_seed(seed)
     n_heads, n_groups, ctx, d, C, topk = 4, 2, 300, 32, 8, 12
@@ -177,6 +205,7 @@ def main():
     merge_case(mem, "merge_chain", seed=30)
     dense_ref_case(mem, "dense_ref_two_shards", seed=40)
     centroids_case(mem, "compute_centroids", seed=50)
+    backward_case(mem, "backward_two_shards", seed=60)
 
 
 if __name__ == "__main__":

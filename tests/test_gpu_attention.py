@@ -176,3 +176,60 @@ def test_merge_out_of_place_equals_in_place(dtype):
     o2, l2 = fm.lse_merge_out(a, al, b, bl, out_dtype=dtype)
     assert o2.dtype == dtype and torch.equal(o2, ref_o.to(dtype)) and torch.equal(l2, ref_l)
 
+
+
+def test_backward_matches_reference_golden(golden_dir):
+    """Outputs of the reference's own backward (mem:166-206) per key shard, through the drop-in's pieces: shard filter,
+    grouping, fm_hashed_attn_bwd."""
+    z = np.load(os.path.join(golden_dir, "backward_two_shards.npz"))
+    t = lambda a: torch.from_numpy(np.asarray(a)).to(DEV)
+    q, d_out, out, lse = t(z["q"])[0], t(z["d_out"])[0], t(z["out"])[0], t(z["lse"])[0]
+    k_hashes, q_hashes = t(z["k_hashes"]), t(z["q_hashes"])
+    k_heads, G, S = q_hashes.shape
+    C, d = k_hashes.shape[0], q.shape[-1]
+    qf = q.reshape(k_heads * G * S, d).contiguous()
+    hashes = (q_hashes.reshape(k_heads, G * S) + torch.arange(k_heads, device=DEV)[:, None] * C).reshape(-1).int()
+    group_off, perm = fm.group_rows(hashes, k_heads * C)
+    for r in range(z["k"].shape[0]):
+        k, v = t(z["k"])[r, 0].contiguous(), t(z["v"])[r, 0].contiguous()
+        ctx = k.shape[1]
+        flat, counts = fm.shard_filter(k_hashes, r * ctx, (r + 1) * ctx)
+        bucket_off = torch.zeros(k_heads * C + 1, dtype=torch.int64, device=DEV)
+        bucket_off[1:] = torch.cumsum(counts.reshape(-1), 0)
+        kbase = (torch.arange(k_heads, device=DEV, dtype=torch.int32) * ctx).repeat_interleave(C)
+        dq, dk, dv = fm.hashed_attention_backward(qf, k.reshape(-1, d), v.reshape(-1, d), flat, bucket_off, group_off, perm,
+                                                  float(z["sm_scale"]), out.reshape(-1, d).contiguous(), lse.reshape(-1).contiguous(),
+                                                  d_out.reshape(-1, d).contiguous(), bucket_kbase=kbase)
+        assert (dq.reshape(q.shape).cpu() - torch.from_numpy(z[f"dq_rank{r}"])[0]).abs().max() <= 2e-5
+        assert (dk.reshape(k.shape).cpu() - torch.from_numpy(z[f"dk_rank{r}"])[0]).abs().max() <= 2e-5
+        assert (dv.reshape(v.shape).cpu() - torch.from_numpy(z[f"dv_rank{r}"])[0]).abs().max() <= 2e-5
+
+
+@pytest.mark.parametrize("dtype,d,tol", [(torch.float32, 64, 2e-4), (torch.float32, 256, 2e-4), (torch.bfloat16, 128, 4e-2),
+                                         (torch.float16, 32, 1e-2)])
+def test_memory_query_backward_vs_oracle(dtype, d, tol):
+    """Memory.query + Memory.query_backward against the dense restatement: ragged query blocks (17 and more queries in
+    a bucket), buckets nobody asks for, keys that sit in several buckets, accumulation into given dk / dv."""
+    g = torch.Generator().manual_seed(d)
+    H, N, S, C, Z = 2, 700, 90, 6, 150
+    k = (torch.randn(H, N, d, generator=g) * 0.5).to(dtype)
+    v = (torch.randn(H, N, d, generator=g) * 0.5).to(dtype)
+    q = (torch.randn(H, S, d, generator=g) * 0.5).to(dtype)
+    d_out = torch.randn(H, S, d, generator=g).to(dtype)
+    A = torch.nn.functional.normalize(torch.randn(H, C, d, generator=g), dim=-1).to(dtype)
+    mem = fm.Memory.build(k.to(DEV), v.to(DEV), A=A.to(DEV), bucket_size=Z)
+    sm = d ** -0.5
+    o, lse = mem.query(q.to(DEV), sm)
+    dq, dk, dv = mem.query_backward(q.to(DEV), sm, o, lse, d_out.to(DEV))
+    table = torch.stack([mem.table_of(h).long().cpu() for h in range(H)])
+    counts = torch.full((H, C), table.shape[-1])
+    hashes = mem.hash_queries(q.to(DEV)).long().cpu()
+    rq, rk, rv = O.hashed_attention_backward_dense(q, k, v, table, counts, hashes, sm, o.cpu(), lse.cpu(), d_out)
+    scale = lambda x: max(1.0, float(x.abs().max()))
+    assert (dq.cpu().double() - rq).abs().max() <= tol * scale(rq)
+    assert (dk.cpu().double() - rk).abs().max() <= tol * scale(rk)
+    assert (dv.cpu().double() - rv).abs().max() <= tol * scale(rv)
+    # accumulation: a second call into the same buffers doubles them
+    dq2, dk2, dv2 = mem.query_backward(q.to(DEV), sm, o, lse, d_out.to(DEV), dk=dk.clone(), dv=dv.clone())
+    assert torch.allclose(dk2, 2 * dk, rtol=1e-4, atol=1e-5) and torch.allclose(dv2, 2 * dv, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(dq2, dq, rtol=1e-5, atol=1e-6)

@@ -141,3 +141,36 @@ def test_kmeans_restatement_invariants():
     U = torch.from_numpy(O.unit_rows(X))
     obj = lambda c: float((U @ torch.nn.functional.normalize(c.float(), dim=-1).T).max(-1).values.mean())
     assert obj(A) >= obj(O.spherical_kmeans(X, X[:8], 1)) - 1e-3 >= obj(X[:8]) - 2e-3
+
+
+def _padded_table(flat, counts):
+    """(flat (head, bucket, slot) indices, counts [H, C]) -> table [H, C, max count] padded with 0."""
+    H, C = counts.shape
+    table = torch.zeros(H, C, max(int(counts.max()), 1), dtype=torch.long)
+    pos = 0
+    for h in range(H):
+        for c in range(C):
+            n = int(counts[h, c])
+            table[h, c, :n] = flat[pos:pos + n]
+            pos += n
+    return table
+
+
+def test_backward_restatement_matches_reference(golden_dir):
+    """mem:166-206 run eagerly on two key shards with the merged forward result; GQA folded into the query axis."""
+    z = np.load(os.path.join(golden_dir, "backward_two_shards.npz"))
+    t = lambda a: torch.from_numpy(np.asarray(a))
+    q, d_out, out, lse = t(z["q"])[0], t(z["d_out"])[0], t(z["out"])[0], t(z["lse"])[0]       # [Hq, S, d], [Hq, S]
+    k_hashes, q_hashes = t(z["k_hashes"]), t(z["q_hashes"])
+    k_heads, G, S = q_hashes.shape
+    d = q.shape[-1]
+    fold = lambda x: x.reshape(k_heads, G * S, *x.shape[2:])
+    for r in range(z["k"].shape[0]):
+        k, v = t(z["k"])[r, 0], t(z["v"])[r, 0]
+        flat, counts = O.shard_filter(k_hashes, r, k.shape[1])
+        dq, dk, dv = O.hashed_attention_backward_dense(fold(q), k, v, _padded_table(flat, counts), counts,
+                                                       q_hashes.reshape(k_heads, G * S), float(z["sm_scale"]),
+                                                       fold(out), fold(lse), fold(d_out))
+        assert torch.allclose(dq.float().reshape(q.shape), t(z[f"dq_rank{r}"])[0], atol=2e-6, rtol=1e-5)
+        assert torch.allclose(dk.float(), t(z[f"dk_rank{r}"])[0], atol=2e-6, rtol=1e-5)
+        assert torch.allclose(dv.float(), t(z[f"dv_rank{r}"])[0], atol=2e-6, rtol=1e-5)
