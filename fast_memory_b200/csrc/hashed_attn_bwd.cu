@@ -9,7 +9,7 @@
 //     dQ = dS K * sm_scale,  dK += dS^T Q * sm_scale
 // One CTA per bucket walks the bucket's query blocks (16 queries) and key tiles (64 keys) on the CUDA cores in fp32.
 // A query lies in exactly one bucket, so dQ rows are written once; a key lies in several buckets, so dK and dV are
-// accumulated with fp32 atomics into buffers the caller has zeroed (or is accumulating shard after shard).
+// accumulated with fp32 (16-byte vector) atomics into buffers the caller has zeroed (or is accumulating shard after shard).
 // This is the training-time companion of the forward kernels, written for parity first: no tensor cores yet.
 #include "attn_common.cuh"
 
@@ -35,7 +35,9 @@ struct BwdParams {
     float *dq, *dk, *dv;
 };
 
-template <typename T>
+// PASSES = ceil(d / 128): in the d-wide phases a lane owns four consecutive columns of every 128-column pass and a warp
+// a quarter of the tile's keys, so that dK and dV go out as 16-byte vector atomics (a quarter of the atomic traffic).
+template <typename T, int PASSES>
 __global__ void __launch_bounds__(kBwdThreads)
 attn_bwd_kernel(BwdParams p, int d)
 {
@@ -59,7 +61,6 @@ attn_bwd_kernel(BwdParams p, int d)
     const int64_t kbase = p.bucket_kbase ? p.bucket_kbase[gb] : 0;
     const T *qg = reinterpret_cast<const T *>(p.q), *og = reinterpret_cast<const T *>(p.o), *gg = reinterpret_cast<const T *>(p.d_o);
     const T *kg = reinterpret_cast<const T *>(p.k), *vg = reinterpret_cast<const T *>(p.v);
-    const int cpt = (d + kBwdThreads - 1) / kBwdThreads;      // columns per thread in the d-wide phases (1 or 2)
 
     for (int qb = 0; qb < nq_all; qb += kBwdQ) {
         const int nq = min(kBwdQ, nq_all - qb);
@@ -89,9 +90,11 @@ attn_bwd_kernel(BwdParams p, int d)
                 Lq[qi] = qi < nq ? p.lse[p.perm[q0 + qb + qi]] : INFINITY;       // +inf: P = 0 for rows that do not exist
             }
         }
-        float dq_acc[kBwdQ][2];
+        float dq_acc[PASSES][kBwdQ][4];                      // this warp's keys only; folded over the warps at the end
 #pragma unroll
-        for (int a = 0; a < kBwdQ; ++a) dq_acc[a][0] = dq_acc[a][1] = 0.f;
+        for (int u = 0; u < PASSES; ++u)
+#pragma unroll
+            for (int a = 0; a < kBwdQ; ++a) dq_acc[u][a][0] = dq_acc[u][a][1] = dq_acc[u][a][2] = dq_acc[u][a][3] = 0.f;
 
         for (int64_t t0 = 0; t0 < len; t0 += kBwdK) {
             const int nk = int(min(int64_t(kBwdK), len - t0));
@@ -137,40 +140,55 @@ attn_bwd_kernel(BwdParams p, int d)
                 }
             }
             __syncthreads();
-            // the d-wide phases: thread -> column(s) c
+            // the d-wide phases: warp -> keys j = warp, warp + 4, ...; lane -> columns 4 lane .. 4 lane + 3 of each pass
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int c = t + u * kBwdThreads;
-                if (u < cpt && c < d) {
-                    // dQ += dS K
-                    for (int j = 0; j < nk; ++j) {
-                        const float kv = Ks[j * ld + c];
-#pragma unroll
-                        for (int a = 0; a < kBwdQ; ++a) dq_acc[a][u] = fmaf(Ss[a * kPLd + j], kv, dq_acc[a][u]);
-                    }
-                    // dK += dS^T Q * scale, dV += P^T dO: one key row at a time, consecutive threads = consecutive columns
-                    for (int j = 0; j < nk; ++j) {
-                        float dkv = 0.f, dvv = 0.f;
+            for (int u = 0; u < PASSES; ++u) {
+                const int c = u * 128 + lane * 4;
+                if (c < d) {
+                    for (int j = warp; j < nk; j += kBwdThreads / 32) {
+                        const float k0 = Ks[j * ld + c], k1 = Ks[j * ld + c + 1], k2 = Ks[j * ld + c + 2], k3 = Ks[j * ld + c + 3];
+                        float4 dk4 = make_float4(0.f, 0.f, 0.f, 0.f), dv4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                         for (int a = 0; a < kBwdQ; ++a) {
-                            dkv = fmaf(Ss[a * kPLd + j], Qs[a * d + c], dkv);
-                            dvv = fmaf(Ps[a * kPLd + j], Gs[a * d + c], dvv);
+                            const float ds = Ss[a * kPLd + j], pv = Ps[a * kPLd + j];
+                            const float4 q4 = *reinterpret_cast<const float4 *>(Qs + a * d + c);
+                            const float4 g4 = *reinterpret_cast<const float4 *>(Gs + a * d + c);
+                            dq_acc[u][a][0] = fmaf(ds, k0, dq_acc[u][a][0]);      // dQ += dS K
+                            dq_acc[u][a][1] = fmaf(ds, k1, dq_acc[u][a][1]);
+                            dq_acc[u][a][2] = fmaf(ds, k2, dq_acc[u][a][2]);
+                            dq_acc[u][a][3] = fmaf(ds, k3, dq_acc[u][a][3]);
+                            dk4.x = fmaf(ds, q4.x, dk4.x); dk4.y = fmaf(ds, q4.y, dk4.y);      // dK += dS^T Q
+                            dk4.z = fmaf(ds, q4.z, dk4.z); dk4.w = fmaf(ds, q4.w, dk4.w);
+                            dv4.x = fmaf(pv, g4.x, dv4.x); dv4.y = fmaf(pv, g4.y, dv4.y);      // dV += P^T dO
+                            dv4.z = fmaf(pv, g4.z, dv4.z); dv4.w = fmaf(pv, g4.w, dv4.w);
                         }
                         const size_t off = size_t(rows_s[j]) * d + c;
-                        atomicAdd(p.dk + off, dkv * p.sm_scale);
-                        atomicAdd(p.dv + off, dvv);
+                        dk4.x *= p.sm_scale; dk4.y *= p.sm_scale; dk4.z *= p.sm_scale; dk4.w *= p.sm_scale;
+                        atomicAdd(reinterpret_cast<float4 *>(p.dk + off), dk4);
+                        atomicAdd(reinterpret_cast<float4 *>(p.dv + off), dv4);
                     }
                 }
             }
         }
+        // fold the four warps' dQ through shared memory (the key tiles are done with)
+        __syncthreads();
+        float *fold = Ks;                                    // [4][kBwdQ][d] <= the K and V tiles
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int c = t + u * kBwdThreads;
-            if (u < cpt && c < d) {
+        for (int u = 0; u < PASSES; ++u) {
+            const int c = u * 128 + lane * 4;
+            if (c < d) {
 #pragma unroll
                 for (int a = 0; a < kBwdQ; ++a)
-                    if (a < nq) p.dq[size_t(p.perm[q0 + qb + a]) * d + c] = dq_acc[a][u] * p.sm_scale;
+                    *reinterpret_cast<float4 *>(fold + (warp * kBwdQ + a) * d + c) =
+                        make_float4(dq_acc[u][a][0], dq_acc[u][a][1], dq_acc[u][a][2], dq_acc[u][a][3]);
             }
+        }
+        __syncthreads();
+        for (int e = t; e < nq * d; e += kBwdThreads) {
+            const int a = e / d, c = e - a * d;
+            const float sum = (fold[(0 * kBwdQ + a) * d + c] + fold[(1 * kBwdQ + a) * d + c]) +
+                              (fold[(2 * kBwdQ + a) * d + c] + fold[(3 * kBwdQ + a) * d + c]);
+            p.dq[size_t(p.perm[q0 + qb + a]) * d + c] = sum * p.sm_scale;
         }
     }
 }
@@ -178,8 +196,13 @@ attn_bwd_kernel(BwdParams p, int d)
 template <typename T> static int launch_bwd(const BwdParams &p, int d, int64_t total_buckets, cudaStream_t st)
 {
     const size_t smem = sizeof(float) * (2 * size_t(kBwdQ) * d + 2 * size_t(kBwdK) * (d + 1) + 2 * kBwdQ * kPLd + 2 * kBwdQ);
-    FM_CUDA_OK(cudaFuncSetAttribute(attn_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attn_bwd_kernel<T><<<(unsigned)total_buckets, kBwdThreads, smem, st>>>(p, d);
+    if (d <= 128) {
+        FM_CUDA_OK(cudaFuncSetAttribute(attn_bwd_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attn_bwd_kernel<T, 1><<<(unsigned)total_buckets, kBwdThreads, smem, st>>>(p, d);
+    } else {
+        FM_CUDA_OK(cudaFuncSetAttribute(attn_bwd_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attn_bwd_kernel<T, 2><<<(unsigned)total_buckets, kBwdThreads, smem, st>>>(p, d);
+    }
     FM_LAUNCHED("attn_bwd_kernel");
     return FM_OK;
 }
