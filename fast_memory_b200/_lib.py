@@ -12,7 +12,7 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfastmem_b200.so")
+LIB_PATH = os.environ.get("FASTMEM_B200_LIB") or os.path.join(_HERE, "libfastmem_b200.so")      # another build of the library
 
 F32, BF16, F16 = 0, 1, 2
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}

@@ -1,7 +1,7 @@
 // Tensor-core hashed attention for 16-bit inputs (bf16 / fp16, head dim 64 or 128).
 //
 // The path is HBM-bound (arithmetic intensity ~ queries per bucket, far below the ridge), so the kernel
-// is built around the gather: each CTA streams the K and V rows of its bucket chunk through a 3-stage
+// is built around the gather: each warp streams its share of the K and V rows of the bucket chunk through a 3-stage
 // cp.async pipeline of 64-key tiles (16-byte pieces, XOR-swizzled rows), keeping ~64 KB of row fetches in
 // flight, and the math rides along on mma.sync m16n8k16:
 //   * a work item holds <= 32 queries = one or two MMA row tiles that share every gathered key tile (a bucket with 17
@@ -26,8 +26,8 @@ constexpr int kMaxQ = 32;                   // queries per work item (two row ti
 
 template <int D> struct MmaCfg {
     static constexpr int CPR = D / 8;                           // 16-byte chunks per row
-    static constexpr int ROWS_PER_PASS = kThreads / CPR;        // rows covered by one sweep of the CTA
-    static constexpr int PASSES = kTK / ROWS_PER_PASS;          // copies per thread per matrix per tile
+    static constexpr int ROWS_PER_PASS = 32 / CPR;              // rows covered by one sweep of a warp over its 16 keys
+    static constexpr int PASSES = 16 / ROWS_PER_PASS;           // copies per thread per matrix per tile
     static constexpr int TILE_BYTES = kTK * D * 2;              // one K (or V) tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int ACC_LD = D + 4;                        // combine buffer row stride (floats)
@@ -49,8 +49,10 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
     const char *vg = reinterpret_cast<const char *>(p.v);
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t q_smem = smem_base + kStages * C::STAGE_BYTES;
-    const int my_c = t % C::CPR;                                 // chunk column this thread copies
-    const int my_r = t / C::CPR;                                 // first row this thread copies
+    // every warp gathers the 16 keys of the tile it will itself consume: no CTA-wide barrier inside the tile loop,
+    // the four warps drift apart and hide one another's latencies
+    const int my_c = lane % C::CPR;                              // chunk column this thread copies
+    const int my_r = warp * 16 + lane / C::CPR;                  // first row this thread copies
 
     const int gb = it.x, q_begin = it.y, kc = it.z, nkc = it.w;
     const int64_t kb = p.bucket_off[gb];
@@ -81,7 +83,8 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
             if (r < nq) val = *reinterpret_cast<const uint4 *>(qg + size_t(p.perm[q_begin + r]) * D + c * 8);
             *reinterpret_cast<uint4 *>(smem + kStages * C::STAGE_BYTES + swz<D>(r, c)) = val;
-        }                                                        // visible after the first barrier of the tile loop
+        }
+        __syncthreads();                                         // the query tile is shared by the four warps
     }
 
     // ---- gather pipeline -----------------------------------------------------------------------------
@@ -136,7 +139,7 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
 
     for (int tile = 0; tile < n_tiles; ++tile) {
         cp_async_wait<kStages - 2>();
-        __syncthreads();                                     // tile landed; the stage refilled below is free
+        __syncwarp();                                        // this warp's rows of the tile landed; its rows of the stage refilled below are free
         issue(tile + kStages - 1);
         load_rows(tile + kStages);
         const int st = tile % kStages;
