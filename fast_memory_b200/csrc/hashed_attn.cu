@@ -349,7 +349,11 @@ extern "C" int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, i
 
     // the tensor-core kernel tracks the row maximum before scaling, which needs a positive scale
     const bool use_mma = attn_mma_supported(dtype, d) && sm_scale > 0.f;
-    p.q_block = use_mma ? 32 : kQB;
+    // items of up to 32 queries gather a bucket once for two row tiles but take twice as long as a 16-query item: with
+    // plenty of (bucket, queries) groups per CTA that is a pure gain, with few (decode) the long items leave CTAs idle
+    // at the end of the launch, so the queries are cut into 16-query items there
+    const int64_t groups_bound = std::min<int64_t>(total_buckets, n_q_rows);
+    p.q_block = use_mma ? (groups_bound >= int64_t(24) * sms ? 32 : 16) : kQB;
 
     FM_CUDA_OK(cudaMemsetAsync(p.counters, 0, 8, st));
     if (L.nkc_max > 1) FM_CUDA_OK(cudaMemsetAsync(p.qparts, 0, size_t(n_q_rows) * 4, st));
@@ -357,7 +361,7 @@ extern "C" int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, i
     FM_LAUNCHED("attn_plan_kernel");
 
     int rc;
-    int grid = (int)std::min<int64_t>(L.max_items, int64_t(sms) * (use_mma ? 2 : 4));
+    int grid = (int)std::min<int64_t>(L.max_items, int64_t(sms) * (use_mma ? 3 : 4));
     if (use_mma) rc = launch_attn_mma(p, dtype, d, grid, st);
     else if (dtype == FM_F32) rc = dispatch_simt<float>(p, d, grid, st);
     else if (dtype == FM_BF16) rc = dispatch_simt<__nv_bfloat16>(p, d, grid, st);

@@ -1,15 +1,18 @@
 // Tensor-core hashed attention for 16-bit inputs (bf16 / fp16, head dim 64 or 128).
 //
-// The path is HBM-bound (arithmetic intensity ~ queries per bucket, far below the ridge), so the kernel
-// is built around the gather: each warp streams its share of the K and V rows of the bucket chunk through a 3-stage
-// cp.async pipeline of 64-key tiles (16-byte pieces, XOR-swizzled rows), keeping ~64 KB of row fetches in
-// flight, and the math rides along on mma.sync m16n8k16:
-//   * a work item holds <= 32 queries = one or two MMA row tiles that share every gathered key tile (a bucket with 17
-//     to 32 queries costs one gather, not two); the 4 warps split every key tile four ways (16 keys each), so all
-//     warps do equal work however few queries the bucket has;
+// The path is HBM / L2-bound (arithmetic intensity ~ queries per bucket, far below the ridge), so the kernel is built
+// around the gather and around occupancy: 128-thread CTAs that fit three to an SM (<= 168 registers, two stages of a
+// 64-key K tile and V tile), each warp streaming the K and V rows it needs through its own cp.async pipeline
+// (16-byte pieces, XOR-swizzled rows), and the math rides along on mma.sync m16n8k16:
+//   * a work item holds <= 32 queries.  Up to 16 queries (one MMA row tile): the 4 warps split every key tile four
+//     ways (16 keys each) and each warp gathers exactly the keys it consumes - no CTA-wide barrier in the tile loop,
+//     the warps drift apart and hide one another's latencies.  17 to 32 queries (two row tiles): warps 2h and 2h+1
+//     form a pair that shares the 32 keys of half h of every tile - each gathers 16 of them, a 64-thread named
+//     barrier per tile hands them over, warp 2h+r computes row tile r over the 32 keys - so the bucket is gathered
+//     once, not twice, with the register footprint of a single row tile;
 //   * S = Q K^T from ldmatrix'd K rows, base-2 online softmax per warp in registers, P rounded to the
 //     input dtype and fed straight back as the A operand of P V (V through ldmatrix.trans);
-//   * at the end of the item the four (m, l, acc) states are folded through shared memory and written out
+//   * at the end of the item the warps' (m, l, acc) states are folded through shared memory and written out
 //     through the grouping permutation (or as a partial when the bucket is split over CTAs).
 // Rounding points follow the reference kernel (triton_kernel.py:248-263).
 #include "attn_common.cuh"
@@ -21,8 +24,9 @@ namespace {
 
 constexpr int kThreads = 128;
 constexpr int kTK = 64;                     // keys per tile
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr int kMaxQ = 32;                   // queries per work item (two row tiles)
+constexpr int kCtasPerSm = 3;
 
 template <int D> struct MmaCfg {
     static constexpr int CPR = D / 8;                           // 16-byte chunks per row
@@ -31,26 +35,34 @@ template <int D> struct MmaCfg {
     static constexpr int TILE_BYTES = kTK * D * 2;              // one K (or V) tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int ACC_LD = D + 4;                        // combine buffer row stride (floats)
-    static constexpr int Q_BYTES = kMaxQ * D * 2;               // query tile of an item with two row tiles
-    static constexpr size_t smem = size_t(kStages) * STAGE_BYTES + Q_BYTES;
-    static_assert(4 * kMaxQ * ACC_LD * 4 + 4 * kMaxQ * 8 <= kStages * STAGE_BYTES, "combine buffer must fit in the tile stages");
+    static constexpr size_t smem = size_t(kStages) * STAGE_BYTES;
+    static_assert(4 * 16 * ACC_LD * 4 + 4 * 16 * 8 <= kStages * STAGE_BYTES, "combine buffer must fit in the tile stages");
 };
 
-// One work item with MT row tiles of 16 queries.
-template <typename T, int D, int MT>
+__device__ __forceinline__ void pair_barrier(int pair)
+{
+    // immediate barrier numbers: a register operand makes the compiler reserve all sixteen
+    if (pair == 0) asm volatile("bar.sync 1, 64;" ::: "memory");
+    else asm volatile("bar.sync 2, 64;" ::: "memory");
+}
+
+// One work item.  PAIR = false: one row tile of 16 queries, every warp takes 16 keys of each tile.  PAIR = true: two
+// row tiles; warp w computes row tile (w & 1) over the 32 keys of half (w >> 1) of each tile, gathered by the pair.
+template <typename T, int D, bool PAIR>
 __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *smem, const int4 it, const int nq)
 {
     using C = MmaCfg<D>;
-    constexpr int NQ = 16 * MT;
+    constexpr int NQ = PAIR ? 32 : 16;
+    constexpr int SUB = PAIR ? 2 : 1;                            // 16-key slices a warp consumes per tile
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int g = lane >> 2, tq = lane & 3;
     const T *qg = reinterpret_cast<const T *>(p.q);
     const char *kg = reinterpret_cast<const char *>(p.k);
     const char *vg = reinterpret_cast<const char *>(p.v);
     const uint32_t smem_base = smem_u32(smem);
-    const uint32_t q_smem = smem_base + kStages * C::STAGE_BYTES;
-    // every warp gathers the 16 keys of the tile it will itself consume: no CTA-wide barrier inside the tile loop,
-    // the four warps drift apart and hide one another's latencies
+    const int rt = PAIR ? (warp & 1) : 0;                        // row tile of this warp
+    const int wk0 = PAIR ? (warp >> 1) * 32 : warp * 16;         // first key of the tile this warp consumes
+    // every warp gathers 16 keys of each tile: the ones it consumes itself, or half of the ones its pair consumes
     const int my_c = lane % C::CPR;                              // chunk column this thread copies
     const int my_r = warp * 16 + lane / C::CPR;                  // first row this thread copies
 
@@ -63,10 +75,10 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
     const int64_t kbase = p.bucket_kbase ? p.bucket_kbase[gb] : 0;
     const int64_t tbl0 = kb + k0;
 
-    // ---- Q (A operand) through the permutation: one row tile stays in registers, two go through shared memory ----
-    uint32_t qf[MT == 1 ? D / 16 : 1][4];
-    if constexpr (MT == 1) {
-        const int r0 = g, r1 = g + 8;
+    // ---- Q (A operand) of the warp's row tile, through the permutation, in registers ----
+    uint32_t qf[D / 16][4];
+    {
+        const int r0 = rt * 16 + g, r1 = r0 + 8;
         const T *q0 = r0 < nq ? qg + size_t(p.perm[q_begin + r0]) * D : nullptr;
         const T *q1 = r1 < nq ? qg + size_t(p.perm[q_begin + r1]) * D : nullptr;
 #pragma unroll
@@ -77,14 +89,6 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
             qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t *>(q0 + c + 8) : 0u;
             qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t *>(q1 + c + 8) : 0u;
         }
-    } else {
-        for (int e = t; e < NQ * C::CPR; e += kThreads) {
-            const int r = e / C::CPR, c = e - r * C::CPR;
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (r < nq) val = *reinterpret_cast<const uint4 *>(qg + size_t(p.perm[q_begin + r]) * D + c * 8);
-            *reinterpret_cast<uint4 *>(smem + kStages * C::STAGE_BYTES + swz<D>(r, c)) = val;
-        }
-        __syncthreads();                                         // the query tile is shared by the four warps
     }
 
     // ---- gather pipeline -----------------------------------------------------------------------------
@@ -125,184 +129,155 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
         load_rows(s + 1);
     }
 
-    float m_run[MT][2], l_run[MT][2];
-    float acc[MT][D / 8][4];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {1.f, 1.f};
+    float acc[D / 8][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        m_run[mt][0] = m_run[mt][1] = -INFINITY;
-        l_run[mt][0] = l_run[mt][1] = 1.f;
+    for (int n = 0; n < D / 8; ++n)
 #pragma unroll
-        for (int n = 0; n < D / 8; ++n)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[mt][n][e] = 0.f;
-    }
+        for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
 
     for (int tile = 0; tile < n_tiles; ++tile) {
         cp_async_wait<kStages - 2>();
-        __syncwarp();                                        // this warp's rows of the tile landed; its rows of the stage refilled below are free
+        // the rows of the tile landed and the stage refilled below is free: a matter of this warp alone, or of the pair
+        if constexpr (PAIR) pair_barrier(warp >> 1);
+        else __syncwarp();
         issue(tile + kStages - 1);
         load_rows(tile + kStages);
         const int st = tile % kStages;
         const uint32_t ks_base = smem_base + st * C::STAGE_BYTES;
         const uint32_t vs_base = ks_base + C::TILE_BYTES;
-        const int wk = warp * 16;                            // this warp's 16 keys of the tile
 
-        // S = Q K^T for 16 MT queries x 16 keys
-        float s[MT][2][4];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+        for (int sub = 0; sub < SUB; ++sub) {
+            const int wk = wk0 + sub * 16;                       // 16 keys of the tile
+
+            // S = Q K^T for 16 queries x 16 keys; even and odd k-steps accumulate separately: four independent
+            // MMA chains instead of two
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) s[mt][n][e] = 0.f;
-        float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
-            const int j = wk + (lane & 7) + ((lane >> 4) << 3);
-            const int c = ks * 2 + ((lane >> 3) & 1);
-            uint32_t b[4];
-            ldmatrix_x4(b, ks_base + swz<D>(j, c));
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                if constexpr (MT == 1) {
-                    // even and odd k-steps accumulate separately: four independent MMA chains instead of two
-                    if (ks & 1) {
-                        mma16816<T>(s_odd[0], qf[ks], b[0], b[1]);
-                        mma16816<T>(s_odd[1], qf[ks], b[2], b[3]);
-                    } else {
-                        mma16816<T>(s[mt][0], qf[ks], b[0], b[1]);
-                        mma16816<T>(s[mt][1], qf[ks], b[2], b[3]);
-                    }
+            for (int ks = 0; ks < D / 16; ++ks) {
+                // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+                const int j = wk + (lane & 7) + ((lane >> 4) << 3);
+                const int c = ks * 2 + ((lane >> 3) & 1);
+                uint32_t b[4];
+                ldmatrix_x4(b, ks_base + swz<D>(j, c));
+                if (ks & 1) {
+                    mma16816<T>(s_odd[0], qf[ks], b[0], b[1]);
+                    mma16816<T>(s_odd[1], qf[ks], b[2], b[3]);
                 } else {
-                    // matrices: (rows 0-7, d lo), (rows 8-15, d lo), (rows 0-7, d hi), (rows 8-15, d hi) of the row tile
-                    uint32_t qa[4];
-                    ldmatrix_x4(qa, q_smem + swz<D>(mt * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), ks * 2 + (lane >> 4)));
-                    mma16816<T>(s[mt][0], qa, b[0], b[1]);
-                    mma16816<T>(s[mt][1], qa, b[2], b[3]);
+                    mma16816<T>(s[0], qf[ks], b[0], b[1]);
+                    mma16816<T>(s[1], qf[ks], b[2], b[3]);
                 }
             }
-        }
-        if constexpr (MT == 1) {
 #pragma unroll
             for (int n = 0; n < 2; ++n)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) s[0][n][e] += s_odd[n][e];
-        }
-        // mask (only the last tile can be partial), online softmax in the scaled base-2 domain
-        // (rows g and g + 8 of each row tile; this thread's keys: wk + 8 n + 2 tq + {0, 1})
-        if (tile == n_tiles - 1) {
-            const int live = chunk_len - tile * kTK;
+                for (int e = 0; e < 4; ++e) s[n][e] += s_odd[n][e];
+            // mask (only the last tile can be partial), online softmax in the scaled base-2 domain
+            // (rows g and g + 8 of the row tile; this thread's keys: wk + 8 n + 2 tq + {0, 1})
+            if (tile == n_tiles - 1) {
+                const int live = chunk_len - tile * kTK;
 #pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const int jk = wk + n * 8 + tq * 2;
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    if (jk >= live) { s[mt][n][0] = -INFINITY; s[mt][n][2] = -INFINITY; }
-                    if (jk + 1 >= live) { s[mt][n][1] = -INFINITY; s[mt][n][3] = -INFINITY; }
+                for (int n = 0; n < 2; ++n) {
+                    const int jk = wk + n * 8 + tq * 2;
+                    if (jk >= live) { s[n][0] = -INFINITY; s[n][2] = -INFINITY; }
+                    if (jk + 1 >= live) { s[n][1] = -INFINITY; s[n][3] = -INFINITY; }
                 }
             }
-        }
-        uint32_t pa[MT][4];
-        float alpha[MT][2];
-        bool moved = false;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
+            uint32_t pa[4];
+            float alpha[2];
+            bool moved = false;
             float mx[2];
-            mx[0] = fmaxf(fmaxf(s[mt][0][0], s[mt][0][1]), fmaxf(s[mt][1][0], s[mt][1][1]));
-            mx[1] = fmaxf(fmaxf(s[mt][0][2], s[mt][0][3]), fmaxf(s[mt][1][2], s[mt][1][3]));
+            mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+            mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                const float m_new = fmaxf(m_run[mt][r], mx[r] * p.scale2);      // scale2 > 0 keeps the order
+                const float m_new = fmaxf(m_run[r], mx[r] * p.scale2);          // scale2 > 0 keeps the order
                 const float m_sub = m_new > -INFINITY ? m_new : 0.f;            // nothing live yet: p = 2^-inf = 0
-                alpha[mt][r] = fast_exp2(m_run[mt][r] - m_sub);
-                const float p00 = fast_exp2(fmaf(s[mt][0][2 * r], p.scale2, -m_sub));
-                const float p01 = fast_exp2(fmaf(s[mt][0][2 * r + 1], p.scale2, -m_sub));
-                const float p10 = fast_exp2(fmaf(s[mt][1][2 * r], p.scale2, -m_sub));
-                const float p11 = fast_exp2(fmaf(s[mt][1][2 * r + 1], p.scale2, -m_sub));
+                alpha[r] = fast_exp2(m_run[r] - m_sub);
+                const float p00 = fast_exp2(fmaf(s[0][2 * r], p.scale2, -m_sub));
+                const float p01 = fast_exp2(fmaf(s[0][2 * r + 1], p.scale2, -m_sub));
+                const float p10 = fast_exp2(fmaf(s[1][2 * r], p.scale2, -m_sub));
+                const float p11 = fast_exp2(fmaf(s[1][2 * r + 1], p.scale2, -m_sub));
                 float sum = (p00 + p01) + (p10 + p11);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                l_run[mt][r] = l_run[mt][r] * alpha[mt][r] + sum;
-                m_run[mt][r] = m_new;
-                pa[mt][r] = pack2<T>(p00, p01);                  // keys 0-7 of the warp's slice
-                pa[mt][2 + r] = pack2<T>(p10, p11);              // keys 8-15
-                moved = moved || alpha[mt][r] != 1.f;
+                l_run[r] = l_run[r] * alpha[r] + sum;
+                m_run[r] = m_new;
+                pa[r] = pack2<T>(p00, p01);                      // keys 0-7 of the slice
+                pa[2 + r] = pack2<T>(p10, p11);                  // keys 8-15
+                moved = moved || alpha[r] != 1.f;
             }
-        }
-        // the running maxima settle after a few tiles; rescale the accumulators only when one moved
-        if (__any_sync(0xffffffffu, moved)) {
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+            // the running maxima settle after a few tiles; rescale the accumulators only when one moved
+            if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
                 for (int n = 0; n < D / 8; ++n) {
-                    acc[mt][n][0] *= alpha[mt][0];
-                    acc[mt][n][1] *= alpha[mt][0];
-                    acc[mt][n][2] *= alpha[mt][1];
-                    acc[mt][n][3] *= alpha[mt][1];
+                    acc[n][0] *= alpha[0];
+                    acc[n][1] *= alpha[0];
+                    acc[n][2] *= alpha[1];
+                    acc[n][3] *= alpha[1];
                 }
-        }
-        // acc += P V  (k = the warp's 16 keys, n = head dim)
+            }
+            // acc += P V  (k = the slice's 16 keys, n = head dim)
 #pragma unroll
-        for (int n2 = 0; n2 < D / 16; ++n2) {
-            // matrices: (keys 0-7, d n2*16 + 0-7), (keys 8-15, same d), (keys 0-7, d + 8), (keys 8-15, d + 8)
-            const int j = wk + (lane & 7) + (((lane >> 3) & 1) << 3);
-            const int c = n2 * 2 + (lane >> 4);
-            uint32_t b[4];
-            ldmatrix_x4_trans(b, vs_base + swz<D>(j, c));
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                mma16816<T>(acc[mt][2 * n2], pa[mt], b[0], b[1]);
-                mma16816<T>(acc[mt][2 * n2 + 1], pa[mt], b[2], b[3]);
+            for (int n2 = 0; n2 < D / 16; ++n2) {
+                // matrices: (keys 0-7, d n2*16 + 0-7), (keys 8-15, same d), (keys 0-7, d + 8), (keys 8-15, d + 8)
+                const int j = wk + (lane & 7) + (((lane >> 3) & 1) << 3);
+                const int c = n2 * 2 + (lane >> 4);
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vs_base + swz<D>(j, c));
+                mma16816<T>(acc[2 * n2], pa, b[0], b[1]);
+                mma16816<T>(acc[2 * n2 + 1], pa, b[2], b[3]);
             }
         }
     }
     cp_async_wait<0>();
     __syncthreads();                                         // all tiles consumed: the stages become the combine buffer
 
-    // ---- fold the four warps' states ---------------------------------------------------------------------
-    float *acc_s = reinterpret_cast<float *>(smem);          // [4][NQ][ACC_LD]
-    float *ml_s = acc_s + 4 * NQ * C::ACC_LD;                 // [4][NQ][2]
+    // ---- fold the warps' states: four per query (PAIR = false), two per query (the two key halves of its row tile) ----
+    float *acc_s = reinterpret_cast<float *>(smem);          // [4 warps][16][ACC_LD]
+    float *ml_s = acc_s + 4 * 16 * C::ACC_LD;                 // [4 warps][16][2]
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-        for (int n = 0; n < D / 8; ++n) {
-            float *a0 = acc_s + (warp * NQ + mt * 16 + g) * C::ACC_LD + n * 8 + tq * 2;
-            *reinterpret_cast<float2 *>(a0) = make_float2(acc[mt][n][0], acc[mt][n][1]);
-            *reinterpret_cast<float2 *>(a0 + 8 * C::ACC_LD) = make_float2(acc[mt][n][2], acc[mt][n][3]);
-        }
-        if (tq == 0) {
-            ml_s[(warp * NQ + mt * 16 + g) * 2] = m_run[mt][0];
-            ml_s[(warp * NQ + mt * 16 + g) * 2 + 1] = l_run[mt][0];
-            ml_s[(warp * NQ + mt * 16 + g + 8) * 2] = m_run[mt][1];
-            ml_s[(warp * NQ + mt * 16 + g + 8) * 2 + 1] = l_run[mt][1];
-        }
+    for (int n = 0; n < D / 8; ++n) {
+        float *a0 = acc_s + (warp * 16 + g) * C::ACC_LD + n * 8 + tq * 2;
+        *reinterpret_cast<float2 *>(a0) = make_float2(acc[n][0], acc[n][1]);
+        *reinterpret_cast<float2 *>(a0 + 8 * C::ACC_LD) = make_float2(acc[n][2], acc[n][3]);
+    }
+    if (tq == 0) {
+        ml_s[(warp * 16 + g) * 2] = m_run[0];
+        ml_s[(warp * 16 + g) * 2 + 1] = l_run[0];
+        ml_s[(warp * 16 + g + 8) * 2] = m_run[1];
+        ml_s[(warp * 16 + g + 8) * 2 + 1] = l_run[1];
     }
     __syncthreads();
     {
         constexpr int TPQ = kThreads / NQ;                   // threads per query (8 or 4)
         constexpr int CPT = D / TPQ;                         // columns per thread
+        constexpr int NW = PAIR ? 2 : 4;                     // states per query
         const int qi = t / TPQ, c0 = (t % TPQ) * CPT;
+        // state w of query qi lives in the rows of warp (PAIR ? 2 w + row tile : w), row qi % 16
+        const int wfirst = PAIR ? (qi >> 4) : 0, wstep = PAIR ? 2 : 1, qr = qi & 15;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, ml_s[(w * NQ + qi) * 2]);
-        float wgt[4], Lsum = 0.f;
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, ml_s[((wfirst + w * wstep) * 16 + qr) * 2]);
+        float wgt[NW], Lsum = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = ml_s[(w * NQ + qi) * 2];
+        for (int w = 0; w < NW; ++w) {
+            const float mw = ml_s[((wfirst + w * wstep) * 16 + qr) * 2];
             wgt[w] = mw > -INFINITY ? exp2f(mw - M) : 0.f;
             // a warp that saw no key still carries its initial l = 1 with m = -inf: weight 0 drops it
-            Lsum += wgt[w] * ml_s[(w * NQ + qi) * 2 + 1];
+            Lsum += wgt[w] * ml_s[((wfirst + w * wstep) * 16 + qr) * 2 + 1];
         }
         if (M == -INFINITY) Lsum = 1.f;                       // empty bucket: o = 0, lse = -inf
         float o[CPT];
 #pragma unroll
         for (int c = 0; c < CPT; ++c) o[c] = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float *src = acc_s + (w * NQ + qi) * C::ACC_LD + c0;
+        for (int w = 0; w < NW; ++w) {
+            const float *src = acc_s + ((wfirst + w * wstep) * 16 + qr) * C::ACC_LD + c0;
 #pragma unroll
             for (int c = 0; c < CPT; c += 4) {
                 float4 v4 = *reinterpret_cast<const float4 *>(src + c);
@@ -342,7 +317,7 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 attn_mma_kernel(AttnParams p)
 {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -355,9 +330,9 @@ attn_mma_kernel(AttnParams p)
         const int item = s_item;
         if (item >= n_items) break;
         const int4 it = p.items[item];
-        const int nq = min(kMaxQ, p.group_off[it.x + 1] - it.y);
-        if (nq > 16) run_item<T, D, 2>(p, smem, it, nq);
-        else run_item<T, D, 1>(p, smem, it, nq);
+        const int nq = min(min(kMaxQ, p.q_block), p.group_off[it.x + 1] - it.y);
+        if (nq > 16) run_item<T, D, true>(p, smem, it, nq);
+        else run_item<T, D, false>(p, smem, it, nq);
     }
 }
 
