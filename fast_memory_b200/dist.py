@@ -125,6 +125,29 @@ def allreduce_merge_partials(o: torch.Tensor, lse: torch.Tensor, group: Optional
     return out, M + torch.log(den)
 
 
+def reduce_scatter_merge_partials(o: torch.Tensor, lse: torch.Tensor, group: Optional[dist.ProcessGroup] = None
+                                  ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """:func:`allreduce_merge_partials` for a caller that needs only its own rows: ``o`` ``[W, n, d]`` and ``lse`` fp32
+    ``[W, n]`` are this rank's partial results for the rows of every rank (block r belongs to rank r); the MAX
+    all-reduce runs on the LSEs (small), the SUM on ``[w o | w]`` is a reduce-scatter, so every rank receives and
+    normalises ``n`` rows instead of ``W n``.  Returns fp32 ``(out [n, d], lse [n])`` of this rank's block."""
+    W, n, d = o.shape
+    r = dist.get_rank(group)
+    assert W == dist.get_world_size(group) and lse.shape == (W, n)
+    M = lse.clone()
+    dist.all_reduce(M, op=dist.ReduceOp.MAX, group=group)
+    M = torch.where(torch.isinf(M), torch.zeros_like(M), M)
+    acc = torch.empty(W, n, d + 1, dtype=torch.float32, device=o.device)
+    w = torch.exp(lse - M)
+    torch.mul(o, w[..., None], out=acc[..., :d]) if o.dtype == torch.float32 else acc[..., :d].copy_(o.float() * w[..., None])
+    acc[..., d] = w
+    mine = torch.empty(n, d + 1, dtype=torch.float32, device=o.device)
+    dist.reduce_scatter_tensor(mine, acc.view(W * n, d + 1), op=dist.ReduceOp.SUM, group=group)
+    den = mine[:, d]
+    out = mine[:, :d] / den.clamp_min(torch.finfo(torch.float32).tiny)[:, None]
+    return out, M[r] + torch.log(den)
+
+
 def all_gather_chunks(chunk: torch.Tensor, own: int, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """Rank r contributes the chunk it owns (index ``own = (r + 1) % W``); returns all chunks in row order."""
     W = dist.get_world_size(group)
@@ -226,6 +249,27 @@ class ShardedMemory:
         full_o = all_gather_chunks(oc, own, self.group)[:rows].reshape(Hq, S, d)
         full_l = all_gather_chunks(lc, own, self.group)[:rows].reshape(Hq, S)
         return full_o, full_l
+
+
+    def query_sharded(self, q_local: torch.Tensor, sm_scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The reference's own layout of the ring (mem:291-338): queries are sequence-sharded like the keys, rank r
+        holds ``q_local`` ``[Hq, S / W, d]`` = positions ``[r S / W, (r + 1) S / W)`` and wants the result for them.
+        The query slices are all-gathered (they are small against the keys, which never move), every rank attends
+        all queries to its own shards in one pass, and the partial results are merged by a MAX all-reduce of the
+        LSEs and a SUM reduce-scatter of ``[w o | w]``.  Returns fp32 ``(out [Hq, S / W, d], lse [Hq, S / W])``."""
+        Hq, n, d = q_local.shape
+        W = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        if W == 1:
+            o, lse = self.local.query(q_local, sm_scale)
+            return o.float(), lse
+        q_all = torch.empty(W, Hq, n, d, dtype=q_local.dtype, device=q_local.device)
+        dist.all_gather_into_tensor(q_all, q_local.contiguous(), group=self.group)
+        # the local memory hashes head h's rows with head h's A: [Hq, W n, d], rank blocks side by side
+        o, lse = self.local.query(q_all.permute(1, 0, 2, 3).reshape(Hq, W * n, d), sm_scale)
+        o = o.reshape(Hq, W, n, d).permute(1, 0, 2, 3).reshape(W, Hq * n, d)
+        lse = lse.reshape(Hq, W, n).permute(1, 0, 2).reshape(W, Hq * n)
+        out, l = reduce_scatter_merge_partials(o, lse, self.group)
+        return out.reshape(Hq, n, d), l.reshape(Hq, n)
 
 
 # ---------------------------------------------------------------------------------------------------

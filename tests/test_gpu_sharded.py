@@ -63,6 +63,11 @@ def _rank_main(rank, world, port, n_shards, H, L, S, C, Z, result):
     o2, lse2 = mem.query(q.to(dev), cfg.d ** -0.5, exchange="allreduce")
     torch.cuda.synchronize()
     assert (o2 - o).abs().max() <= 1e-4 and (lse2 - lse).abs().max() <= 1e-4       # two ways to merge the same partials
+    # queries sequence-sharded like the keys (the reference's layout): this rank's slice in, its rows of the result out
+    n = S // world
+    o3, lse3 = mem.query_sharded(q[:, rank * n:(rank + 1) * n].contiguous().to(dev), cfg.d ** -0.5)
+    torch.cuda.synchronize()
+    assert (o3 - o[:, rank * n:(rank + 1) * n]).abs().max() <= 1e-4 and (lse3 - lse[:, rank * n:(rank + 1) * n]).abs().max() <= 1e-4
     # the reference's global index over the two ranks' keys, and all queries through it
     from fast_memory_b200 import dist as fmd
     k_hashes = fmd.build_global_table(k[:, lo:hi].contiguous().to(dev), A.to(dev), Z)

@@ -52,6 +52,13 @@ def _worker(rank, world, port, rows, d, result):
     assert torch.equal(torch.isfinite(al), fin)
     assert torch.allclose(al[fin], full_l[fin], atol=1e-5) and torch.allclose(ao[fin], full_o[fin], atol=1e-5)
     assert (ao[~fin] == 0).all()
+    # and as a MAX all-reduce + SUM reduce-scatter: every rank gets its own block of rows only
+    n = rows // world
+    so, sl = fmd.reduce_scatter_merge_partials(o.reshape(world, n, d).clone(), l.reshape(world, n).clone())
+    mine = slice(rank * n, (rank + 1) * n)
+    fin_m = fin[mine]
+    assert torch.equal(torch.isfinite(sl), fin_m)
+    assert torch.allclose(sl[fin_m], full_l[mine][fin_m], atol=1e-5) and torch.allclose(so[fin_m], full_o[mine][fin_m], atol=1e-5)
     # SendRecv misuse raises like the reference (mem:39-40, 45-46)
     c = fmd.SendRecv()
     with pytest.raises(RuntimeError, match="Wait called before commit"):
