@@ -64,6 +64,16 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
     const int wk0 = PAIR ? (warp >> 1) * 32 : warp * 16;         // first key of the tile this warp consumes
     // every warp gathers 16 keys of each tile: the ones it consumes itself, or half of the ones its pair consumes
     const int my_c = lane % C::CPR;                              // chunk column this thread copies
+    // ldmatrix addresses inside a swizzled tile: row j, chunk c = 2 i + b sit at j 2D + ((c ^ (j & 7)) << 4).  With
+    // x = j & 7 = lane & 7 this splits into ((i & 4) << 5) + (((i & 3) ^ (x >> 1)) << 5) + ((b ^ (x & 1)) << 4): a
+    // compile-time term, one of four lane constants, and a lane constant - no XOR left in the tile loop.
+    uint32_t sw_i[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sw_i[i] = uint32_t((i ^ ((lane >> 1) & 3)) << 5);
+    // K (S = Q K^T): matrices (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+    const uint32_t k_lane = uint32_t(((lane & 7) + ((lane >> 4) << 3)) * (D * 2) + ((((lane >> 3) & 1) ^ (lane & 1)) << 4));
+    // V (P V, transposed loads): matrices (keys 0-7, d 16 n2 + 0-7), (keys 8-15, same d), (keys 0-7, d + 8), (keys 8-15, d + 8)
+    const uint32_t v_lane = uint32_t(((lane & 7) + (((lane >> 3) & 1) << 3)) * (D * 2) + (((lane >> 4) ^ (lane & 1)) << 4));
     const int my_r = warp * 16 + lane / C::CPR;                  // first row this thread copies
 
     const int gb = it.x, q_begin = it.y, kc = it.z, nkc = it.w;
@@ -151,29 +161,20 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
         for (int sub = 0; sub < SUB; ++sub) {
             const int wk = wk0 + sub * 16;                       // 16 keys of the tile
 
-            // S = Q K^T for 16 queries x 16 keys; even and odd k-steps accumulate separately: four independent
-            // MMA chains instead of two
+            // S = Q K^T for 16 queries x 16 keys (two accumulation chains; with 12 warps per SM splitting them further
+            // into even and odd k-steps only cost instructions)
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            float s_odd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            const uint32_t k_sub = ks_base + wk * (D * 2) + k_lane;
+            const uint32_t k_addr[4] = {k_sub + sw_i[0], k_sub + sw_i[1], k_sub + sw_i[2], k_sub + sw_i[3]};
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-                // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
-                const int j = wk + (lane & 7) + ((lane >> 4) << 3);
-                const int c = ks * 2 + ((lane >> 3) & 1);
                 uint32_t b[4];
-                ldmatrix_x4(b, ks_base + swz<D>(j, c));
-                if (ks & 1) {
-                    mma16816<T>(s_odd[0], qf[ks], b[0], b[1]);
-                    mma16816<T>(s_odd[1], qf[ks], b[2], b[3]);
-                } else {
-                    mma16816<T>(s[0], qf[ks], b[0], b[1]);
-                    mma16816<T>(s[1], qf[ks], b[2], b[3]);
-                }
+                if (ks < 4) ldmatrix_x4_off<0>(b, k_addr[ks & 3]);
+                else ldmatrix_x4_off<128>(b, k_addr[ks & 3]);
+                mma16816<T>(s[0], qf[ks], b[0], b[1]);
+                mma16816<T>(s[1], qf[ks], b[2], b[3]);
             }
-#pragma unroll
-            for (int n = 0; n < 2; ++n)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) s[n][e] += s_odd[n][e];
             // mask (only the last tile can be partial), online softmax in the scaled base-2 domain
             // (rows g and g + 8 of the row tile; this thread's keys: wk + 8 n + 2 tq + {0, 1})
             if (tile == n_tiles - 1) {
@@ -223,12 +224,13 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
             }
             // acc += P V  (k = the slice's 16 keys, n = head dim)
 #pragma unroll
+            const uint32_t v_sub = vs_base + wk * (D * 2) + v_lane;
+            const uint32_t v_addr[4] = {v_sub + sw_i[0], v_sub + sw_i[1], v_sub + sw_i[2], v_sub + sw_i[3]};
+#pragma unroll
             for (int n2 = 0; n2 < D / 16; ++n2) {
-                // matrices: (keys 0-7, d n2*16 + 0-7), (keys 8-15, same d), (keys 0-7, d + 8), (keys 8-15, d + 8)
-                const int j = wk + (lane & 7) + (((lane >> 3) & 1) << 3);
-                const int c = n2 * 2 + (lane >> 4);
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, vs_base + swz<D>(j, c));
+                if (n2 < 4) ldmatrix_x4_trans_off<0>(b, v_addr[n2 & 3]);
+                else ldmatrix_x4_trans_off<128>(b, v_addr[n2 & 3]);
                 mma16816<T>(acc[2 * n2], pa, b[0], b[1]);
                 mma16816<T>(acc[2 * n2 + 1], pa, b[2], b[3]);
             }

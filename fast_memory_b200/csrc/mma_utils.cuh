@@ -61,6 +61,18 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
+// the same loads with a compile-time byte offset folded into the address operand
+template <int OFF> __device__ __forceinline__ void ldmatrix_x4_off(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(OFF));
+}
+template <int OFF> __device__ __forceinline__ void ldmatrix_x4_trans_off(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr), "n"(OFF));
+}
+
 // byte offset of 16-byte chunk `c` of row `j` inside a swizzled tile
 template <int D> __device__ __forceinline__ uint32_t swz(int j, int c) { return uint32_t(j * (D * 2) + ((c ^ (j & 7)) << 4)); }
 

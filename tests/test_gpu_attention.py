@@ -79,6 +79,24 @@ def test_many_groups_items_of_two_row_tiles(dtype, d):
         assert_attn_close(o[b:b + 1, pick], lse[b:b + 1, pick], o_ref, lse_ref, dtype)
 
 
+def test_many_groups_two_row_tile_items_with_split_buckets():
+    """The 17-32 query items together with buckets cut into key chunks (partials folded by the combine kernel)."""
+    B, S, N, C, Z, d, dtype = 1, 4096 * 24, 2048, 4096, 203, 128, torch.bfloat16
+    q, k, v, kh, cnt, qh = random_case(B, S, N, C, Z, d, dtype, seed=77)
+    dev = lambda t: t.to(DEV)
+    bucket_off = torch.zeros(B * C + 1, dtype=torch.int64)
+    bucket_off[1:] = torch.cumsum(cnt.reshape(-1), 0)
+    group_off, perm = fm.group_rows(dev(qh.reshape(-1).int()), B * C)
+    o, lse = fm.hashed_attention(dev(q[0]), dev(k[0]), dev(v[0]), dev(kh), dev(bucket_off), group_off, perm,
+                                 d ** -0.5, int(cnt.max()), key_chunk=64)
+    o_whole, lse_whole = fm.hashed_attention(dev(q[0]), dev(k[0]), dev(v[0]), dev(kh), dev(bucket_off), group_off, perm,
+                                             d ** -0.5, int(cnt.max()))
+    assert (o.float() - o_whole.float()).abs().max() <= 2e-2 and (lse - lse_whole).abs().max() <= 1e-3
+    pick = torch.randperm(S, generator=torch.Generator().manual_seed(3))[:128]
+    o_ref, lse_ref = O.hashed_attention(q[:, pick], k, v, kh, cnt, qh[:, pick], d ** -0.5)
+    assert_attn_close(o[None, pick], lse[None, pick], o_ref, lse_ref, dtype)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("key_chunk", [64, 128, 1000])
 def test_split_buckets_match_unsplit(dtype, key_chunk):
