@@ -139,7 +139,8 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
         load_rows(s + 1);
     }
 
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {1.f, 1.f};
+    // l is kept as per-thread partial sums (the four threads of a row share m, hence alpha) and added up at the end
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {tq == 0 ? 1.f : 0.f, tq == 0 ? 1.f : 0.f};
     float acc[D / 8][4];
 #pragma unroll
     for (int n = 0; n < D / 8; ++n)
@@ -203,10 +204,7 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
                 const float p01 = fast_exp2(fmaf(s[0][2 * r + 1], p.scale2, -m_sub));
                 const float p10 = fast_exp2(fmaf(s[1][2 * r], p.scale2, -m_sub));
                 const float p11 = fast_exp2(fmaf(s[1][2 * r + 1], p.scale2, -m_sub));
-                float sum = (p00 + p01) + (p10 + p11);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                l_run[r] = l_run[r] * alpha[r] + sum;
+                l_run[r] = l_run[r] * alpha[r] + ((p00 + p01) + (p10 + p11));
                 m_run[r] = m_new;
                 pa[r] = pack2<T>(p00, p01);                      // keys 0-7 of the slice
                 pa[2 + r] = pack2<T>(p10, p11);                  // keys 8-15
@@ -237,6 +235,11 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
         }
     }
     cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
     __syncthreads();                                         // all tiles consumed: the stages become the combine buffer
 
     // ---- fold the warps' states: four per query (PAIR = false), two per query (the two key halves of its row tile) ----
