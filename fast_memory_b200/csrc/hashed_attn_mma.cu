@@ -158,79 +158,90 @@ __device__ __forceinline__ void run_item(const AttnParams &p, unsigned char *sme
         const uint32_t ks_base = smem_base + st * C::STAGE_BYTES;
         const uint32_t vs_base = ks_base + C::TILE_BYTES;
 
+        // S = Q K^T for 16 queries x 16 SUB keys (two accumulation chains per 16-key slice; with 12 warps per SM
+        // splitting them further into even and odd k-steps only cost instructions)
+        float s[SUB][2][4];
 #pragma unroll
         for (int sub = 0; sub < SUB; ++sub) {
-            const int wk = wk0 + sub * 16;                       // 16 keys of the tile
-
-            // S = Q K^T for 16 queries x 16 keys (two accumulation chains; with 12 warps per SM splitting them further
-            // into even and odd k-steps only cost instructions)
-            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-            const uint32_t k_sub = ks_base + wk * (D * 2) + k_lane;
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[sub][n][e] = 0.f;
+            const uint32_t k_sub = ks_base + (wk0 + sub * 16) * (D * 2) + k_lane;
             const uint32_t k_addr[4] = {k_sub + sw_i[0], k_sub + sw_i[1], k_sub + sw_i[2], k_sub + sw_i[3]};
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
                 uint32_t b[4];
                 if (ks < 4) ldmatrix_x4_off<0>(b, k_addr[ks & 3]);
                 else ldmatrix_x4_off<128>(b, k_addr[ks & 3]);
-                mma16816<T>(s[0], qf[ks], b[0], b[1]);
-                mma16816<T>(s[1], qf[ks], b[2], b[3]);
+                mma16816<T>(s[sub][0], qf[ks], b[0], b[1]);
+                mma16816<T>(s[sub][1], qf[ks], b[2], b[3]);
             }
-            // mask (only the last tile can be partial), online softmax in the scaled base-2 domain
-            // (rows g and g + 8 of the row tile; this thread's keys: wk + 8 n + 2 tq + {0, 1})
-            if (tile == n_tiles - 1) {
-                const int live = chunk_len - tile * kTK;
+        }
+        // mask (only the last tile can be partial), online softmax in the scaled base-2 domain over the warp's keys of
+        // the tile (rows g and g + 8 of the row tile; this thread's keys: wk0 + 16 sub + 8 n + 2 tq + {0, 1})
+        if (tile == n_tiles - 1) {
+            const int live = chunk_len - tile * kTK;
+#pragma unroll
+            for (int sub = 0; sub < SUB; ++sub)
 #pragma unroll
                 for (int n = 0; n < 2; ++n) {
-                    const int jk = wk + n * 8 + tq * 2;
-                    if (jk >= live) { s[n][0] = -INFINITY; s[n][2] = -INFINITY; }
-                    if (jk + 1 >= live) { s[n][1] = -INFINITY; s[n][3] = -INFINITY; }
+                    const int jk = wk0 + sub * 16 + n * 8 + tq * 2;
+                    if (jk >= live) { s[sub][n][0] = -INFINITY; s[sub][n][2] = -INFINITY; }
+                    if (jk + 1 >= live) { s[sub][n][1] = -INFINITY; s[sub][n][3] = -INFINITY; }
                 }
-            }
-            uint32_t pa[4];
-            float alpha[2];
-            bool moved = false;
-            float mx[2];
-            mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-            mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        }
+        uint32_t pa[SUB][4];
+        float alpha[2];
+        bool moved = false;
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                const float m_new = fmaxf(m_run[r], mx[r] * p.scale2);          // scale2 > 0 keeps the order
-                const float m_sub = m_new > -INFINITY ? m_new : 0.f;            // nothing live yet: p = 2^-inf = 0
-                alpha[r] = fast_exp2(m_run[r] - m_sub);
-                const float p00 = fast_exp2(fmaf(s[0][2 * r], p.scale2, -m_sub));
-                const float p01 = fast_exp2(fmaf(s[0][2 * r + 1], p.scale2, -m_sub));
-                const float p10 = fast_exp2(fmaf(s[1][2 * r], p.scale2, -m_sub));
-                const float p11 = fast_exp2(fmaf(s[1][2 * r + 1], p.scale2, -m_sub));
-                l_run[r] = l_run[r] * alpha[r] + ((p00 + p01) + (p10 + p11));
-                m_run[r] = m_new;
-                pa[r] = pack2<T>(p00, p01);                      // keys 0-7 of the slice
-                pa[2 + r] = pack2<T>(p10, p11);                  // keys 8-15
-                moved = moved || alpha[r] != 1.f;
-            }
-            // the running maxima settle after a few tiles; rescale the accumulators only when one moved
-            if (__any_sync(0xffffffffu, moved)) {
+        for (int r = 0; r < 2; ++r) {
+            float mx = -INFINITY;
 #pragma unroll
-                for (int n = 0; n < D / 8; ++n) {
-                    acc[n][0] *= alpha[0];
-                    acc[n][1] *= alpha[0];
-                    acc[n][2] *= alpha[1];
-                    acc[n][3] *= alpha[1];
-                }
-            }
-            // acc += P V  (k = the slice's 16 keys, n = head dim)
+            for (int sub = 0; sub < SUB; ++sub)
+                mx = fmaxf(mx, fmaxf(fmaxf(s[sub][0][2 * r], s[sub][0][2 * r + 1]), fmaxf(s[sub][1][2 * r], s[sub][1][2 * r + 1])));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[r], mx * p.scale2);                 // scale2 > 0 keeps the order
+            const float m_sub = m_new > -INFINITY ? m_new : 0.f;                // nothing live yet: p = 2^-inf = 0
+            alpha[r] = fast_exp2(m_run[r] - m_sub);
+            float sum = 0.f;
 #pragma unroll
-            const uint32_t v_sub = vs_base + wk * (D * 2) + v_lane;
+            for (int sub = 0; sub < SUB; ++sub) {
+                const float p00 = fast_exp2(fmaf(s[sub][0][2 * r], p.scale2, -m_sub));
+                const float p01 = fast_exp2(fmaf(s[sub][0][2 * r + 1], p.scale2, -m_sub));
+                const float p10 = fast_exp2(fmaf(s[sub][1][2 * r], p.scale2, -m_sub));
+                const float p11 = fast_exp2(fmaf(s[sub][1][2 * r + 1], p.scale2, -m_sub));
+                sum += (p00 + p01) + (p10 + p11);
+                pa[sub][r] = pack2<T>(p00, p01);                 // keys 0-7 of the slice
+                pa[sub][2 + r] = pack2<T>(p10, p11);             // keys 8-15
+            }
+            l_run[r] = l_run[r] * alpha[r] + sum;
+            m_run[r] = m_new;
+            moved = moved || alpha[r] != 1.f;
+        }
+        // the running maxima settle after a few tiles; rescale the accumulators only when one moved
+        if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) {
+                acc[n][0] *= alpha[0];
+                acc[n][1] *= alpha[0];
+                acc[n][2] *= alpha[1];
+                acc[n][3] *= alpha[1];
+            }
+        }
+        // acc += P V  (k = 16 keys per slice, n = head dim)
+#pragma unroll
+        for (int sub = 0; sub < SUB; ++sub) {
+            const uint32_t v_sub = vs_base + (wk0 + sub * 16) * (D * 2) + v_lane;
             const uint32_t v_addr[4] = {v_sub + sw_i[0], v_sub + sw_i[1], v_sub + sw_i[2], v_sub + sw_i[3]};
 #pragma unroll
             for (int n2 = 0; n2 < D / 16; ++n2) {
                 uint32_t b[4];
                 if (n2 < 4) ldmatrix_x4_trans_off<0>(b, v_addr[n2 & 3]);
                 else ldmatrix_x4_trans_off<128>(b, v_addr[n2 & 3]);
-                mma16816<T>(acc[2 * n2], pa, b[0], b[1]);
-                mma16816<T>(acc[2 * n2 + 1], pa, b[2], b[3]);
+                mma16816<T>(acc[2 * n2], pa[sub], b[0], b[1]);
+                mma16816<T>(acc[2 * n2 + 1], pa[sub], b[2], b[3]);
             }
         }
     }
