@@ -37,7 +37,7 @@ UNIT = "queries/s"
 
 # DRAM bytes (read + write) of one attention launch per KV head of cfg2, from the ncu capture summarised in
 # profiles/attn_mma_kernel_cfg2_8heads.md (1.352 GB for 8 heads); traffic grows in proportion to the heads.
-NCU_ATTN_DRAM_BYTES_PER_HEAD = {"cfg2": 0.910e9 / 8}
+NCU_ATTN_DRAM_BYTES_PER_HEAD = {"cfg2": 0.901e9 / 8}
 
 
 def measured_peaks():
