@@ -10,7 +10,12 @@ the timed region.  The index build (projection + top-Z) is timed separately (``i
 
 Multi-GPU: heads (and whole memories) are independent, so under torchrun every rank serves its own memory
 of the same shape (weak scaling, no data-path collective); ``value`` is the sum over ranks divided by the
-slowest rank's time.
+slowest rank's time.  The line of the default workload also carries a ``sharded`` record: the sequence-sharded
+ring configuration (cfg5: 8 fixed logical key shards spread over the ranks, partial (O, LSE) merged across
+ranks; strong scaling) with its own timing, roofline and a parity figure of the merged multi-rank result
+against the CPU oracle on sampled query rows.  Where the reference's modules have been copied into
+``baseline/_ref`` the line also carries ``gpu_comparator``: the reference's own Triton kernel, JIT-compiled
+for this GPU, timed on the same tensors.
 
 ``--impl reference`` times the CPU port of the reference algorithm (``oracle/``) on the host cores on a
 bounded sample of the same workload.
@@ -35,9 +40,24 @@ import torch
 METRIC = "hashed_attn_queries_per_s"
 UNIT = "queries/s"
 
-# DRAM bytes (read + write) of one attention launch per KV head of cfg2, from the ncu capture summarised in
-# profiles/attn_mma_kernel_cfg2_8heads.md (1.352 GB for 8 heads); traffic grows in proportion to the heads.
-NCU_ATTN_DRAM_BYTES_PER_HEAD = {"cfg2": 0.901e9 / 8}
+
+def profiled_traffic(workload: str, kernel: str):
+    """DRAM bytes (read + write) of one launch of ``kernel`` on ``workload`` from the ncu captures recorded as small
+    JSON files under ``profiles/`` (one beside each summary: workload, KV heads captured, bytes, duration).  The
+    captures are taken on a cut of the workload with fewer KV heads; traffic grows in proportion to the heads
+    because every head has the same reuse pattern.  Returns ``(bytes_per_head, source)`` or ``(None, None)``."""
+    import glob
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "*.json"))):
+        try:
+            with open(path) as fh:
+                rec = json.load(fh)
+        except (OSError, ValueError):
+            continue
+        if rec.get("workload") == workload and rec.get("kernel") == kernel:
+            total = float(rec["dram_bytes_read"]) + float(rec["dram_bytes_write"])
+            return total / rec["kv_heads"], {"file": "profiles/" + os.path.basename(path), "kv_heads_captured": rec["kv_heads"],
+                                            "dram_bytes": total, "duration_us": rec.get("duration_us")}
+    return None, None
 
 
 def measured_peaks():
@@ -127,6 +147,97 @@ def algorithmic_attention_bytes(mem, group_off, d, esize):
     return int((per_group * (nq > 0)).sum().item() + nq.sum().item() * (2 * d * esize + 8)), int((nq > 0).sum().item())
 
 
+def compulsory_attention_bytes(mem, n_queries, d, esize):
+    """The least the attention launch must move through DRAM: every K / V row that some bucket refers to once, the
+    table once, and per query the q row, the o row, the hash and the LSE."""
+    uniq = int(torch.unique(mem.table).numel())
+    return uniq * 2 * d * esize + mem.table.numel() * mem.table.element_size() + n_queries * (2 * d * esize + 8)
+
+
+def time_events(fn, steps, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def gpu_comparator(cfg, mem, q, k, v, sm_scale, attn_ms, step_fn, steps):
+    """The reference's own kernel on the same tensors: ``attention_hash_varlen`` (triton_kernel.py:51-119) with the Triton
+    kernel it launches (triton_kernel.py:135-272) compiled natively for this GPU, fed this memory's table (as int64
+    per-head indices, the reference's layout) and this library's query hashes.  Timed with CUDA events after the
+    autotuner has run; the kernel alone is timed through the reference's registered operator on pre-sorted operands.
+    Returns None when the reference modules are not in ``baseline/_ref``."""
+    from baseline import ref_gpu
+    if not ref_gpu.available():
+        return None
+    try:
+        tk = ref_gpu.load()
+        H, N, d = k.shape
+        Hq, S, _ = q.shape
+        C, Z = cfg.n_buckets, min(cfg.bucket_size, N)
+        qf = q.reshape(H, -1, d)                                            # GQA groups folded into the query axis (mem:134)
+        hashes = mem.hash_queries(q).reshape(H, -1).long()
+        k_hashes = (mem.table.reshape(H, C * Z).long() - (torch.arange(H, device=q.device) * N)[:, None]).reshape(-1)
+        counts = torch.full((H, C), Z, dtype=torch.long, device=q.device)
+        ref = lambda: tk.attention_hash_varlen(qf, k, v, k_hashes, counts, hashes, sm_scale)
+        wrapper_ms = time_events(ref, steps)
+        qs, order, gz, gc, go, k_off = ref_gpu.sorted_operands(qf, hashes, counts)
+        op = lambda: torch.ops.notbad.attention_hash_varlen(qs, k, v, k_hashes, counts, k_off, gz, gc, go, sm_scale=sm_scale,
+                                                            q_seq_len=qf.shape[1], kv_seq_len=N, d_head=d, n_buckets=C)
+        kernel_ms = time_events(op, steps)
+        o_ref, lse_ref = ref_gpu.reference_forward_fp32_lse(tk, qf, k, v, k_hashes, counts, hashes, sm_scale)
+        o, lse = mem.query(q, sm_scale)
+        ours_ms = time_events(lambda: mem.query(q, sm_scale, q_hashes=hashes), steps)     # grouping + attention, hashes given
+        fin = torch.isfinite(lse_ref)
+        rec = {"kernel": "reference Triton _attn_fwd, JIT-compiled natively (triton_kernel.py:135-272)",
+               "kernel_ms": kernel_ms, "ours_kernel_ms": attn_ms, "speedup_vs_triton": kernel_ms / attn_ms,
+               "wrapper_ms": wrapper_ms, "ours_group_and_attend_ms": ours_ms, "speedup_wrapper": wrapper_ms / ours_ms,
+               "max_abs_diff_o": float((o.reshape(H, -1, d).float() - o_ref.float()).abs().max()),
+               "max_abs_diff_lse": float((lse.reshape(H, -1)[fin] - lse_ref[fin]).abs().max()),
+               "dtype": str(q.dtype).replace("torch.", "")}
+        del o_ref, lse_ref, k_hashes, qs
+        return rec
+    except Exception as e:                                                   # the comparator never takes the benchmark down
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+
+
+def host_copy_ceiling(q_host, o_host, l_host, q_dev, barrier, reps=5):
+    """Host<->device bandwidth of this rank's pinned buffers with both directions busy at once and (under torchrun) all
+    ranks copying at the same time: what bounds the end-to-end figure when the kernels are hidden under the copies."""
+    dev = q_dev.device
+    o_dev = torch.empty(o_host.shape, dtype=o_host.dtype, device=dev)
+    l_dev = torch.empty(l_host.shape, dtype=l_host.dtype, device=dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    times = []
+    for it in range(reps + 1):
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(s_in):
+            a0.record()
+            q_dev.copy_(q_host, non_blocking=True)
+            a1.record()
+        with torch.cuda.stream(s_out):
+            b0.record()
+            o_host.copy_(o_dev, non_blocking=True)
+            l_host.copy_(l_dev, non_blocking=True)
+            b1.record()
+        torch.cuda.synchronize()
+        if it:
+            times.append((a0.elapsed_time(a1), b0.elapsed_time(b1)))
+    h2d_ms = statistics.median(t[0] for t in times)
+    d2h_ms = statistics.median(t[1] for t in times)
+    h2d_b = q_host.numel() * q_host.element_size()
+    d2h_b = o_host.numel() * o_host.element_size() + l_host.numel() * l_host.element_size()
+    return {"h2d_gbs": h2d_b / h2d_ms / 1e6, "d2h_gbs": d2h_b / d2h_ms / 1e6, "copy_bound_ms": max(h2d_ms, d2h_ms)}
+
+
 def run_ours(args, rank, world):
     import fast_memory_b200 as fm
     from fast_memory_b200 import ops, synth
@@ -206,17 +317,11 @@ def run_ours(args, rank, world):
     kk, vv = k.reshape(-1, d), v.reshape(-1, d)
     attn = lambda: ops.hashed_attention(qf, kk, vv, mem.table, mem.bucket_off, group_off, perm, sm_scale,
                                         mem.max_bucket_len, out=o_buf, lse=l_buf)
-    for _ in range(3):
-        attn()
-    torch.cuda.synchronize()
-    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a0.record()
-    for _ in range(args.steps):
-        attn()
-    a1.record()
-    torch.cuda.synchronize()
-    attn_ms = a0.elapsed_time(a1) / args.steps
+    attn_ms = time_events(attn, args.steps)
     attn_bytes, n_groups = algorithmic_attention_bytes(mem, group_off, d, esize)
+    nq_g = (group_off[1:] - group_off[:-1]).to(torch.int64)
+    attn_flops = float((4 * d * nq_g * (mem.bucket_off[1:] - mem.bucket_off[:-1])).sum().item())
+    compulsory = compulsory_attention_bytes(mem, qf.shape[0], d, esize)
 
     # ---- end to end: pinned host queries in, result out, inside the timed region ------------------------
     q_host = q.cpu().pin_memory()
@@ -242,18 +347,57 @@ def run_ours(args, rank, world):
     barrier()
     e2e_ms = e0.elapsed_time(e1) / args.steps
 
+    # latency of ONE host-to-host call with nothing else in flight (1 and 4 head slices), and the copy ceiling
+    latency = {}
+    for nc in (1, 4):
+        lat = []
+        for it in range(6):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            mem.query_from_host(q_host, sm_scale, o_host, l_host, n_chunks=nc, local=local, overlap_calls=False)
+            e1.record()
+            torch.cuda.synchronize()
+            if it:
+                lat.append(e0.elapsed_time(e1))
+        latency[f"n_chunks_{nc}"] = statistics.median(lat)
+    ceiling = host_copy_ceiling(q_host, o_host, l_host, q_dev, barrier)
+
     if world > 1:
-        t = torch.tensor([step_ms, e2e_ms, statistics.median(build_ms)], device=dev, dtype=torch.float64)
+        t = torch.tensor([step_ms, e2e_ms, statistics.median(build_ms), ceiling["copy_bound_ms"], latency["n_chunks_1"],
+                          latency["n_chunks_4"]], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        step_ms, e2e_ms, build_med = t.tolist()
+        step_ms, e2e_ms, build_med, ceiling["copy_bound_ms"], latency["n_chunks_1"], latency["n_chunks_4"] = t.tolist()
     else:
         build_med = statistics.median(build_ms)
+
+    comparator = None
+    if rank == 0 and not args.no_comparator and cfg.name in ("cfg2", "cfg3"):
+        comparator = gpu_comparator(cfg, mem, q, k, v, sm_scale, attn_ms, step, min(args.steps, 10))
     if rank != 0:
         return None
 
     peaks = measured_peaks()
     achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
     build_flops = 2.0 * cfg.n_buckets * N * d * H
+    per_head, source = profiled_traffic(cfg.name, "attn_mma_kernel")
+    traffic = per_head * H if per_head is not None else None
+    kv_per_head_mb = 2 * N * d * esize / 1e6
+    in_l2 = kv_per_head_mb < 126
+    roofline = {
+        "kernel": "hashed attention forward", "bound": "sm-issue (gather served by L2)" if in_l2 else "hbm",
+        "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+        "peak_source": peaks["source"], "algorithmic_bytes": attn_bytes, "ms_per_launch": attn_ms,
+        "traffic": traffic, "traffic_source": source,
+        "dram_gbs": (traffic / (attn_ms * 1e-3) / 1e9) if traffic else None,
+        "frac_dram": (traffic / (attn_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if traffic else None,
+        "compulsory_bytes": compulsory, "frac_compulsory": compulsory / (attn_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+        "tflops": attn_flops / (attn_ms * 1e-3) / 1e12, "frac_tensor": attn_flops / (attn_ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        "note": (f"algorithmic bytes count a key row once per bucket it sits in (C*Z/N = {cfg.n_buckets * cfg.bucket_size / N:.0f}); "
+                 f"a head's K+V ({kv_per_head_mb:.0f} MB) fits the 126 MB L2, so most gathered bytes never reach DRAM and "
+                 "`frac` can pass 1: `frac_dram` (ncu DRAM bytes / time / peak) and `frac_compulsory` are the HBM figures")
+                if in_l2 else "a head's K+V exceeds L2: the gather is served by DRAM",
+    }
     res = {
         "metric": METRIC, "value": world * n_queries / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
@@ -262,23 +406,27 @@ def run_ours(args, rank, world):
         "config": {"workload": ("CUT-DOWN " if args.kv_heads else "") + f"{cfg.name}: {H} KV heads x {cfg.q_groups} groups, d={d}, N={N} keys/head, C={cfg.n_buckets}, "
                                f"Z={cfg.bucket_size}, {S} queries/head" + (f", merged with a causal local window of {cfg.local_window}" if cfg.local_window else ""),
                    "parallelism": f"independent memories per GPU x{world}" if world > 1 else "single GPU",
-                   "l2": f"inputs larger than L2 ({attn_bytes / 1e9:.2f} GB gathered per step)",
+                   "l2": f"a step touches K+V of {H} heads in turn ({H * kv_per_head_mb / 1e3:.2f} GB, {kv_per_head_mb:.0f} MB per head): nothing "
+                         f"survives in the 126 MB L2 from step to step; inside a step a head's rows are re-read from L2",
                    "non_empty_groups": n_groups},
         "clocks": clocks.summary(),
         "e2e": {"value": world * n_queries / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": q_host.numel() * q_host.element_size(),
                 "d2h_bytes_per_step": o_host.numel() * o_host.element_size() + l_host.numel() * 4,
                 "pipeline": f"query_from_host, {args.e2e_chunks} head slice(s) per call, consecutive calls overlap "
-                            "(copy-in of step i+1 and copy-out of step i-1 run under the kernels of step i)"},
+                            "(copy-in of step i+1 and copy-out of step i-1 run under the kernels of step i): a throughput "
+                            "figure with two requests in flight",
+                "latency_ms": latency,
+                "host_copy": dict(ceiling, frac_of_copy_bound=ceiling["copy_bound_ms"] / e2e_ms,
+                                  note="per rank, both directions and all ranks copying at once, same pinned buffers")},
         "gpu_launches": int(launches),
-        "roofline": {"kernel": "hashed attention forward", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                     "traffic": (NCU_ATTN_DRAM_BYTES_PER_HEAD[cfg.name] * H if cfg.name in NCU_ATTN_DRAM_BYTES_PER_HEAD else None),
-                     "algorithmic_bytes": attn_bytes, "ms_per_launch": attn_ms},
+        "roofline": roofline,
         "index_build": {"metric": "index_build_keys_per_s", "value": world * H * N / (build_med * 1e-3), "unit": "keys/s",
                         "ms": build_med, "tflops": build_flops / (build_med * 1e-3) / 1e12,
                         "frac_of_tensor_peak": build_flops / (build_med * 1e-3) / 1e12 / peaks["bf16_tflops"]},
     }
+    if comparator is not None:
+        res["gpu_comparator"] = comparator
     if world == 1 and not args.no_cpu_baseline:
         res["cpu_baseline"] = cpu_baseline(cfg, args.seed, target_s=args.cpu_seconds)
     return res
@@ -411,10 +559,53 @@ def run_varlen(args, rank, world):
     }
 
 
+def sharded_parity(mem, q, out, lse, sm_scale, rank, world, n_rows=64, seed=1234):
+    """max |dO| and |dLSE| of ``n_rows`` sampled query rows of the MERGED multi-rank result against the CPU oracle
+    evaluated over the concatenation of each row's bucket on every shard of every rank (the single-device result over
+    the concatenated per-shard indices).  A checker, outside every timed region: the rows' bucket contents are
+    gathered from all ranks to rank 0, which runs the oracle."""
+    import torch.distributed as dist
+    loc = mem.local
+    dev = q.device
+    Hq, S, d = q.shape
+    G = Hq // loc.n_heads
+    C = loc.seq_buckets[0]
+    rows = torch.randint(Hq * S, (n_rows,), generator=torch.Generator().manual_seed(seed)).to(dev)
+    hashes = loc.hash_queries(q).reshape(-1)[rows].long()
+    gb = (rows // S // G) * C + hashes                                    # global bucket of every sampled row
+    zl = loc.max_bucket_len                                               # keys of a bucket on this rank (all local shards)
+    pos = loc.bucket_off[gb][:, None] + torch.arange(zl, device=dev)[None]
+    idx = loc.table[pos.reshape(-1)].long()
+    kk = loc.k.reshape(-1, d)[idx].reshape(n_rows, zl, d)
+    vv = loc.v.reshape(-1, d)[idx].reshape(n_rows, zl, d)
+    if world > 1:
+        ka = torch.empty((world,) + tuple(kk.shape), dtype=kk.dtype, device=dev)
+        va = torch.empty_like(ka)
+        dist.all_gather_into_tensor(ka, kk.contiguous())
+        dist.all_gather_into_tensor(va, vv.contiguous())
+        kk = ka.permute(1, 0, 2, 3).reshape(n_rows, world * zl, d)           # rank order = shard order = ascending keys
+        vv = va.permute(1, 0, 2, 3).reshape(n_rows, world * zl, d)
+    if rank != 0:
+        return None
+    from oracle import oracle as O
+    kk, vv = kk.cpu(), vv.cpu()
+    qs = q.reshape(-1, d)[rows].cpu()
+    got_o, got_l = out.reshape(-1, d)[rows].float().cpu(), lse.reshape(-1)[rows].cpu()
+    n = kk.shape[1]
+    err_o = err_l = 0.0
+    for i in range(n_rows):
+        o_ref, l_ref = O.hashed_attention(qs[i][None, None], kk[i][None], vv[i][None], torch.arange(n),
+                                          torch.tensor([[n]]), torch.zeros(1, 1, dtype=torch.long), sm_scale)
+        err_o = max(err_o, float((got_o[i] - o_ref[0, 0].float()).abs().max()))
+        err_l = max(err_l, abs(float(got_l[i]) - float(l_ref[0, 0])))
+    return {"rows": n_rows, "keys_per_row": n, "max_abs_o": err_o, "max_abs_lse": err_l, "tol_o": 2e-2, "tol_lse": 1e-3,
+            "ok": bool(err_o <= 2e-2 and err_l <= 1e-3), "oracle": "CPU port, concatenated per-shard buckets"}
+
+
 def run_ring(args, rank, world):
     """cfg5: keys sharded over the sequence into 8 logical shards (fixed, so the result does not depend on the
     GPU count), every rank indexes its own shards, all queries attend everywhere, partial (O, LSE) are merged
-    around the ring.  Strong scaling: the same job on 1, 2, 4 or 8 GPUs."""
+    across the ranks.  Strong scaling: the same job on 1, 2, 4 or 8 GPUs."""
     import fast_memory_b200 as fm
     from fast_memory_b200 import synth
     from fast_memory_b200.dist import ShardedMemory
@@ -462,33 +653,32 @@ def run_ring(args, rank, world):
         if it > 0 or args.build_steps == 0:
             build_ms.append(e0.elapsed_time(e1))
 
+    steps = min(args.steps, args.sharded_steps) if args.workload != "cfg5" else args.steps
+    warmup = min(args.warmup, 5) if args.workload != "cfg5" else args.warmup
     with ClockSampler(dev.index or 0) as clocks:             # samples span the warm-up and the timed region (both under load)
-        for _ in range(args.warmup):
+        for _ in range(warmup):
             mem.query(q, sm_scale, exchange=args.exchange)
         barrier()
         launches0 = fm.launch_count()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             mem.query(q, sm_scale, exchange=args.exchange)
         t1.record()
         barrier()
-        step_ms = t0.elapsed_time(t1) / args.steps
+        step_ms = t0.elapsed_time(t1) / steps
     launches = fm.launch_count() - launches0
 
-    # attention alone on the local shards (the dominant kernel)
-    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for _ in range(2):
-        mem.query_partial(q, sm_scale)
-    torch.cuda.synchronize()
-    a0.record()
-    for _ in range(args.steps):
-        mem.query_partial(q, sm_scale)
-    a1.record()
-    torch.cuda.synchronize()
-    part_ms = a0.elapsed_time(a1) / args.steps
+    # the local part alone (hash + group + attention over this rank's shards: the dominant kernel)
+    barrier()
+    part_ms = time_events(lambda: mem.query_partial(q, sm_scale), steps, warmup=2)
     n_buckets_total = H * cfg.n_buckets
     attn_bytes = n_buckets_total * per * min(cfg.bucket_size, shard_len) * (4 + 2 * d * 2) + H * S * (2 * d * 2 + 8)
+
+    # parity of the merged multi-rank result (outside the timed regions)
+    o_full, l_full = mem.query(q, sm_scale, exchange=args.exchange)
+    parity = sharded_parity(mem, q, o_full, l_full, sm_scale, rank, world, n_rows=args.parity_rows)
+    del o_full, l_full
 
     # end to end in the reference's layout of the ring (queries sequence-sharded like the keys): every rank takes its
     # own slice of the queries from pinned host memory and returns the result for that slice to pinned host memory
@@ -504,37 +694,44 @@ def run_ring(args, rank, world):
         o_host.copy_(o, non_blocking=True)
         l_host.copy_(lse, non_blocking=True)
 
-    for _ in range(2):
+    for _ in range(3):
         e2e_step()
-    e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         e2e_step()
     e1.record()
     barrier()
-    e2e_ms = e0.elapsed_time(e1) / args.steps
+    e2e_ms = e0.elapsed_time(e1) / steps
 
     build_med = statistics.median(build_ms)
+    clk = clocks.summary()
     if world > 1:
         t = torch.tensor([step_ms, e2e_ms, build_med, part_ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         step_ms, e2e_ms, build_med, part_ms = t.tolist()
+        mhz = torch.tensor([float(clk["sm_mhz"] or 0)], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(mhz, op=torch.distributed.ReduceOp.MIN)
+        clk["sm_mhz_min_over_ranks"] = mhz.item()
     if rank != 0:
         return None
     peaks = measured_peaks()
     n_queries = H * S
     achieved = attn_bytes / (part_ms * 1e-3) / 1e9
+    kv_mb = 2 * per * shard_len * d * 2 / 1e6
     return {
-        "metric": METRIC, "value": n_queries / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "metric": METRIC, "value": n_queries / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": ("CUT-DOWN " if args.kv_heads else "") + f"cfg5: {H} heads, d={d}, N={cfg.n_keys} keys/head in {cfg.shards} shards of "
                                f"{shard_len}, C={cfg.n_buckets}, Z={cfg.bucket_size} per shard, {S} queries/head",
-                   "parallelism": f"{per} shard(s) per GPU, ring reduce-scatter of partial (O, LSE) + all-gather",
-                   "l2": f"inputs larger than L2 ({attn_bytes / 1e9:.1f} GB gathered per GPU per step)"},
-        "clocks": clocks.summary(),
+                   "parallelism": f"{per} shard(s) per GPU, partial (O, LSE) merged across ranks ({args.exchange})",
+                   "l2": f"a head's local K+V is {kv_mb:.0f} MB per GPU, beyond the 126 MB L2: the gather is served by DRAM"},
+        "clocks": clk,
+        "local_ms": part_ms, "exchange_ms": step_ms - part_ms, "exchange": args.exchange if world > 1 else "none",
+        "ms_x_ghz": step_ms * (clk["sm_mhz"] or 0) / 1e3,
+        "parity": parity,
         "e2e": {"value": n_queries / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": world * q_host.numel() * 2,
                 "d2h_bytes_per_step": world * (o_host.numel() * 4 + l_host.numel() * 4),
@@ -542,12 +739,26 @@ def run_ring(args, rank, world):
                             "all-gathered over NVLink, partial results merged by MAX all-reduce + SUM reduce-scatter, "
                             "every rank copies out the result of its slice"},
         "gpu_launches": int(launches),
-        "roofline": {"kernel": "hashed attention forward (hash + group + attention over the local shards)", "bound": "hbm",
+        "roofline": {"kernel": "hash + group + hashed attention forward over the local shards", "bound": "hbm",
                      "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "peak_source": peaks["source"], "traffic": None, "algorithmic_bytes": attn_bytes, "ms_per_launch": part_ms},
         "index_build": {"metric": "index_build_keys_per_s", "value": H * cfg.n_keys / (build_med * 1e-3), "unit": "keys/s",
                         "ms": build_med, "tflops": 2.0 * cfg.n_buckets * cfg.n_keys * d * H / (build_med * 1e-3) / 1e12},
     }
+
+
+def sharded_record(full):
+    """The compact form of :func:`run_ring`'s line carried by the default workload's line."""
+    if full is None:
+        return None
+    r = full["roofline"]
+    return {"workload": full["config"]["workload"], "parallelism": full["config"]["parallelism"], "scaling": "strong",
+            "n_gpus": full["n_gpus"], "steps": full["steps"], "value": full["value"], "unit": UNIT,
+            "ms_per_step": full["ms_per_step"], "local_ms": full["local_ms"], "exchange_ms": full["exchange_ms"],
+            "exchange": full["exchange"], "build_ms": full["index_build"]["ms"], "ms_x_ghz": full["ms_x_ghz"],
+            "clocks": full["clocks"], "parity": full["parity"], "e2e_value": full["e2e"]["value"],
+            "roofline": {"bound": r["bound"], "achieved": r["achieved"], "peak": r["peak"], "unit": r["unit"], "frac": r["frac"],
+                         "algorithmic_bytes": r["algorithmic_bytes"], "ms_per_launch": r["ms_per_launch"]}}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -664,6 +875,10 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=1,
                     help="head slices of one host-to-host query call (consecutive calls overlap one another, so for "
                          "throughput one slice is best; more slices shorten a single call's latency)")
+    ap.add_argument("--no-comparator", action="store_true", help="skip the reference's Triton kernel (gpu_comparator)")
+    ap.add_argument("--no-sharded", action="store_true", help="default workload: skip the cfg5 `sharded` record")
+    ap.add_argument("--sharded-steps", type=int, default=20, help="timed steps of the `sharded` record (at most --steps)")
+    ap.add_argument("--parity-rows", type=int, default=64, help="cfg5: query rows checked against the CPU oracle")
     ap.add_argument("--kv-heads", type=int, default=0,
                     help="run a cut-down workload with this many KV heads (small case for profiler captures; "
                          "not a benchmark number)")
@@ -681,6 +896,16 @@ def main():
                 print(note, file=sys.stderr)
             torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))))
         res = (run_ring if args.workload == "cfg5" else run_varlen if args.workload == "cfg4" else run_ours)(args, rank, world)
+        if args.workload == "cfg2" and not args.no_sharded and not args.kv_heads:
+            # the sequence-sharded ring configuration rides along in the same line: 8 fixed shards over the ranks
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            if world > 1:
+                torch.distributed.barrier()
+            sh = sharded_record(run_ring(args, rank, world))
+            if res is not None:
+                res["sharded"] = sh
         if world > 1:
             torch.distributed.destroy_process_group()
     if res is not None:

@@ -25,6 +25,12 @@ __global__ void attn_plan_kernel(AttnParams p)
     if (nq <= 0) return;
     int64_t len = p.bucket_off[b + 1] - p.bucket_off[b];
     int nkc = len > 0 ? int((len + p.key_chunk - 1) / p.key_chunk) : 1;
+    if (nkc > p.nkc_max) {
+        // a bucket longer than the max_bucket_len the workspace was sized for: its partials would not fit, so the keys
+        // beyond nkc_max chunks are left out and the anomaly is recorded in the workspace's third counter
+        nkc = p.nkc_max;
+        p.counters[2] = 1;
+    }
     int nqb = (nq + p.q_block - 1) / p.q_block;
     int base = atomicAdd(&p.counters[0], nqb * nkc);
     for (int qb = 0; qb < nqb; ++qb)
@@ -355,7 +361,7 @@ extern "C" int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, i
     const int64_t groups_bound = std::min<int64_t>(total_buckets, n_q_rows);
     p.q_block = use_mma ? (groups_bound >= int64_t(24) * sms ? 32 : 16) : kQB;
 
-    FM_CUDA_OK(cudaMemsetAsync(p.counters, 0, 8, st));
+    FM_CUDA_OK(cudaMemsetAsync(p.counters, 0, 12, st));
     if (L.nkc_max > 1) FM_CUDA_OK(cudaMemsetAsync(p.qparts, 0, size_t(n_q_rows) * 4, st));
     attn_plan_kernel<<<(unsigned)ceil_div(total_buckets, 256), 256, 0, st>>>(p);
     FM_LAUNCHED("attn_plan_kernel");

@@ -88,7 +88,11 @@ def compute_centroids(kq: torch.Tensor, centroids: torch.Tensor, n_hashes: int, 
 
 
 class Memory:
-    """An indexed set of keys/values.  Create with :meth:`build`."""
+    """An indexed set of keys/values.  Create with :meth:`build`.
+
+    Streams.  Every call runs on the current CUDA stream.  Scratch buffers are kept per stream, so calls on different
+    streams may overlap; results are ordered like any other work on their stream.  A memory's own tensors (table, A)
+    are written by :meth:`build` on the stream it ran on: make other streams wait for that stream before they query."""
 
     def __init__(self):
         self.k = self.v = self.A = None
@@ -99,6 +103,7 @@ class Memory:
         self.table_off: List[int] = []
         self.n_heads = self.n_seq = self.d = 0
         self.max_bucket_len = 0
+        self.compacted = False             # True once key_range dropped entries: buckets are ragged, table_off is void
         self._seg_cb_dev = None
         self._q_seg_cache = {}
 
@@ -246,6 +251,9 @@ class Memory:
         off = torch.zeros(counts.numel() + 1, dtype=torch.int64, device=t.device)
         torch.cumsum(counts, 0, out=off[1:])
         self.bucket_off = off
+        # buckets are ragged from here on: the fixed-Z views (table_of, append) no longer apply
+        self.compacted = True
+        self.table_off = []
 
     # ---- views -------------------------------------------------------------------------------------
     @property
@@ -254,6 +262,8 @@ class Memory:
 
     def table_of(self, head: int, seq: int = 0) -> torch.Tensor:
         """``[C, min(Z, N)]`` int32 table of one segment as indices LOCAL to the segment's keys."""
+        if self.compacted:
+            raise ValueError("table_of: key_range compacted this memory's table (ragged buckets): slice `table` with `bucket_off`")
         s = head * self.n_seq + seq
         C = self.seg_cb[s + 1] - self.seg_cb[s]
         t = self.table[self.table_off[s]: self.table_off[s + 1]].reshape(C, -1)
@@ -328,7 +338,8 @@ class Memory:
             hashes = q_hashes.reshape(-1).to(torch.int32).contiguous()
         group_off, perm = ops.group_rows(hashes, self.total_buckets, seg_xb, seg_cb)
         o, lse = ops.hashed_attention(qf, self.k.reshape(-1, d), self.v.reshape(-1, d), self.table, self.bucket_off,
-                                      group_off, perm, sm_scale, self.max_bucket_len, key_chunk=key_chunk)
+                                      group_off, perm, sm_scale, self.max_bucket_len, key_chunk=key_chunk,
+                                      prefill=q_hashes is not None)       # caller-made hashes may fall outside the buckets
         return o.reshape(Hq, S, d), lse.reshape(Hq, S)
 
     def query_backward(self, q: torch.Tensor, sm_scale: float, out: torch.Tensor, lse: torch.Tensor, d_out: torch.Tensor,
@@ -435,7 +446,7 @@ class Memory:
         return dict(A=self.A, table=self.table, bucket_off=self.bucket_off, seg_kb=self.seg_kb, seg_cb=self.seg_cb,
                     seg_z=self.seg_z, table_off=self.table_off, n_heads=self.n_heads, n_seq=self.n_seq, d=self.d,
                     max_bucket_len=self.max_bucket_len, seq_buckets=self.seq_buckets,
-                    cu_seqlens_k=self.cu_seqlens_k)
+                    cu_seqlens_k=self.cu_seqlens_k, compacted=self.compacted)
 
     def append(self, k_new: torch.Tensor, v_new: torch.Tensor) -> "Memory":
         """A memory over the old keys followed by ``k_new`` / ``v_new`` (``[H, N_new, d]``; uniform memories), with the
@@ -444,8 +455,8 @@ class Memory:
         ``fm_table_scores``) and the new block's own top-Z are merged by one exact row select.  The table equals the one
         a full build over all the keys gives.  Returns a new ``Memory``; this one stays valid."""
         from .dist import merge_shard_candidates, shard_candidates
-        if self.n_seq != 1:
-            raise ValueError("append serves uniform memories")
+        if self.n_seq != 1 or self.compacted:
+            raise ValueError("append serves uniform memories whose table was not compacted by key_range")
         dev = L.require_cuda(k_new, v_new)
         H, N, d = self.k.shape
         if k_new.dim() != 3 or k_new.shape[0] != H or k_new.shape[2] != d or v_new.shape != k_new.shape or k_new.dtype != self.k.dtype:
@@ -478,12 +489,18 @@ class Memory:
 
     @classmethod
     def from_state_dict(cls, state: dict, k: torch.Tensor, v: torch.Tensor) -> "Memory":
+        """A memory over ``k`` / ``v`` (the keys and values the state was built from) with the saved index; the index
+        tensors are moved to ``k``'s device wherever the state was loaded to."""
+        dev = L.require_cuda(k, v)
         self = cls()
         for name, val in state.items():
-            setattr(self, name, val)
+            setattr(self, name, val.to(dev) if isinstance(val, torch.Tensor) else val)
+        if self.seg_kb[-1] != k.shape[0] * k.shape[1] or k.shape[2] != self.d or v.shape != k.shape:
+            raise ValueError("from_state_dict: k / v do not have the shape the index was built for")
         self.k, self.v = k.contiguous(), v.contiguous()
         self.centroids_f32 = None
-        self._seg_cb_dev = torch.tensor(self.seg_cb, dtype=torch.int32, device=k.device)
+        self.build_status = torch.zeros((), dtype=torch.int32, device=dev)
+        self._seg_cb_dev = torch.tensor(self.seg_cb, dtype=torch.int32, device=dev)
         return self
 
 

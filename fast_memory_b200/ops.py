@@ -22,13 +22,18 @@ from . import _lib as L
 
 
 class _Workspace:
-    """Per-device scratch buffers that grow on demand and are reused between calls."""
+    """Scratch buffers that grow on demand and are reused between calls, one per (operator, device, CUDA stream).
+
+    Kernels of one operator launched on the same stream run one after the other, so they can share a buffer; calls
+    on DIFFERENT streams may overlap on the device and therefore get buffers of their own.  A buffer is allocated
+    while its stream is current, so when a larger request replaces it the caching allocator hands the old block out
+    again only in that stream's order, after the kernels that still use it."""
 
     def __init__(self):
         self._bufs = {}
 
     def get(self, key: str, nbytes: int, device) -> torch.Tensor:
-        k = (key, device)
+        k = (key, device, torch.cuda.current_stream(device).cuda_stream)
         buf = self._bufs.get(k)
         if buf is None or buf.numel() < nbytes:
             buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
@@ -79,11 +84,15 @@ def group_rows(hashes: torch.Tensor, total_buckets: int, seg_xb: Optional[torch.
 def hashed_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: torch.Tensor,
                      bucket_off: torch.Tensor, group_off: torch.Tensor, perm: torch.Tensor, sm_scale: float,
                      max_bucket_len: int, bucket_kbase: Optional[torch.Tensor] = None, key_chunk: int = 0,
-                     out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None
+                     out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None, prefill: bool = False
                      ) -> Tuple[torch.Tensor, torch.Tensor]:
     """q ``[n_q, d]``, k/v ``[n_k, d]``; flat ``table`` (int32 or int64) cut by ``bucket_off`` (int64
     ``[buckets+1]``); queries grouped by ``group_off`` / ``perm``.  Returns o (q's dtype) and fp32
-    natural-log LSE (``-inf`` where the bucket is empty)."""
+    natural-log LSE (``-inf`` where the bucket is empty).
+
+    Rows that no group claims (a caller-made hash outside ``[0, buckets)`` is dropped by :func:`group_rows`) are not
+    written by the kernel; ``prefill=True`` starts the outputs at o = 0, LSE = -inf so that such rows read as "no key".
+    ``max_bucket_len`` must bound every bucket's length: the part of a longer bucket beyond it is left out."""
     dev = L.require_cuda(q, k, v, table, bucket_off, group_off, perm, bucket_kbase)
     if not (q.dtype == k.dtype == v.dtype):
         raise TypeError("q, k and v must share a dtype")
@@ -94,9 +103,10 @@ def hashed_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: t
     n_q, d = q.shape
     total_buckets = bucket_off.numel() - 1
     if out is None:
-        out = torch.empty_like(q)
+        out = torch.zeros_like(q) if prefill else torch.empty_like(q)
     if lse is None:
-        lse = torch.empty(n_q, dtype=torch.float32, device=dev)
+        lse = torch.full((n_q,), float("-inf"), dtype=torch.float32, device=dev) if prefill else \
+            torch.empty(n_q, dtype=torch.float32, device=dev)
     need = L.lib().fm_hashed_attn_workspace_bytes(n_q, total_buckets, int(max_bucket_len), d, int(key_chunk))
     ws = _ws.get("attn", need, dev)
     L.check(L.lib().fm_hashed_attn_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.dtype_id(q.dtype), d, n_q, k.shape[0],
@@ -218,11 +228,13 @@ def topz_select(Y: torch.Tensor, Z: int, index_base: int = 0) -> torch.Tensor:
     return out
 
 
+@torch.library.custom_op("fast_memory_b200::shard_filter", mutates_args=())
 def shard_filter(k_hashes: torch.Tensor, lo: int, hi: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """``k_hashes`` ``[C, H, Z]`` int64 global key indices -> (flat int64 indices of the entries in ``[lo, hi)``
     rebased by ``lo`` and packed (head, bucket, slot); counts ``[H, C]`` int64).  The flat tensor keeps its full
     ``C*H*Z`` capacity (only the first ``counts.sum()`` entries are meaningful), which avoids reading the total
-    back from the device."""
+    back from the device.  Registered as an operator so that a traced caller (the reference compiles this step,
+    mem:106) sees one opaque node."""
     dev = L.require_cuda(k_hashes)
     assert k_hashes.dim() == 3 and k_hashes.dtype == torch.int64
     k_hashes = k_hashes.contiguous()
@@ -233,6 +245,12 @@ def shard_filter(k_hashes: torch.Tensor, lo: int, hi: int) -> Tuple[torch.Tensor
     L.check(L.lib().fm_shard_filter(L.ptr(k_hashes), C, H, Z, int(lo), int(hi), L.ptr(flat), L.ptr(counts), L.ptr(ws),
                                     ws.numel(), L.stream_ptr(dev)), "fm_shard_filter")
     return flat, counts
+
+
+@shard_filter.register_fake
+def _(k_hashes, lo, hi):
+    C, H, Z = k_hashes.shape
+    return k_hashes.new_empty(C * H * Z), k_hashes.new_empty(H, C)
 
 
 def unit_rows(X: torch.Tensor) -> torch.Tensor:
@@ -259,32 +277,133 @@ def _uniform_kbase(B: int, C: int, N: int, device) -> torch.Tensor:
     return t
 
 
-@torch.library.custom_op("fast_memory_b200::attention_hash_varlen", mutates_args=())
-def _attention_hash_varlen_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_hashes: torch.Tensor,
-                              k_hash_counts: torch.Tensor, q_hashes: torch.Tensor, sm_scale: float,
-                              max_bucket_len: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Registered operator behind :func:`attention_hash_varlen` (the reference registers
-    ``notbad::attention_hash_varlen``, tk:16).  Returns o ``[B, S, d]`` and fp32 natural-log LSE ``[B, S]``."""
-    B, S, d = q.shape
-    N = k.shape[1]
-    C = k_hash_counts.shape[1]
-    dev = q.device
+def _grouping(q_hashes: torch.Tensor, k_hash_counts: torch.Tensor, S: int, N: int):
+    """(bucket_off, group_off, perm, kbase) of a uniform batch: ``q_hashes`` ``[B, S]``, ``k_hash_counts`` ``[B, C]``."""
+    B, C = k_hash_counts.shape
+    dev = q_hashes.device
     bucket_off = torch.zeros(B * C + 1, dtype=torch.int64, device=dev)
-    torch.cumsum(k_hash_counts.reshape(-1), 0, out=bucket_off[1:])
+    bucket_off[1:] = torch.cumsum(k_hash_counts.reshape(-1).to(torch.int64), 0)
     hashes = q_hashes.reshape(-1).to(torch.int32)
     seg_xb = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
     seg_cb = torch.arange(0, (B + 1) * C, C, dtype=torch.int32, device=dev)
     group_off, perm = group_rows(hashes, B * C, seg_xb, seg_cb)
-    table = k_hashes if k_hashes.dtype in (torch.int32, torch.int64) else k_hashes.to(torch.int64)
-    o, lse = hashed_attention(q.reshape(B * S, d), k.reshape(B * N, d), v.reshape(B * N, d), table.contiguous(),
-                              bucket_off, group_off, perm, sm_scale, max_bucket_len,
-                              bucket_kbase=_uniform_kbase(B, C, N, dev))
+    return bucket_off, group_off, perm, _uniform_kbase(B, C, N, dev)
+
+
+def _index_table(k_hashes: torch.Tensor) -> torch.Tensor:
+    return (k_hashes if k_hashes.dtype in (torch.int32, torch.int64) else k_hashes.to(torch.int64)).contiguous()
+
+
+@torch.library.custom_op("fast_memory_b200::hashed_attention_grouped", mutates_args=())
+def _hashed_attention_grouped_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_hashes: torch.Tensor,
+                                 k_hash_counts: torch.Tensor, q_hashes: torch.Tensor, sm_scale: float,
+                                 max_bucket_len: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The operator behind :func:`attention_hash_varlen`, taking that function's own arguments: grouping of the
+    queries by bucket and the attention, both in the library.  Returns o ``[B, S, d]`` in the original query order
+    and fp32 natural-log LSE ``[B, S]``."""
+    B, S, d = q.shape
+    N = k.shape[1]
+    bucket_off, group_off, perm, kbase = _grouping(q_hashes, k_hash_counts, S, N)
+    o, lse = hashed_attention(q.reshape(B * S, d), k.reshape(B * N, d), v.reshape(B * N, d), _index_table(k_hashes),
+                              bucket_off, group_off, perm, sm_scale, max_bucket_len, bucket_kbase=kbase, prefill=True)
     return o.reshape(B, S, d), lse.reshape(B, S)
 
 
-@_attention_hash_varlen_op.register_fake
+@_hashed_attention_grouped_op.register_fake
 def _(q, k, v, k_hashes, k_hash_counts, q_hashes, sm_scale, max_bucket_len):
     return torch.empty_like(q), q.new_empty(q.shape[:-1], dtype=torch.float32)
+
+
+@torch.library.custom_op("fast_memory_b200::hashed_attention_grouped_backward", mutates_args=())
+def _hashed_attention_grouped_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_hashes: torch.Tensor,
+                                     k_hash_counts: torch.Tensor, q_hashes: torch.Tensor, o: torch.Tensor,
+                                     lse: torch.Tensor, d_o: torch.Tensor, sm_scale: float
+                                     ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of ``hashed_attention_grouped`` with respect to q, k and v for the output gradient ``d_o`` (the
+    gathered-row form of mem:166-206), in the dtypes of q, k and v."""
+    B, S, d = q.shape
+    N = k.shape[1]
+    bucket_off, group_off, perm, kbase = _grouping(q_hashes, k_hash_counts, S, N)
+    dq, dk, dv = hashed_attention_backward(q.reshape(B * S, d), k.reshape(B * N, d), v.reshape(B * N, d),
+                                           _index_table(k_hashes), bucket_off, group_off, perm, sm_scale,
+                                           o.reshape(B * S, d).contiguous(), lse.reshape(B * S).contiguous(),
+                                           d_o.reshape(B * S, d).contiguous(), bucket_kbase=kbase)
+    return dq.reshape(q.shape).to(q.dtype), dk.reshape(k.shape).to(k.dtype), dv.reshape(v.shape).to(v.dtype)
+
+
+@_hashed_attention_grouped_bwd_op.register_fake
+def _(q, k, v, k_hashes, k_hash_counts, q_hashes, o, lse, d_o, sm_scale):
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+def _grouped_setup_context(ctx, inputs, output):
+    q, k, v, k_hashes, k_hash_counts, q_hashes, sm_scale, _ = inputs
+    o, lse = output
+    ctx.save_for_backward(q, k, v, k_hashes, k_hash_counts, q_hashes, o, lse)
+    ctx.sm_scale = sm_scale
+
+
+def _grouped_backward(ctx, grad_o, grad_lse):
+    # The reference registers a backward that returns no gradient at all (tk:44-48) and differentiates its dense
+    # restatement instead (mem:166-206).  Here the operator itself is differentiable in q, k and v through o; the LSE
+    # output is treated as a constant (a caller that merges partial results differentiates the merged pair through
+    # Memory.query_backward, as mem:354-378 does).
+    q, k, v, k_hashes, k_hash_counts, q_hashes, o, lse = ctx.saved_tensors
+    if grad_o is None:
+        return (None,) * 8
+    dq, dk, dv = _hashed_attention_grouped_bwd_op(q, k, v, k_hashes, k_hash_counts, q_hashes, o, lse,
+                                                  grad_o.contiguous(), ctx.sm_scale)
+    return dq, dk, dv, None, None, None, None, None
+
+
+_hashed_attention_grouped_op.register_autograd(_grouped_backward, setup_context=_grouped_setup_context)
+
+
+@torch.library.custom_op("fast_memory_b200::attention_hash_varlen", mutates_args=())
+def _attention_hash_varlen_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                              k_hashes: torch.Tensor, k_hash_counts: torch.Tensor, k_hash_offset: torch.Tensor,
+                              q_hashes_z: torch.Tensor, q_hashes_count: torch.Tensor, q_hashes_offset: torch.Tensor,
+                              sm_scale: float, q_seq_len: int, kv_seq_len: int,
+                              d_head: int, n_buckets: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Drop-in for the reference's registered operator ``notbad::attention_hash_varlen`` (tk:16-41): the same fourteen
+    arguments with the same meaning and the same outputs.
+
+    ``q`` ``[B, S, d]`` holds the queries ALREADY sorted by bucket inside each batch row (tk:75-78); group g - one per
+    non-empty (row, bucket) pair, in sorted order - is bucket ``q_hashes_z[g]`` with ``q_hashes_count[g]`` queries
+    starting at flat position ``q_hashes_offset[g]`` (its batch row is ``offset // q_seq_len``, tk:181);
+    ``k_hash_offset`` ``[B, C]`` is the exclusive prefix sum of ``k_hash_counts`` over the flattened table (tk:86-88).
+    Returns o in q's dtype in the sorted order and the fp32 LSE in BASE 2 (``m + log2 l``, tk:222), ``-inf`` for a
+    bucket without keys - what the reference kernel writes; its wrapper converts afterwards (tk:111)."""
+    B, S, d = q.shape
+    N, C = kv_seq_len, n_buckets
+    dev = q.device
+    gb = (q_hashes_offset // q_seq_len) * C + q_hashes_z
+    n_per_bucket = torch.zeros(B * C, dtype=torch.int64, device=dev)
+    n_per_bucket.index_put_((gb,), q_hashes_count.to(torch.int64))
+    group_off = torch.zeros(B * C + 1, dtype=torch.int32, device=dev)
+    group_off[1:] = torch.cumsum(n_per_bucket, 0)
+    perm = torch.arange(B * S, dtype=torch.int32, device=dev)                # the queries come sorted
+    flat_counts = k_hash_counts.reshape(-1)
+    bucket_off = torch.cat([k_hash_offset.reshape(-1).to(torch.int64),
+                            (k_hash_offset.reshape(-1)[-1:] + flat_counts[-1:]).to(torch.int64)])
+    max_len = int(flat_counts.max().item()) if flat_counts.numel() else 0
+    o, lse = hashed_attention(q.reshape(B * S, d), k.reshape(B * N, d), v.reshape(B * N, d), _index_table(k_hashes),
+                              bucket_off, group_off, perm, sm_scale, max_len, bucket_kbase=_uniform_kbase(B, C, N, dev))
+    return o.reshape(B, S, d), (lse * (1.0 / math.log(2))).reshape(B, S)
+
+
+@_attention_hash_varlen_op.register_fake
+def _(q, k, v, k_hashes, k_hash_counts, k_hash_offset, q_hashes_z, q_hashes_count, q_hashes_offset,
+      sm_scale, q_seq_len, kv_seq_len, d_head, n_buckets):
+    return torch.empty_like(q), q.new_empty(q.shape[:-1], dtype=torch.float32)
+
+
+def _attention_hash_varlen_backward(ctx, grad_o, grad_lse):
+    # as the reference registers it (tk:44-48): no gradient flows through this operator
+    return (None,) * 14
+
+
+_attention_hash_varlen_op.register_autograd(_attention_hash_varlen_backward)
 
 
 def attention_hash_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
@@ -324,7 +443,7 @@ def attention_hash_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     # the longest bucket sizes the work split; like the reference wrapper (unique_consecutive, tk:81)
     # this reads one number back from the device
     max_len = int(k_hash_counts.max().item()) if k_hash_counts.numel() else 0
-    o, lse = _attention_hash_varlen_op(q, k, v, k_hashes, k_hash_counts, q_hashes, float(sm_scale), max_len)
+    o, lse = _hashed_attention_grouped_op(q, k, v, k_hashes, k_hash_counts, q_hashes, float(sm_scale), max_len)
     if return_fp32_lse:
         return o, lse
     lse = (lse * (1.0 / math.log(2))).to(q.dtype) * math.log(2)

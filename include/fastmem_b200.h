@@ -114,6 +114,10 @@ int fm_group_rows_static(const int32_t *hash, int64_t n_rows, int64_t total_buck
  *   lse       [n_q_rows] fp32 natural-log LSE; -inf (and o = 0) where the bucket is empty
  *   key_chunk  keys per work item; 0 lets the library choose.  Buckets longer than one chunk are
  *              split over CTAs and combined by a second kernel (needs the workspace).
+ *   max_bucket_len  an upper bound of every bucket's length (it sizes the workspace).  The keys of a
+ *              longer bucket beyond the bound are left out, and the third int32 of the workspace
+ *              reads 1 after the launch.  Query rows that no group of group_off / perm lists are not
+ *              written: start o / lse at 0 / -inf if the hashes are not known to be in range.
  * ------------------------------------------------------------------------------------------- */
 size_t fm_hashed_attn_workspace_bytes(int64_t n_q_rows, int64_t total_buckets, int64_t max_bucket_len, int d,
                                       int64_t key_chunk);

@@ -1,8 +1,9 @@
-"""Generate the golden vectors in this folder by running the REFERENCE's own code on CPU.
+"""Generate the golden vectors in this folder by running the REFERENCE's own code.
 
 Run once where the reference checkout is available (it is not needed to run the tests):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference                       # CPU: fp32 / fp16 vectors
+    python tests/golden/make_golden.py /path/to/reference --native-bf16 OUTDIR  # on a GPU: bf16 vectors
 
 What is run, unmodified:
   * ``triton_kernel.attention_hash_varlen`` (the wrapper, tk:51-119) with the Triton kernel ``_attn_fwd``
@@ -13,6 +14,11 @@ What is run, unmodified:
     and ``memory.compute_centroids`` (mem:209-231), eager (``TORCHDYNAMO_DISABLE=1``).
 A stub ``labml`` module stands in for the third-party logger the reference imports.
 
+``--native-bf16`` runs the same wrapper with the kernel compiled natively by Triton on the GPU present (the
+CPU interpreter cannot do bf16), launcher and all unmodified, on bf16 inputs generated on the CPU from the
+same seeded recipe; besides the wrapper's outputs (LSE rounded to bf16, tk:111) it records the fp32 LSE the
+kernel itself wrote, converted to natural log.
+
 Inputs follow the reference's self-test generator (tk:302-322): N(0, 0.5^2) tensors, random query
 hashes, table = topk of uniform noise, entries >= 0.9 N masked out.
 """
@@ -20,7 +26,9 @@ import os
 import sys
 import types
 
-os.environ["TRITON_INTERPRET"] = "1"
+NATIVE = "--native-bf16" in sys.argv
+if not NATIVE:
+    os.environ["TRITON_INTERPRET"] = "1"
 os.environ["TORCHDYNAMO_DISABLE"] = "1"
 
 import numpy as np
@@ -193,8 +201,60 @@ def centroids_case(mem, name, seed):
     print(name, tuple(out.shape))
 
 
+def native_attn_case(tk, out_dir, name, B, S, N, C, Z, d, dtype, seed, keep=0.9):
+    """The reference wrapper and kernel, natively compiled, on a GPU.  Inputs are drawn on the CPU."""
+    import math
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.randn(B, S, d, generator=g) * 0.5).to(dtype)
+    k = (torch.randn(B, N, d, generator=g) * 0.5).to(dtype)
+    v = (torch.randn(B, N, d, generator=g) * 0.5).to(dtype)
+    q_hashes = torch.randint(C, (B, S), generator=g)
+    table = torch.topk(torch.rand(B, C, N, generator=g), dim=-1, k=Z, sorted=True)[1]
+    mask = table < int(N * keep)
+    mask[:, C // 2] = False                  # one bucket without keys in every batch row
+    counts = mask.to(torch.long).sum(-1)
+    sm_scale = d ** -0.5
+    dev = "cuda"
+    seen = {}
+    launch = tk._attention_hash_varlen
+
+    def spy(*a, **kw):                        # the fp32 base-2 LSE as the kernel wrote it, in sorted order
+        o, lse = launch(*a, **kw)
+        seen["lse2"] = lse.clone()
+        return o, lse
+
+    tk._attention_hash_varlen = spy
+    o, lse = tk.attention_hash_varlen(q.to(dev), k.to(dev), v.to(dev), table[mask].to(dev), counts.to(dev),
+                                      q_hashes.to(dev), sm_scale)
+    tk._attention_hash_varlen = launch
+    order = torch.sort(q_hashes, dim=1, stable=True)[1]
+    lse_f32 = torch.empty(B, S)
+    lse_f32[torch.arange(B)[:, None], order] = seen["lse2"].cpu() * math.log(2)
+    np.savez_compressed(os.path.join(out_dir, name + ".npz"),
+                        q=_np(q), k=_np(k), v=_np(v), q_hashes=q_hashes.numpy(),
+                        k_hashes=table[mask].numpy(), k_hash_counts=counts.numpy(),
+                        sm_scale=np.float64(sm_scale), dtype=str(dtype).replace("torch.", ""),
+                        o=_np(o.cpu()), lse=_np(lse.cpu()), lse_f32=lse_f32.numpy(),
+                        device=torch.cuda.get_device_name(0))
+    print(name, "o", tuple(o.shape), "lse range", float(lse_f32[torch.isfinite(lse_f32)].min()), float(lse_f32.max()))
+
+
+def main_native(ref, out_dir):
+    _stub_labml()
+    sys.path.insert(0, ref)
+    import triton_kernel as tk
+    os.makedirs(out_dir, exist_ok=True)
+    native_attn_case(tk, out_dir, "attn_bf16_ragged", 2, 300, 1024, 16, 100, 64, torch.bfloat16, seed=25)
+    native_attn_case(tk, out_dir, "attn_bf16_d128", 2, 200, 2048, 8, 300, 128, torch.bfloat16, seed=26)
+    native_attn_case(tk, out_dir, "attn_f16_native_d64", 1, 150, 1024, 8, 200, 64, torch.float16, seed=27)
+
+
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference [--native-bf16 OUTDIR]")
+    ref = sys.argv[1]
+    if NATIVE:
+        return main_native(ref, sys.argv[sys.argv.index("--native-bf16") + 1])
     tk, mem = _load_reference(ref)
     # the reference self-test's small shape (tk:500) and cut-down versions of its large one (tk:502)
     attn_case(tk, "attn_f32_tiny", 1, 24, 1024, 8, 16, 16, torch.float32, seed=20)

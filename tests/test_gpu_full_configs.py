@@ -151,3 +151,43 @@ def test_config5_shards_several_workspace_groups():
     check_table_properties(mem)
     check_buckets_against_oracle(mem, 1, [0, 500, 1023])
     check_buckets_against_oracle(mem, 14, [3, 777])
+
+
+def test_config5_full_size_queries_over_all_shards():
+    """Two heads of the ring config at full size, queried: 8 shards of 524288 keys per head on one device through
+    ``ShardedMemory`` (every bucket = the concatenation of its 8 per-shard tables, 65536 keys), all 16384 queries of a
+    head.  The local table equals the per-shard oracle tables side by side; hashes and sampled query rows equal the
+    oracle over the concatenated per-shard buckets; merging eight independent per-shard memories gives the same."""
+    from fast_memory_b200.dist import ShardedMemory
+    cfg = synth.config("cfg5")
+    q, k, v = synth.make(cfg, seed=6, device=DEV, kv_heads=2)
+    H, N, d = k.shape
+    S = q.shape[1]
+    L, C, Z = N // cfg.shards, cfg.n_buckets, cfg.bucket_size
+    sm = d ** -0.5
+    A = torch.stack([fm.kmeans_projection(k[h, :L].contiguous(), q[h, :C].contiguous(), 1, [0, L], [0, C])[0] for h in range(H)])
+    mem = ShardedMemory.build(k, v, L, A=A, bucket_size=Z)
+    loc = mem.local
+    assert loc.max_bucket_len == cfg.shards * Z and loc.table.numel() == H * C * cfg.shards * Z
+    # the table of bucket (h, c): per-shard oracle rows (canonical projection + top-Z over the shard's keys), shard by shard
+    h, buckets = 1, [0, 511, 1023]
+    for s_ in (0, 5):
+        ref = O.topz(O.project(A[h, buckets].cpu(), k[h, s_ * L:(s_ + 1) * L].cpu()), Z) + s_ * L
+        got = loc.table.reshape(H, C, cfg.shards, Z)[h, buckets, s_].cpu().numpy() - h * N
+        assert np.array_equal(got, ref), f"shard {s_}"
+    o, lse = mem.query(q, sm)
+    assert o.dtype == torch.float32 and o.shape == (H, S, d)
+    hashes = loc.hash_queries(q)
+    qf, of, lf, hf = q.reshape(-1, d), o.reshape(-1, d), lse.reshape(-1), hashes.reshape(-1)
+    check_hashes(loc, qf, hf, 1, torch.arange(S, S + 2048, device=DEV))
+    g = torch.Generator().manual_seed(7)
+    rows = torch.randint(H * S, (20,), generator=g).tolist()
+    check_sampled_queries(loc, qf, of, lf, hf, lambda r: r // S, rows, sm, cfg.dtype)
+    # the reference's structure: one memory per shard, partial results LSE-merged (mem:319-332)
+    out, acc_l = None, None
+    for s_ in range(cfg.shards):
+        ms = fm.Memory.build(k[:, s_ * L:(s_ + 1) * L].contiguous(), v[:, s_ * L:(s_ + 1) * L].contiguous(), A=A, bucket_size=Z)
+        bo, bl = ms.query(q, sm, q_hashes=hashes)
+        out, acc_l = fm.update_out_and_lse(out, acc_l, bo, bl)
+        del ms
+    assert (out - o).abs().max() <= 2e-2 and (acc_l.squeeze(-1) - lse).abs().max() <= 1e-3

@@ -312,13 +312,25 @@ def test_head_slices_and_host_pipeline_match_one_call():
         assert torch.equal(oi, o_ref.cpu()) and torch.equal(li, l_ref.cpu())
 
 
-def test_state_dict_round_trip():
+def test_state_dict_round_trip(tmp_path):
+    """The index goes through ``torch.save`` / ``torch.load`` on disk (map_location CPU, as a checkpoint is read) and
+    serves the same answers; the restored table is the oracle's table."""
     cfg = synth.config("cfg1")
     q, k, v = synth.make(cfg, seed=2)
     mem = fm.Memory.build(k.to(DEV), v.to(DEV), n_buckets=32, bucket_size=100, kmeans_iters=1)
-    m2 = fm.Memory.from_state_dict(mem.state_dict(), k.to(DEV), v.to(DEV))
+    path = tmp_path / "memory_index.pt"
+    torch.save(mem.state_dict(), path)
+    state = torch.load(path, map_location="cpu")
+    assert state["table"].device.type == "cpu"
+    m2 = fm.Memory.from_state_dict(state, k.to(DEV), v.to(DEV))
+    m2.check_build()
     a, b = mem.query(q.to(DEV), 0.2), m2.query(q.to(DEV), 0.2)
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    A = O.spherical_kmeans(k[0], k[0, :32], 1)
+    assert np.array_equal(m2.table_of(0).cpu().numpy(), O.build_table(A[None], k, 100)[0])
+    o_ref, l_ref = O.hashed_attention(q, k, v, torch.from_numpy(O.build_table(A[None], k, 100)).reshape(-1).long(),
+                                      torch.full((1, 32), 100), torch.from_numpy(O.query_hash(A[None], q)).long(), 0.2)
+    assert (b[0].cpu() - o_ref).abs().max() <= 1e-4 and (b[1].cpu() - l_ref).abs().max() <= 1e-3
 
 
 def test_compute_centroids_code_variant(golden_dir):
@@ -388,7 +400,9 @@ def test_append_equals_full_build():
     mem = mem.append(kd[:, 16384:20000].contiguous(), vd[:, 16384:20000].contiguous())
     mem = mem.append(kd[:, 20000:].contiguous(), vd[:, 20000:].contiguous())          # twice, ragged block sizes
     assert torch.equal(mem.k, kd) and torch.equal(mem.v, vd)
+    ref_table = O.build_table(A.cpu(), k, Z)                         # the oracle over ALL the keys: independent of Memory.build
     for h in range(2):
+        assert np.array_equal(mem.table_of(h).cpu().numpy(), ref_table[h]), f"head {h} differs from the oracle"
         assert torch.equal(mem.table_of(h), full.table_of(h)), f"head {h}"
     o1, l1 = mem.query(q.to(DEV), 0.1)
     o2, l2 = full.query(q.to(DEV), 0.1)
@@ -397,5 +411,11 @@ def test_append_equals_full_build():
     small = fm.Memory.build(kd[:, :300].contiguous(), vd[:, :300].contiguous(), A=A, bucket_size=Z)
     small = small.append(kd[:, 300:900].contiguous(), vd[:, 300:900].contiguous())
     ref = fm.Memory.build(kd[:, :900].contiguous(), vd[:, :900].contiguous(), A=A, bucket_size=Z)
+    ref_small = O.build_table(A.cpu(), k[:, :900].contiguous(), Z)
     for h in range(2):
         assert torch.equal(small.table_of(h), ref.table_of(h))
+        assert np.array_equal(small.table_of(h).cpu().numpy(), ref_small[h])
+    # a grown memory persists like a built one
+    m3 = fm.Memory.from_state_dict(mem.state_dict(), kd, vd)
+    o3, l3 = m3.query(q.to(DEV), 0.1)
+    assert torch.equal(o3, o1) and torch.equal(l3, l1)

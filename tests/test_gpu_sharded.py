@@ -89,8 +89,10 @@ def test_global_table_from_shard_candidates_equals_single_device_build():
     cands = [fmd.shard_candidates(kd[:, s * L:(s + 1) * L].contiguous(), Ad, Z, s * L) for s in range(n_shards)]
     k_hashes = fmd.merge_shard_candidates([c[0] for c in cands], [c[1] for c in cands], Z)        # [C, H, Z]
     assert k_hashes.shape == (C, H, Z) and k_hashes.dtype == torch.int64
+    oracle_table = O.build_table(A, k, Z)                              # CPU oracle over the concatenated keys
     ref = fm.Memory.build(kd, vd, A=Ad, bucket_size=Z)
     for h in range(H):
+        assert np.array_equal(k_hashes[:, h].cpu().numpy(), oracle_table[h]), f"head {h} differs from the oracle"
         assert torch.equal(k_hashes[:, h].cpu(), ref.table_of(h).long().cpu()), f"head {h}"
     # attending through the global table, shard by shard, equals the single memory
     sm = cfg.d ** -0.5
@@ -125,7 +127,9 @@ def test_two_ranks_equal_single_device():
     assert (l1.cpu() - l2).abs().max() <= 1e-3
     # global table built by the two ranks = the table one device builds over all the keys; queries through it
     whole = fm.Memory.build(k.to(DEV), v.to(DEV), A=A.to(DEV), bucket_size=Z)
+    oracle_table = O.build_table(A, k, Z)
     for h in range(H):
+        assert np.array_equal(kh[:, h].numpy(), oracle_table[h]), f"head {h} differs from the oracle"
         assert torch.equal(kh[:, h], whole.table_of(h).long().cpu())
     ow, lw = whole.query(q.to(DEV), cfg.d ** -0.5)
     assert (ow.float().cpu() - go).abs().max() <= 2e-2 and (lw.cpu() - gl).abs().max() <= 3e-2

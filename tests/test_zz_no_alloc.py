@@ -49,7 +49,16 @@ def test_static_scratch_grouping_matches_workspace_grouping_twice():
     cb = torch.tensor([0, 7, 40, 300], dtype=torch.int32, device=DEV)
     local = torch.cat([torch.randint(7, (300,), generator=g), torch.randint(33, (1,), generator=g),
                        torch.randint(260, (699,), generator=g)]).int().to(DEV)
-    got2 = _group_static(L, lib, local, 300, xb, cb)
+    group_off2 = torch.empty(301, dtype=torch.int32, device=DEV)
+    perm2 = torch.empty(1000, dtype=torch.int32, device=DEV)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    L.check(lib.fm_group_rows_static(L.ptr(local), 1000, 300, 3, L.ptr(xb), L.ptr(cb), L.ptr(group_off2), L.ptr(perm2),
+                                     L.stream_ptr(torch.device(DEV))), "fm_group_rows_static")
+    torch.cuda.synchronize()
+    # the claim itself: with the outputs made beforehand, the call leaves the device's free memory where it was
+    assert torch.cuda.mem_get_info()[0] == free_before
+    got2 = (group_off2, perm2)
     seg = torch.bucketize(torch.arange(1000, device=DEV), xb[1:].long(), right=True)
     _same_grouping(got2, fm.group_rows(local, 300, xb, cb), local + cb[seg])
 
