@@ -167,7 +167,7 @@ static FusedList fused_segments(int n_seg, const int64_t *seg_kb, const int64_t 
     // with 32-bit byte offsets
     if (!F.seg.empty()) {
         const FusedPlan P = fused_plan((int)F.seg.size(), F.nk.data(), F.nbk.data(), F.zc.data());
-        if (P.cap > kFusedMaxCap || uint64_t(P.group_buckets) * uint64_t(P.cap) * 16 >= (uint64_t(1) << 32)) return FusedList();
+        if (P.cap > kFusedMaxCap || P.sel_smem > kFusedMaxSelSmem || uint64_t(P.group_buckets) * uint64_t(P.cap) * 16 >= (uint64_t(1) << 32)) return FusedList();
     }
     return F;
 }

@@ -22,6 +22,7 @@
 #include "topz_row.cuh"
 
 #include <cmath>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -33,7 +34,7 @@ namespace fm {
 constexpr float kBandEps = 1.0f / 4096.0f;
 constexpr int kMaxBand = 512;               // largest band re-scored exactly; beyond it the bucket goes to the fallback
 constexpr int kMaxFail = 64;                // buckets the fallback can take per group of segments
-constexpr int kMaxSample = 49152;           // sample scores of one bucket held in shared memory (192 KB)
+constexpr int kMaxSample = 49152;           // sample scores of one bucket the threshold kernel can hold in its registers
 constexpr int kMaxRanges = 8;               // key ranges a bucket tile's keys may be split into (one CTA each)
 
 struct FusedSeg {
@@ -93,152 +94,7 @@ __device__ __forceinline__ int seg_of_out_row(const FusedSeg *__restrict__ segs,
     return lo;
 }
 
-__device__ __forceinline__ float key_to_float(uint32_t key)
-{
-    return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
-}
-
-// ---- selection of the r-th largest of n floats ----------------------------------------------------------------------
-// All threads of the CTA call; `load(i)` returns value i (from global memory / L2: the lists are re-read in a few
-// passes instead of being held in shared memory, which keeps a CTA's footprint at a few KB and many CTAs per SM
-// in flight).  The values are binned LINEARLY between their minimum and maximum (scores near a threshold are
-// spread over a narrow interval, where the radix digits of the floats would all collide), the bin holding the
-// r-th largest is found from the top, and the search recurses into that bin until it holds at most kSmallSel
-// values, which are ranked directly.  Returns theta = the r-th largest value (the same in every thread).
-constexpr int kSelBins = 512;
-constexpr int kSmallSel = 256;
-
-// COPIES: lanes spread their increments over that many copies of the histogram (a power of two) - scores pile up in
-// a few bins and same-address shared-memory atomics serialise; small inputs do with one.
-template <int COPIES> struct SelScratch {
-    static constexpr int kCopies = COPIES;
-    int hist[COPIES * kSelBins];
-    float small[kSmallSel];
-    float red[64];
-    int bin, want, count, n_small;
-    float lo, hi, theta;
-};
-
-// A value source exposes  template <class F> void for_each(F f)  which calls f(ordinal, score) for the values this
-// thread owns.  When the caller knows an interval [lo0, hi0] that holds every value it passes it (have_range) and
-// the first look at the values is saved.
-template <class Source, class Scratch>
-__device__ __forceinline__ float select_rth(const Source &src, int n, int r, Scratch &S, bool have_range = false, float lo0 = 0.f,
-                                            float hi0 = 0.f)
-{
-    constexpr int kHistCopies = Scratch::kCopies;
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nthreads = blockDim.x, nw = (nthreads + 31) >> 5;
-    float lo = -INFINITY, hi = INFINITY;
-    int want = r;                                            // rank from the top inside [lo, hi]
-    for (int iter = 0; iter < 40; ++iter) {
-        if (iter == 0 && have_range) {
-            __syncthreads();
-            for (int i = t; i < kHistCopies * kSelBins; i += nthreads) S.hist[i] = 0;
-            __syncthreads();
-            lo = lo0; hi = hi0;
-        } else {
-            // exact value range of what is left
-            float mn = INFINITY, mx = -INFINITY;
-            src.for_each([&](int, float v) {
-                if (v >= lo && v <= hi) { mn = fminf(mn, v); mx = fmaxf(mx, v); }
-            });
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) {
-                mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-            }
-            __syncthreads();
-            if (lane == 0) { S.red[warp] = mn; S.red[32 + warp] = mx; }
-            for (int i = t; i < kHistCopies * kSelBins; i += nthreads) S.hist[i] = 0;
-            __syncthreads();
-            mn = INFINITY; mx = -INFINITY;
-            for (int w = 0; w < nw; ++w) { mn = fminf(mn, S.red[w]); mx = fmaxf(mx, S.red[32 + w]); }
-            lo = mn; hi = mx;
-        }
-        if (!(hi > lo)) return lo;                           // every remaining value is equal (uniform across the CTA)
-        const float scale = float(kSelBins) / (hi - lo);
-        src.for_each([&](int, float v) {
-            if (v >= lo && v <= hi) atomicAdd(&S.hist[(lane & (kHistCopies - 1)) * kSelBins + min(kSelBins - 1, int((v - lo) * scale))], 1);
-        });
-        __syncthreads();
-        for (int i = t; i < kSelBins; i += nthreads) {       // fold the copies into copy 0
-            int sum = 0;
-#pragma unroll
-            for (int c = 0; c < kHistCopies; ++c) sum += S.hist[c * kSelBins + i];
-            S.hist[i] = sum;
-        }
-        __syncthreads();
-        // find the bin from the top: thread t owns bins [t * per, (t + 1) * per)
-        {
-            const int per = (kSelBins + nthreads - 1) / nthreads;
-            int mine = 0;
-            for (int k = 0; k < per; ++k) mine += t * per + k < kSelBins ? S.hist[t * per + k] : 0;
-            int inc = mine;                                  // suffix sum inside the warp
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int o = __shfl_down_sync(0xffffffffu, inc, off);
-                if (lane + off < 32) inc += o;
-            }
-            int *wsum = reinterpret_cast<int *>(S.red);
-            __syncthreads();
-            if (lane == 0) wsum[warp] = inc;
-            __syncthreads();
-            int above = inc - mine;                          // values in bins above this thread's
-            for (int w = warp + 1; w < nw; ++w) above += wsum[w];
-            if (mine > 0 && above < want && want <= above + mine) {
-                int acc = above;
-                for (int k = per - 1; k >= 0; --k) {
-                    const int h = t * per + k < kSelBins ? S.hist[t * per + k] : 0;
-                    if (want <= acc + h) { S.bin = t * per + k; S.want = want - acc; S.count = h; break; }
-                    acc += h;
-                }
-            }
-            __syncthreads();
-        }
-        const int bin = S.bin, cnt = S.count;
-        want = S.want;
-        if (cnt <= kSmallSel) {
-            if (t == 0) S.n_small = 0;
-            __syncthreads();
-            src.for_each([&](int, float v) {
-                if (v >= lo && v <= hi && min(kSelBins - 1, int((v - lo) * scale)) == bin) S.small[atomicAdd(&S.n_small, 1)] = v;
-            });
-            __syncthreads();
-            for (int i = t; i < cnt; i += nthreads) {
-                const float v = S.small[i];
-                int gt = 0, eq = 0;
-                for (int o = 0; o < cnt; ++o) { gt += S.small[o] > v; eq += S.small[o] == v; }
-                if (gt < want && want <= gt + eq) S.theta = v;     // all writers hold the same value
-            }
-            __syncthreads();
-            return S.theta;
-        }
-        // recurse into the bin: narrow [lo, hi] to the bin's value interval (the next round finds its exact range)
-        {
-            float nlo = INFINITY, nhi = -INFINITY;
-            src.for_each([&](int, float v) {
-                if (v >= lo && v <= hi && min(kSelBins - 1, int((v - lo) * scale)) == bin) { nlo = fminf(nlo, v); nhi = fmaxf(nhi, v); }
-            });
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) {
-                nlo = fminf(nlo, __shfl_xor_sync(0xffffffffu, nlo, off));
-                nhi = fmaxf(nhi, __shfl_xor_sync(0xffffffffu, nhi, off));
-            }
-            __syncthreads();
-            if (lane == 0) { S.red[warp] = nlo; S.red[32 + warp] = nhi; }
-            __syncthreads();
-            nlo = INFINITY; nhi = -INFINITY;
-            for (int w = 0; w < nw; ++w) { nlo = fminf(nlo, S.red[w]); nhi = fmaxf(nhi, S.red[32 + w]); }
-            lo = nlo; hi = nhi;
-            __syncthreads();
-        }
-    }
-    return lo;
-}
-
 // ---- 3. thresholds from the sample scores -----------------------------------------------------------------------
-constexpr int kSelCThreads = 256;           // smallest CTA of the selection kernels (they take any multiple of 32 up to 1024)
-
 // Values held in shared memory.
 struct SmemValues {
     const float *v;
@@ -249,98 +105,595 @@ struct SmemValues {
     }
 };
 
-// One row of the blocked dense scores, read from global memory.
-struct SampleRow {
-    const float *blk;          // block row base + this row's offset inside a block
-    int n;
-    template <class F> __device__ __forceinline__ void for_each(F f) const
+// ---- block-wide helpers of the selection kernels -------------------------------------------------------------------
+// Exclusive prefix sum of one int per thread over the CTA (any multiple of 32 threads up to 1024); `total` receives the sum.
+// `ws` holds 33 ints.  Three barriers.
+__device__ __forceinline__ int block_exclusive_scan(int v, int *ws, int &total)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += o;
+    }
+    __syncthreads();                                         // ws may still be read by an earlier call
+    if (lane == 31) ws[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int w = lane < nw ? ws[lane] : 0;
+        int winc = w;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, winc, off);
+            if (lane >= off) winc += o;
+        }
+        ws[lane] = winc - w;
+        if (lane == 31) ws[32] = winc;
+    }
+    __syncthreads();
+    total = ws[32];
+    return ws[warp] + incl - v;
+}
+
+// The r-th largest of the n floats in shared memory `vals` (n >= r >= 1, all inside [lo, hi]) by ONE warp, without a
+// CTA-wide barrier: a 256-bin histogram finds the bin, its members (few when n is a few hundred) are ranked directly.
+// `hist` holds 256 ints, `small` kWarpSmall floats, `ctl` 2 ints.  When more than kWarpSmall values crowd the bin
+// the smallest of them is returned (at most the r-th largest) and `exact` is cleared.  Every lane returns the result.
+constexpr int kWarpSmall = 128;
+
+__device__ __forceinline__ float warp_select_small(const float *vals, int n, int r, float lo, float hi, int *hist, float *small,
+                                                   int *ctl, bool &exact)
+{
+    const int lane = threadIdx.x & 31;
+    exact = true;
+    if (!(hi > lo)) return lo;
+    for (int i = lane; i < 256; i += 32) hist[i] = 0;
+    if (lane == 0) { ctl[0] = 0; ctl[1] = 0; }
+    __syncwarp();
+    const float scale = 256.f / (hi - lo);
+    for (int i = lane; i < n; i += 32) atomicAdd(&hist[min(255, int((vals[i] - lo) * scale))], 1);
+    __syncwarp();
+    int mine = 0;                                            // lane 0 owns the 8 highest bins
+#pragma unroll
+    for (int k = 0; k < 8; ++k) mine += hist[255 - (lane * 8 + k)];
+    int incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += o;
+    }
+    int bin = -1, want = 0;
     {
-        const int n4 = (n + 3) >> 2;
-        for (int g = threadIdx.x; g < n4; g += blockDim.x) {
-            const float4 v = *reinterpret_cast<const float4 *>(blk + size_t(g >> 3) * 1024 + size_t(g & 7) * 128);
-            const int i = g * 4;
-            f(i, v.x);
-            if (i + 1 < n) f(i + 1, v.y);
-            if (i + 2 < n) f(i + 2, v.z);
-            if (i + 3 < n) f(i + 3, v.w);
+        int acc = incl - mine;
+        if (acc < r && r <= incl) {
+            for (int k = 0; k < 8; ++k) {
+                const int b = 255 - (lane * 8 + k);
+                if (r <= acc + hist[b]) { bin = b; want = r - acc; break; }
+                acc += hist[b];
+            }
         }
     }
-};
-
-// One small CTA per bucket: tau = the r-th largest score of the bucket's row of the blocked sample scores (four
-// consecutive columns are 16 contiguous bytes).  r is small against the row, so most of the row is discarded cheaply:
-// every thread keeps four maxima over disjoint parts of what it loads; the r-th largest of all these maxima is a
-// lower bound of tau (r different scores reach it), and only the scores at or above the bound - a few hundred, found
-// in a second sweep over the row, which by then sits in L2 - enter the selection.  The CTAs are small and hold a
-// few KB each so that an SM keeps dozens of rows in flight: the work per row is a chain of short dependent steps.
-// (Measured on the 32-head benchmark build: 64 threads 2.79 ms, 128 threads 2.72 ms, 256 threads 2.77 ms.)
-constexpr int kTauThreads = 128;
-constexpr int kTopCap = 1024;               // sample scores that may lie at or above the lower bound
-
-__device__ __forceinline__ void load_sample_groups(const float *blk, int g0, int stride, int n4, int n, float4 (&v)[4])
-{
+    const unsigned owner = __ballot_sync(0xffffffffu, bin >= 0);
+    const int src_lane = __ffs(owner) - 1;
+    bin = __shfl_sync(0xffffffffu, bin, src_lane);
+    want = __shfl_sync(0xffffffffu, want, src_lane);
+    float mmin = INFINITY;
+    for (int i = lane; i < n; i += 32) {
+        const float v = vals[i];
+        if (min(255, int((v - lo) * scale)) == bin) {
+            const int slot = atomicAdd(&ctl[0], 1);
+            if (slot < kWarpSmall) small[slot] = v;
+            mmin = fminf(mmin, v);
+        }
+    }
+    __syncwarp();
+    const int cnt = ctl[0];
+    if (cnt > kWarpSmall) {
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        const int g = min(g0 + u * stride, n4 - 1);                                // group of 4 columns
-        v[u] = *reinterpret_cast<const float4 *>(blk + size_t(g >> 3) * 1024 + size_t(g & 7) * 128);
+        for (int off = 16; off >= 1; off >>= 1) mmin = fminf(mmin, __shfl_xor_sync(0xffffffffu, mmin, off));
+        exact = false;
+        return mmin;
+    }
+    float theta = -INFINITY;
+    for (int i = lane; i < cnt; i += 32) {
+        const float v = small[i];
+        int gt = 0, eq = 0;
+        for (int o = 0; o < cnt; ++o) { gt += small[o] > v; eq += small[o] == v; }
+        if (gt < want && want <= gt + eq) theta = v;
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-        const int g = g0 + u * stride;
-        if (g >= n4) v[u].x = -INFINITY;                                           // groups and columns past the row's end
-        if (4 * g + 1 >= n) v[u].y = -INFINITY;
-        if (4 * g + 2 >= n) v[u].z = -INFINITY;
-        if (4 * g + 3 >= n) v[u].w = -INFINITY;
+    for (int off = 16; off >= 1; off >>= 1) theta = fmaxf(theta, __shfl_xor_sync(0xffffffffu, theta, off));
+    return theta;
+}
+
+// The r-th largest of the floats a value source yields (at least r of them), all of them inside [lo, hi]; a source exposes
+//  template <class F> void for_each(F f)  which calls f(ordinal, value) for the values this thread owns.  One histogram of
+// kFineBins linear bins finds the bin that holds it; the members of that bin are ranked directly when they are few, else
+// the bin is cut into kFineBins finer ones (a few rounds at most: scores near a threshold crowd a narrow interval).
+// If the crowd does not thin out the lower edge of the bin is returned, which is at most the r-th largest - callers
+// that need the exact order statistic pass exact = true and get `ok = false` then.  Every thread returns the same value.
+constexpr int kFineBins = 2048;
+constexpr int kFineSmall = 512;
+
+struct FineScratch {
+    int hist[kFineBins];
+    float small[kFineSmall];
+    float wsmall[kWarpSmall];
+    int scan[33];
+    int bin, want, count, n_small, exact;
+    int ctl[2];
+    float theta, mlo, mhi;
+};
+
+template <class Source>
+__device__ __forceinline__ float select_rth_fine(const Source &src, int r, float lo, float hi, FineScratch &S, bool &ok)
+{
+    const int t = threadIdx.x, nthreads = blockDim.x;
+    int want = r;
+    ok = true;
+    for (int round = 0; round < 6; ++round) {
+        if (!(hi > lo)) return lo;                           // everything left is one value
+        __syncthreads();
+        for (int i = t; i < kFineBins; i += nthreads) S.hist[i] = 0;
+        __syncthreads();
+        const float scale = float(kFineBins) / (hi - lo);
+        src.for_each([&](int, float v) {
+            if (v >= lo && v <= hi) atomicAdd(&S.hist[min(kFineBins - 1, int((v - lo) * scale))], 1);
+        });
+        __syncthreads();
+        // suffix sums from the top: thread t owns `per` consecutive bins, highest bins in thread 0
+        const int per = (kFineBins + nthreads - 1) / nthreads;
+        int mine = 0;
+        for (int k = 0; k < per; ++k) {
+            const int b = kFineBins - 1 - (t * per + k);
+            mine += b >= 0 ? S.hist[b] : 0;
+        }
+        int total;
+        const int above = block_exclusive_scan(mine, S.scan, total);
+        if (mine > 0 && above < want && want <= above + mine) {
+            int acc = above;
+            for (int k = 0; k < per; ++k) {
+                const int b = kFineBins - 1 - (t * per + k);
+                const int h = b >= 0 ? S.hist[b] : 0;
+                if (want <= acc + h) { S.bin = b; S.want = want - acc; S.count = h; break; }
+                acc += h;
+            }
+        }
+        if (t == 0) S.n_small = 0;
+        __syncthreads();
+        const int bin = S.bin, cnt = S.count;
+        want = S.want;
+        if (cnt <= kFineSmall) {
+            // the bin's members go to a list that warp 0 ranks by itself
+            float mlo = INFINITY, mhi = -INFINITY;
+            src.for_each([&](int, float v) {
+                if (v >= lo && v <= hi && min(kFineBins - 1, int((v - lo) * scale)) == bin) {
+                    S.small[atomicAdd(&S.n_small, 1)] = v;
+                    mlo = fminf(mlo, v);
+                    mhi = fmaxf(mhi, v);
+                }
+            });
+            if (cnt > 32) {                                  // (a handful is ranked without knowing its range)
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) {
+                    mlo = fminf(mlo, __shfl_xor_sync(0xffffffffu, mlo, off));
+                    mhi = fmaxf(mhi, __shfl_xor_sync(0xffffffffu, mhi, off));
+                }
+                float *red = reinterpret_cast<float *>(S.hist);   // the histogram has been consumed
+                __syncthreads();
+                if ((t & 31) == 0) { red[t >> 5] = mlo; red[32 + (t >> 5)] = mhi; }
+            }
+            __syncthreads();
+            if (t < 32) {
+                float th;
+                bool ex = true;
+                if (cnt > 32) {
+                    const float *red = reinterpret_cast<const float *>(S.hist);
+                    mlo = INFINITY; mhi = -INFINITY;
+                    for (int w = 0; w < (nthreads >> 5); ++w) { mlo = fminf(mlo, red[w]); mhi = fmaxf(mhi, red[32 + w]); }
+                    __syncwarp();
+                    th = warp_select_small(S.small, cnt, want, mlo, mhi, S.hist + 128, S.wsmall, S.ctl, ex);
+                } else {
+                    th = -INFINITY;
+                    for (int i = t; i < cnt; i += 32) {
+                        const float v = S.small[i];
+                        int gt = 0, eq = 0;
+                        for (int o = 0; o < cnt; ++o) { gt += S.small[o] > v; eq += S.small[o] == v; }
+                        if (gt < want && want <= gt + eq) th = v;
+                    }
+#pragma unroll
+                    for (int off = 16; off >= 1; off >>= 1) th = fmaxf(th, __shfl_xor_sync(0xffffffffu, th, off));
+                }
+                if (t == 0) { S.theta = th; S.exact = ex ? 1 : 0; }
+            }
+            __syncthreads();
+            ok = S.exact != 0;
+            return S.theta;
+        }
+        // narrow to the exact value range of the bin's members
+        float nlo = INFINITY, nhi = -INFINITY;
+        src.for_each([&](int, float v) {
+            if (v >= lo && v <= hi && min(kFineBins - 1, int((v - lo) * scale)) == bin) { nlo = fminf(nlo, v); nhi = fmaxf(nhi, v); }
+        });
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            nlo = fminf(nlo, __shfl_xor_sync(0xffffffffu, nlo, off));
+            nhi = fmaxf(nhi, __shfl_xor_sync(0xffffffffu, nhi, off));
+        }
+        float *red = reinterpret_cast<float *>(S.hist);       // the histogram has been consumed
+        __syncthreads();
+        if ((t & 31) == 0) { red[t >> 5] = nlo; red[32 + (t >> 5)] = nhi; }
+        __syncthreads();
+        nlo = INFINITY; nhi = -INFINITY;
+        for (int w = 0; w < (nthreads >> 5); ++w) { nlo = fminf(nlo, red[w]); nhi = fmaxf(nhi, red[32 + w]); }
+        lo = nlo; hi = nhi;
+    }
+    ok = false;                                              // masses of nearly equal values
+    return lo;
+}
+
+// ---- 3a. thresholds, eight rows per CTA ----------------------------------------------------------------------------
+// The blocked layout of the sample scores puts the same four columns of eight consecutive rows into one 128-byte line,
+// so a CTA takes eight rows and reads whole lines: lane = (row, one of four column pieces), 8 warps side by side.
+//   pass 1: every lane keeps eight maxima over interleaved classes of its pieces - 256 maxima per row; the r-th
+//           largest of a row's maxima is a lower bound of its tau (r different scores reach it), found as the lower
+//           edge of a bin of a 256-bin histogram of the maxima (warp w serves row w);
+//   pass 2: the lines are read again (from L2) and the scores at or above the bound - a few hundred per row - go to
+//           the row's list in shared memory;
+//   rank:   warp w ranks the list of row w (warp_select_small) and writes tau.
+// Rows for which this does not work out (rank beyond the maxima, a list that overflows: masses of equal scores) get
+// tau = NaN and are served by the one-row-per-CTA kernel below, which exits at once for every other row.
+constexpr int kTau8Rows = 8;
+constexpr int kTau8Threads = 256;
+constexpr int kTau8List = 1024;             // scores at or above the bound a row's list holds
+
+struct Tau8Warp {
+    int hist[256];
+    float small[kWarpSmall];
+    int ctl[2];
+};
+
+__global__ void __launch_bounds__(kTau8Threads)
+sample_tau8_kernel(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg, float *__restrict__ tau)
+{
+    extern __shared__ __align__(16) unsigned char tau8_dyn[];
+    float *top = reinterpret_cast<float *>(tau8_dyn);                      // [8 rows][kTau8List]
+    Tau8Warp *ws = reinterpret_cast<Tau8Warp *>(top + kTau8Rows * kTau8List);   // one per warp
+    __shared__ float red_hi[kTau8Rows][8], red_lo[kTau8Rows][8];
+    __shared__ float s_hi[kTau8Rows], s_lo[kTau8Rows], s_bound[kTau8Rows];
+    __shared__ int s_cnt[kTau8Rows];
+
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int rr = lane & 7, cc = lane >> 3;                 // row of the eight, column piece of the four
+    const int row0 = blockIdx.x * kTau8Rows;
+    const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row0)];
+    const bool row_ok = row0 + rr - sg.out_row0 < sg.n_buckets;           // rows past the segment's buckets are padding
+    if (row0 - sg.out_row0 >= sg.n_buckets) return;
+    const int n = sg.ns, n4 = (n + 3) >> 2, r = min(sg.rank, n);
+    // piece g of row R sits at block base + (g >> 3) * 1024 + (g & 7) * 128 + (R & 31) * 4 floats
+    const float *base = Ys + dense_block_offset(row0, 0, ldy) + size_t((row0 + rr) & 31) * 4;
+    auto piece = [&](int g) { return *reinterpret_cast<const float4 *>(base + size_t(g >> 3) * 1024 + size_t(g & 7) * 128); };
+    const int n_steps = (n4 + 31) >> 5;                      // 32 pieces of a row per step of the CTA: piece g = step * 32 + warp * 4 + cc
+    float mx[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) mx[k] = -INFINITY;
+    for (int s0 = 0; s0 < n_steps; s0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int g = (s0 + k) * 32 + warp * 4 + cc;
+            v[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            if (g < n4) v[k] = piece(g);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int g = (s0 + k) * 32 + warp * 4 + cc;
+            if (g < n4) {
+                if (4 * g + 1 >= n) v[k].y = -INFINITY;      // columns past the row's end
+                if (4 * g + 2 >= n) v[k].z = -INFINITY;
+                if (4 * g + 3 >= n) v[k].w = -INFINITY;
+                mx[k] = fmaxf(mx[k], fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+            }
+        }
+    }
+    // range of the row's maxima: over the lane's eight, the four lanes of the row in this warp, then the warps
+    float hi = -INFINITY, lo = INFINITY;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        hi = fmaxf(hi, mx[k]);
+        if (mx[k] > -INFINITY) lo = fminf(lo, mx[k]);
+    }
+#pragma unroll
+    for (int off = 8; off <= 16; off <<= 1) {
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+    }
+    if (cc == 0) { red_hi[rr][warp] = hi; red_lo[rr][warp] = lo; }
+    for (int i = lane; i < 256; i += 32) ws[warp].hist[i] = 0;            // warp w's histogram serves row w
+    if (t < kTau8Rows) s_cnt[t] = 0;
+    __syncthreads();
+    if (t < kTau8Rows) {
+        float h = -INFINITY, l = INFINITY;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { h = fmaxf(h, red_hi[t][w]); l = fminf(l, red_lo[t][w]); }
+        s_hi[t] = h;
+        s_lo[t] = l;
+    }
+    __syncthreads();
+    hi = s_hi[rr];
+    lo = s_lo[rr];
+    const float bscale = hi > lo ? 256.f / (hi - lo) : 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        if (mx[k] > -INFINITY && row_ok) atomicAdd(&ws[rr].hist[min(255, int((mx[k] - lo) * bscale))], 1);
+    __syncthreads();
+    {
+        // warp w: the bin of the r-th largest maximum of row w; the bound is a little below the bin's lower edge, so that
+        // every score of that bin and the bins above passes a plain comparison
+        const float h = s_hi[warp], l = s_lo[warp];
+        int mine = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mine += ws[warp].hist[255 - (lane * 8 + k)];
+        int incl = mine;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += o;
+        }
+        const int total = __shfl_sync(0xffffffffu, incl, 31);
+        int acc = incl - mine;
+        float bnd = NAN;
+        if (acc < r && r <= incl) {
+            for (int k = 0; k < 8; ++k) {
+                const int b = 255 - (lane * 8 + k);
+                acc += ws[warp].hist[b];
+                if (r <= acc) { bnd = l + (float(b) - 0.25f) * ((h - l) * (1.f / 256.f)); break; }
+            }
+        }
+        const unsigned owner = __ballot_sync(0xffffffffu, bnd == bnd);
+        if (owner) bnd = __shfl_sync(0xffffffffu, bnd, __ffs(owner) - 1);
+        if (total < r || !(h > l)) bnd = NAN;                // no bound: the row goes to the other kernel
+        if (lane == 0) s_bound[warp] = bnd;
+    }
+    __syncthreads();
+    const float bound = s_bound[rr];
+    if (bound == bound && row_ok) {                          // pass 2 (rows without a bound take no part)
+        float *list = top + rr * kTau8List;
+        for (int s0 = 0; s0 < n_steps; s0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int g = (s0 + k) * 32 + warp * 4 + cc;
+                v[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                if (g < n4) v[k] = piece(g);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int g = (s0 + k) * 32 + warp * 4 + cc;
+                const float f[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (f[e] >= bound && 4 * g + e < n) {
+                        const int pos = atomicAdd(&s_cnt[rr], 1);
+                        if (pos < kTau8List) list[pos] = f[e];
+                    }
+            }
+        }
+    }
+    __syncthreads();
+    {
+        // warp w ranks row w
+        const int row = row0 + warp;
+        if (row - sg.out_row0 < sg.n_buckets) {
+            const float b = s_bound[warp];
+            const int cnt = s_cnt[warp];
+            float th = NAN;
+            if (b == b && cnt >= r && cnt <= kTau8List) {
+                bool exact;
+                th = warp_select_small(top + warp * kTau8List, cnt, r, b, s_hi[warp], ws[warp].hist, ws[warp].small, ws[warp].ctl, exact);
+                // (not exact: the smallest member of a crowded bin, at most the order statistic - a few more candidates pass)
+            }
+            if (lane == 0) tau[row] = th;
+        }
     }
 }
 
-__global__ void __launch_bounds__(kTauThreads)
-sample_tau_kernel(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg, float *__restrict__ tau)
+// One CTA per bucket: tau = the r-th largest score of the bucket's row of the blocked sample scores (four consecutive
+// columns are 16 contiguous bytes).  The whole row is loaded into registers at once (kTauGroups 16-byte pieces per
+// thread, all in flight together), so the row is read exactly once and nothing below waits on memory again.  r is small
+// against the row, so most of it is discarded cheaply: every thread keeps the maxima of two halves of what it holds; the
+// r-th largest of these maxima is a lower bound of tau (r different scores reach it), found with one small histogram
+// (its bin's lower edge: still a lower bound).  Only the scores at or above the bound - a few hundred - are put into
+// shared memory and ranked.
+// The scores a thread holds in registers (-inf marks "no score").
+template <int G> struct RowRegs {
+    const float4 (&v)[G];
+    template <class F> __device__ __forceinline__ void for_each(F f) const
+    {
+#pragma unroll
+        for (int u = 0; u < G; ++u) {
+            if (v[u].x > -INFINITY) f(0, v[u].x);
+            if (v[u].y > -INFINITY) f(0, v[u].y);
+            if (v[u].z > -INFINITY) f(0, v[u].z);
+            if (v[u].w > -INFINITY) f(0, v[u].w);
+        }
+    }
+};
+constexpr int kTopCap = 2048;               // sample scores that may lie at or above the lower bound
+constexpr int kBoundBins = 256;
+
+// THREADS x G 16-byte pieces cover the row: 256 x 8 (rows of up to 8192 scores), 256 x 16, 512 x 16, 1024 x 12 (49152).
+struct TauRowScratch {
+    FineScratch S;
+    float top_s[kTopCap];
+    float red_s[64];
+    int bound_hist[kBoundBins];
+    int s_top, s_bbin;
+};
+
+template <int THREADS, int G>
+__device__ __forceinline__ void tau_of_row(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg,
+                                           float *__restrict__ tau, int row, TauRowScratch &W)
 {
-    __shared__ SelScratch<1> S;
-    __shared__ float tmax_s[4 * kTauThreads];
-    __shared__ float top_s[kTopCap];
-    __shared__ int s_top;
-    const int row = blockIdx.x, t = threadIdx.x;
+    constexpr int kTauGroups = G;
+    FineScratch &S = W.S;
+    float *top_s = W.top_s, *red_s = W.red_s;
+    int *bound_hist = W.bound_hist;
+    int &s_top = W.s_top, &s_bbin = W.s_bbin;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nthreads = blockDim.x, nw = nthreads >> 5;
     const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
     if (row - sg.out_row0 >= sg.n_buckets) return;           // padding between segments
     const float *blk = Ys + dense_block_offset(row, 0, ldy) + size_t(row & 31) * 4;
     const int n = sg.ns, n4 = (n + 3) >> 2, r = min(sg.rank, n);
-    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    for (int g0 = t; g0 < n4; g0 += 4 * kTauThreads) {
-        float4 v[4];
-        load_sample_groups(blk, g0, kTauThreads, n4, n, v);
+
+    float4 v[kTauGroups];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) mx[u] = fmaxf(fmaxf(mx[u], v[u].x), fmaxf(fmaxf(v[u].y, v[u].z), v[u].w));
+    for (int u = 0; u < kTauGroups; ++u) {
+        const int g = t + u * nthreads;
+        v[u] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        if (g < n4) v[u] = *reinterpret_cast<const float4 *>(blk + size_t(g >> 3) * 1024 + size_t(g & 7) * 128);
     }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) tmax_s[u * kTauThreads + t] = mx[u];
-    if (t == 0) s_top = 0;
+    for (int u = 0; u < kTauGroups; ++u) {
+        const int g = t + u * nthreads;
+        if (g < n4) {
+            if (4 * g + 1 >= n) v[u].y = -INFINITY;          // columns past the row's end
+            if (4 * g + 2 >= n) v[u].z = -INFINITY;
+            if (4 * g + 3 >= n) v[u].w = -INFINITY;
+            const float m4 = fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w));
+            if (u & 1) mx1 = fmaxf(mx1, m4); else mx0 = fmaxf(mx0, m4);
+        }
+    }
+    // range of the thread maxima
+    float hi = fmaxf(mx0, mx1), lo = fminf(mx0 > -INFINITY ? mx0 : INFINITY, mx1 > -INFINITY ? mx1 : INFINITY);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+    }
+    if (lane == 0) { red_s[warp] = hi; red_s[32 + warp] = lo; }
+    for (int i = t; i < kBoundBins; i += nthreads) bound_hist[i] = 0;
+    if (t == 0) { s_top = 0; s_bbin = -1; }
     __syncthreads();
-    bool pruned = false;
-    if (r <= 4 * kTauThreads) {
-        const float bound = select_rth(SmemValues{tmax_s, 4 * kTauThreads}, 4 * kTauThreads, r, S);
-        for (int g0 = t; g0 < n4; g0 += 4 * kTauThreads) {
-            float4 v[4];
-            load_sample_groups(blk, g0, kTauThreads, n4, n, v);
+    hi = -INFINITY; lo = INFINITY;
+    for (int w = 0; w < nw; ++w) { hi = fmaxf(hi, red_s[w]); lo = fminf(lo, red_s[32 + w]); }
+    // a score passes the pre-filter when it falls into the bin of the r-th largest thread maximum or above: at least r
+    // scores do (the maxima themselves), and passing is monotone in the score, so the r-th largest of the row is among them
+    const float bscale = hi > lo ? float(kBoundBins) / (hi - lo) : 0.f;
+    auto bound_bin = [&](float f) { return min(kBoundBins - 1, int((f - lo) * bscale)); };
+    const int n_max = min(nthreads, n4) + max(0, min(nthreads, n4 - nthreads));      // thread maxima that exist
+    if (r <= n_max && hi > lo) {
+        if (mx0 > -INFINITY) atomicAdd(&bound_hist[bound_bin(mx0)], 1);
+        if (mx1 > -INFINITY) atomicAdd(&bound_hist[bound_bin(mx1)], 1);
+        __syncthreads();
+        if (warp == 0) {                                     // suffix sums over the 256 bins, 8 per lane, top bins in lane 0
+            int mine = 0;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+            for (int k = 0; k < kBoundBins / 32; ++k) mine += bound_hist[kBoundBins - 1 - (lane * (kBoundBins / 32) + k)];
+            int incl = mine;
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (f[k] >= bound) {
-                        const int pos = atomicAdd(&s_top, 1);
-                        if (pos < kTopCap) top_s[pos] = f[k];
-                    }
+            for (int off = 1; off < 32; off <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += o;
+            }
+            int acc = incl - mine;
+            if (acc < r && r <= incl) {
+                for (int k = 0; k < kBoundBins / 32; ++k) {
+                    const int b = kBoundBins - 1 - (lane * (kBoundBins / 32) + k);
+                    acc += bound_hist[b];
+                    if (r <= acc) { s_bbin = b; break; }
+                }
             }
         }
         __syncthreads();
-        pruned = s_top >= r && s_top <= kTopCap;             // uniform; more than that (masses of equal scores): the plain way
     }
-    float th;
-    if (pruned) th = select_rth(SmemValues{top_s, s_top}, s_top, r, S);
-    else th = select_rth(SampleRow{blk, n}, n, r, S);
+    const int bbin = s_bbin;                                 // -1: no pre-filter
+    float th = 0.f;
+    bool ok = true, listed = false;
+    if (bbin > 0) {
+        float top_min = INFINITY;
+#pragma unroll
+        for (int u = 0; u < kTauGroups; ++u) {
+            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (f[k] > -INFINITY && bound_bin(f[k]) >= bbin) {
+                    const int pos = atomicAdd(&s_top, 1);
+                    if (pos < kTopCap) top_s[pos] = f[k];
+                    top_min = fminf(top_min, f[k]);
+                }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) top_min = fminf(top_min, __shfl_xor_sync(0xffffffffu, top_min, off));
+        if (lane == 0) red_s[warp] = top_min;
+        __syncthreads();
+        listed = s_top >= r && s_top <= kTopCap;             // uniform; more than the list holds: the plain way
+        if (listed) {
+            top_min = INFINITY;
+            for (int w = 0; w < nw; ++w) top_min = fminf(top_min, red_s[w]);
+            if (s_top <= 1024) {
+                // a few hundred scores: one warp ranks them while the others are done (no barrier follows)
+                if (warp == 0) {
+                    th = warp_select_small(top_s, s_top, r, top_min, hi, S.hist, S.wsmall, S.ctl, ok);
+                    if (lane == 0) tau[row] = th;
+                }
+                return;
+            }
+            th = select_rth_fine(SmemValues{top_s, s_top}, r, top_min, hi, S, ok);
+        }
+    }
+    if (!listed) {
+        // no pre-filter (r beyond the number of thread maxima, equal scores in masses): rank the row from the registers
+        float mn = INFINITY;
+#pragma unroll
+        for (int u = 0; u < kTauGroups; ++u) {
+            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (f[k] > -INFINITY) mn = fminf(mn, f[k]);
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+        __syncthreads();
+        if (lane == 0) red_s[warp] = mn;
+        __syncthreads();
+        mn = INFINITY;
+        for (int w = 0; w < nw; ++w) mn = fminf(mn, red_s[w]);
+        th = select_rth_fine(RowRegs<G>{v}, r, mn, hi, S, ok);
+    }
+    // (when the crowd around the order statistic never thins out `th` is a lower edge below it: a few more candidates pass)
     if (t == 0) tau[row] = th;
+}
+
+// only_unset = false: one row per CTA (grid = rows).  only_unset = true: a CTA looks through a stretch of kTauStretch rows
+// and serves just the ones whose tau is still NaN (the eight-row kernel leaves those): grid = rows / kTauStretch.
+constexpr int kTauStretch = 128;
+
+template <int THREADS, int G>
+__global__ void __launch_bounds__(THREADS)
+sample_tau_kernel(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg, float *__restrict__ tau,
+                  int n_rows, bool only_unset)
+{
+    __shared__ TauRowScratch W;
+    __shared__ int todo[kTauStretch];
+    __shared__ int n_todo;
+    if (!only_unset) {
+        tau_of_row<THREADS, G>(Ys, ldy, segs, n_seg, tau, blockIdx.x, W);
+        return;
+    }
+    if (threadIdx.x == 0) n_todo = 0;
+    __syncthreads();
+    const int r0 = blockIdx.x * kTauStretch, r1 = min(n_rows, r0 + kTauStretch);
+    for (int row = r0 + threadIdx.x; row < r1; row += THREADS)
+        if (!(tau[row] == tau[row])) todo[atomicAdd(&n_todo, 1)] = row;
+    __syncthreads();
+    const int n = n_todo;
+    for (int i = 0; i < n; ++i) {
+        tau_of_row<THREADS, G>(Ys, ldy, segs, n_seg, tau, todo[i], W);
+        __syncthreads();
+    }
 }
 
 // ---- 5. exact selection among the candidates ---------------------------------------------------------------------
@@ -358,37 +711,44 @@ struct SelParams {
     int32_t *table;
     int *fail_count;           // buckets handed to the fallback
     int *fail_list;            // their rows inside the group
+    int max_tiles;             // key tiles of the longest segment (sizes the mask arrays in shared memory)
 };
-
-constexpr int kMaxItems = kFusedMaxCap / 32 + 2 * kMaxRanges + 1;   // 32-entry slabs of one bucket's sub-lists
 
 // One CTA per bucket.  The bucket's candidate groups - sub-lists (range 0, group 0), (range 0, group 1), (range 1,
 // group 0), ...; group 0 of a range was written upward from the start of the range's buffer, group 1 downward from
-// its end, so concatenated in this order they are in key order - are cut into slabs of 32 entries, one warp per slab.
-// The scores that reach tau are compacted, still in key order, into shared memory (count per slab, scan, write),
-// where every later step runs; no step inside a loop needs a CTA-wide barrier.
-template <typename T>
-__global__ void __launch_bounds__(1024)
+// its end, so concatenated in this order they are in key order - are dealt out in key order, E consecutive entries per
+// thread.  That makes every ordered step a matter of one count per thread and one prefix sum over the CTA:
+//   1. the tile masks go to shared memory with their prefix population counts (entry ordinal -> key tile and bit);
+//   2. every thread loads its entries (KEEP: they stay in registers; otherwise they are read a second time in step 3)
+//      and counts the scores that reach tau; a prefix sum gives each thread its place among the hits;
+//   3. the hits are written, in key order, to shared memory with their key indices (found by walking the masks from
+//      the thread's first entry);
+//   4. theta = the Z-th largest hit (histogram of 2048 bins over the hits' range, refined inside one bin);
+//   5. hits above theta + eps are in, the band around theta is re-scored with the canonical chain and ranked exactly;
+//   6. every thread counts the selected hits of its stretch of positions, a prefix sum places them, and the table row
+//      comes out in ascending key order.
+template <typename T, int THREADS, int EMAX, bool KEEP>
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS)
 candidate_select_kernel(SelParams p)
 {
     extern __shared__ __align__(16) unsigned char sel_dyn[];
     float *cy = reinterpret_cast<float *>(sel_dyn);                     // [cap] candidate scores, in key order
     int *cid = reinterpret_cast<int *>(cy + p.cap);                     // [cap] their key indices; bit 31 = band entry that made it
-    __shared__ SelScratch<2> S;
+    unsigned long long *m64 = reinterpret_cast<unsigned long long *>(cid + p.cap + (p.cap & 1));   // [n_tiles] tile masks
+    int *tile_pre = reinterpret_cast<int *>(m64 + p.max_tiles);         // [n_tiles + 1] entries before each tile
+    __shared__ FineScratch S;
     __shared__ int band[kMaxBand];                                      // positions of the band entries in cy / cid
     __shared__ float band_y[kMaxBand];                                  // their canonical scores
     __shared__ int band_rank[kMaxBand];
     __shared__ float a_f32[256];
-    __shared__ int item_off[kMaxItems + 1];                             // hits before each slab
-    __shared__ int s_n, s_items, s_fail, s_nband;
+    __shared__ float red_s[64];
+    __shared__ int scan_ws[33];
+    __shared__ int s_fail, s_nband, s_nent;
     __shared__ int s_start[2 * kMaxRanges + 1];                         // entries before each sub-list
-    __shared__ int s_istart[2 * kMaxRanges + 1];                        // slabs before each sub-list
-    __shared__ int warp_in[33];                                         // selected entries per warp range
-    __shared__ int scan_tot[32];
     __shared__ float s_anorm;
 
     const int row = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int nthreads = blockDim.x, nwarps = blockDim.x >> 5;
+    constexpr int nthreads = THREADS, nwarps = THREADS / 32;
     const FusedSeg sg = p.segs[seg_of_out_row(p.segs, p.n_seg, row)];
     if (row - sg.out_row0 >= sg.n_buckets) return;           // padding between segments
     const int bucket = sg.cb + (row - sg.out_row0);
@@ -398,31 +758,32 @@ candidate_select_kernel(SelParams p)
     const int n_sl = 2 * p.n_ranges;
     const uint4 *lists = p.cand + size_t(row) * p.cap;
     const float tau = p.tau[row];
+    const int n_tiles = (sg.n_keys + kTcBN - 1) / kTcBN;
 
-    // sub-list sizes; the two groups of a range share a buffer and must not have met in the middle
+    // ---- 1. sub-list sizes (the two groups of a range share a buffer and must not have met in the middle); masks ----
     if (t == 0) {
-        int n = 0, items = 0, fail = 0;
+        int n = 0, fail = 0;
         for (int r = 0; r < p.n_ranges; ++r) {
             const int c0 = p.cand_count[(size_t(row) * p.n_ranges + r) * 2], c1 = p.cand_count[(size_t(row) * p.n_ranges + r) * 2 + 1];
             if (c0 > sub_cap || c1 > sub_cap || c0 + c1 > sub_cap) fail = 1;
-            s_start[2 * r] = n;      s_istart[2 * r] = items;      n += c0; items += (c0 + 31) >> 5;
-            s_start[2 * r + 1] = n;  s_istart[2 * r + 1] = items;  n += c1; items += (c1 + 31) >> 5;
+            s_start[2 * r] = n;      n += c0;
+            s_start[2 * r + 1] = n;  n += c1;
         }
         s_start[n_sl] = n;
-        s_istart[n_sl] = items;
-        s_items = fail ? 0 : items;
+        if (n > EMAX * THREADS) fail = 1;
+        s_nent = fail ? 0 : n;
         s_fail = fail;
         s_nband = 0;
     }
     for (int i = t; i < p.d; i += nthreads) a_f32[i] = Elem<T>::to_f32(a_row[i]);
-    if (t < 33) warp_in[t] = 0;
-    __syncthreads();
-    // the lists are read twice below, a few entries per thread at a time: ask for them now (128-byte lines into L2)
-    for (int sl = 0; sl < n_sl; ++sl) {
-        const int cnt = s_start[sl + 1] - s_start[sl];
-        const uint4 *first = lists + size_t(sl >> 1) * sub_cap + ((sl & 1) ? sub_cap - cnt : 0);
-        for (int i = t * 8; i < cnt; i += nthreads * 8) asm volatile("prefetch.global.L2 [%0];" ::"l"(first + i));
+    {
+        const uint2 *mcol = p.cand_mask + row;
+        for (int tile = t; tile < n_tiles; tile += nthreads) {
+            const uint2 w = mcol[size_t(tile) * p.mask_ld];
+            m64[tile] = (unsigned long long)w.x | ((unsigned long long)w.y << 32);
+        }
     }
+    __syncthreads();
     if (warp == 0) {                                         // ||a_b||
         float n2 = 0.f;
         for (int i = lane; i < p.d; i += 32) n2 = fmaf(a_f32[i], a_f32[i], n2);
@@ -430,174 +791,117 @@ candidate_select_kernel(SelParams p)
         for (int off = 16; off >= 1; off >>= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, off);
         if (lane == 0) s_anorm = sqrtf(n2) * 1.0001f;
     }
-
-    // Which keys the entries hold: the tile masks, walked in key order, give the first key of the i-th entry (the
-    // sub-lists concatenate in tile order).  The key indices are parked at the END of cid, entry i at
-    // cid[cap - n_ent + i]: the hits are written from the front and hit position <= cap - n_ent + entry ordinal.
-    const int n_items = s_items;
-    const int n_ent = n_items ? s_start[n_sl] : 0;
-    int *ecol = cid + (p.cap - n_ent);
-    if (n_ent) {
-        const int n_tiles = (sg.n_keys + kTcBN - 1) / kTcBN;
-        const uint2 *mcol = p.cand_mask + row;
-        int run = 0;
-        const int tpt = min(4, max(1, (n_tiles + nthreads - 1) / nthreads));       // consecutive tiles per thread and step
-        for (int t0 = 0; t0 < n_tiles; t0 += tpt * nthreads) {
-            unsigned long long m[4];
-            int c = 0;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int tile = t0 + tpt * t + u;
-                uint2 w = make_uint2(0, 0);
-                if (u < tpt && tile < n_tiles) w = mcol[size_t(tile) * p.mask_ld];
-                m[u] = (unsigned long long)w.x | ((unsigned long long)w.y << 32);
-                c += __popcll(m[u]);
-            }
-            int incl = c;
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int o = __shfl_up_sync(0xffffffffu, incl, off);
-                if (lane >= off) incl += o;
-            }
-            if (lane == 31) scan_tot[warp] = incl;
-            __syncthreads();
-            int before = 0, total = 0;
-            for (int w = 0; w < nwarps; ++w) {
-                const int cw = scan_tot[w];
-                before += w < warp ? cw : 0;
-                total += cw;
-            }
-            int e = run + before + incl - c;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int key0 = (t0 + tpt * t + u) * kTcBN;
-                while (m[u]) {
-                    const int bit = __ffsll((long long)m[u]) - 1;
-                    m[u] &= m[u] - 1;
-                    if (e < n_ent) ecol[e] = key0 + 4 * bit;
-                    ++e;
-                }
-            }
-            run += total;
-            __syncthreads();
-        }
-        if (t == 0 && run != n_ent) s_fail = 1;              // masks and list lengths disagree (an overflowed list)
-    }
-    __syncthreads();
-
-    // entry `lane` of slab `it` (all -inf past the sub-list's end); `ord` = its ordinal among the bucket's entries
-    auto slab_entry = [&](int it, int &ord) {
-        const int sl = __popc(__ballot_sync(0xffffffffu, lane < n_sl && it >= s_istart[lane + 1]));
-        const int j = (it - s_istart[sl]) * 32 + lane, cnt = s_start[sl + 1] - s_start[sl];
-        uint4 e = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
-        ord = -1;
-        if (j < cnt) {
-            e = lists[size_t(sl >> 1) * sub_cap + ((sl & 1) ? sub_cap - 1 - j : j)];
-            ord = s_start[sl] + j;
-        }
-        return e;
+    const int n_ent = s_nent;
+    // ---- 2. this thread's entries [e0, e1), in key order; entries before each key tile --------------------------------
+    const int E = (n_ent + nthreads - 1) / nthreads;
+    const int e0 = min(n_ent, t * E), e1 = min(n_ent, e0 + E);
+    auto entry_ptr = [&](int e, int &sl) {                   // sl: sub-list of e, carried from the previous entry
+        while (e >= s_start[sl + 1]) ++sl;
+        const int j = e - s_start[sl], cnt = s_start[sl + 1] - s_start[sl];
+        (void)cnt;
+        return lists + size_t(sl >> 1) * sub_cap + ((sl & 1) ? sub_cap - 1 - j : j);
     };
-    // hits per slab (four slabs per step: the loads are issued together)
-    const unsigned lt_mask = (1u << lane) - 1u;
-    auto hit_ballots = [&](const uint4 &e, unsigned (&bal)[4]) {
-        bal[0] = __ballot_sync(0xffffffffu, __uint_as_float(e.x) >= tau);
-        bal[1] = __ballot_sync(0xffffffffu, __uint_as_float(e.y) >= tau);
-        bal[2] = __ballot_sync(0xffffffffu, __uint_as_float(e.z) >= tau);
-        bal[3] = __ballot_sync(0xffffffffu, __uint_as_float(e.w) >= tau);
-    };
-    for (int it0 = warp; it0 < n_items; it0 += 4 * nwarps) {
-        uint4 e[4];
-        int ord[4];
+    uint4 ent[KEEP ? EMAX : 1];
+    int my_hits = 0;
+    float hmin = INFINITY, hmax = -INFINITY;
+    if constexpr (KEEP) {                                    // ask for the entries now: they arrive while the masks are summed up
+        int sl = 0;
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (it0 + u * nwarps < n_items) e[u] = slab_entry(it0 + u * nwarps, ord[u]);
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (it0 + u * nwarps < n_items) {
-                unsigned bal[4];
-                hit_ballots(e[u], bal);
-                if (lane == 0) item_off[it0 + u * nwarps + 1] = __popc(bal[0]) + __popc(bal[1]) + __popc(bal[2]) + __popc(bal[3]);
-            }
-    }
-    __syncthreads();
-    if (warp == 0) {                                         // exclusive scan over the slabs
-        int run = 0;
-        for (int i0 = 0; i0 < n_items; i0 += 32) {
-            const int c = i0 + lane < n_items ? item_off[i0 + lane + 1] : 0;
-            int incl = c;
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int o = __shfl_up_sync(0xffffffffu, incl, off);
-                if (lane >= off) incl += o;
-            }
-            if (i0 + lane < n_items) item_off[i0 + lane + 1] = run + incl;
-            run += __shfl_sync(0xffffffffu, incl, 31);
-        }
-        if (lane == 0) {
-            item_off[0] = 0;
-            s_n = run;
-            if (run < Z || run > p.cap) s_fail = 1;
+        for (int u = 0; u < EMAX; ++u) {
+            ent[u] = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
+            if (e0 + u < e1) ent[u] = *entry_ptr(e0 + u, sl);
         }
     }
+    {
+        // entries before every tile: a stretch of consecutive tiles per thread, then a prefix sum over the threads
+        const int per_t = (n_tiles + nthreads - 1) / nthreads;
+        const int t0 = min(n_tiles, t * per_t), t1 = min(n_tiles, t0 + per_t);
+        int c = 0;
+        for (int tile = t0; tile < t1; ++tile) c += __popcll(m64[tile]);
+        int total;
+        int before = block_exclusive_scan(c, scan_ws, total);
+        for (int tile = t0; tile < t1; ++tile) { tile_pre[tile] = before; before += __popcll(m64[tile]); }
+        if (t == 0) {
+            tile_pre[n_tiles] = total;
+            if (total != n_ent) s_fail = 1;                  // masks and list lengths disagree (an overflowed list)
+        }
+    }
+    if constexpr (KEEP) {
+#pragma unroll
+        for (int u = 0; u < EMAX; ++u) {
+            const float f[4] = {__uint_as_float(ent[u].x), __uint_as_float(ent[u].y), __uint_as_float(ent[u].z), __uint_as_float(ent[u].w)};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (f[k] >= tau) { ++my_hits; hmin = fminf(hmin, f[k]); hmax = fmaxf(hmax, f[k]); }
+        }
+    } else {
+        int sl = 0;
+        for (int e = e0; e < e1; ++e) {
+            const uint4 x = *entry_ptr(e, sl);
+            const float f[4] = {__uint_as_float(x.x), __uint_as_float(x.y), __uint_as_float(x.z), __uint_as_float(x.w)};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (f[k] >= tau) { ++my_hits; hmin = fminf(hmin, f[k]); hmax = fmaxf(hmax, f[k]); }
+        }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        hmin = fminf(hmin, __shfl_xor_sync(0xffffffffu, hmin, off));
+        hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, off));
+    }
+    if (lane == 0) { red_s[warp] = hmin; red_s[32 + warp] = hmax; }
+    int n;
+    int pos = block_exclusive_scan(my_hits, scan_ws, n);     // (its barriers also publish red_s and s_fail)
+    for (int w = 0; w < nwarps; ++w) { hmin = fminf(hmin, red_s[w]); hmax = fmaxf(hmax, red_s[32 + w]); }
+    if (t == 0 && (n < Z || n > p.cap)) s_fail = 1;
     __syncthreads();
-    const int n = s_n;
+
     if (!s_fail) {
-        // ordered write of the hits; their value range for the selection on the way
-        float hmin = INFINITY, hmax = -INFINITY;
-        for (int ib = 0; ib < n_items; ib += 4 * nwarps) {   // the same trip count in every warp: a barrier inside
-            const int it0 = ib + warp;
-            uint4 e[4];
-            int col[4];
+        // ---- 3. the hits with their key indices, in key order --------------------------------------------------------
+        if (e0 < e1) {
+            int lo = 0, hi = n_tiles;                        // largest tile with tile_pre[tile] <= e0
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (tile_pre[mid] <= e0) lo = mid; else hi = mid;
+            }
+            int tile = lo;
+            unsigned long long m = m64[tile];
+            for (int skip = e0 - tile_pre[tile]; skip > 0; --skip) m &= m - 1;
+            int sl = 0;
+            auto emit = [&](const uint4 &x) {
+                while (m == 0) m = m64[++tile];              // ends inside the masks: their population is n_ent
+                const int key0 = tile * kTcBN + 4 * (__ffsll((long long)m) - 1);
+                m &= m - 1;
+                const uint32_t s4[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (it0 + u * nwarps < n_items) {
-                    int ord;
-                    e[u] = slab_entry(it0 + u * nwarps, ord);
-                    col[u] = ord >= 0 ? ecol[ord] : 0;
+                for (int k = 0; k < 4; ++k) {
+                    const float y = __uint_as_float(s4[k]);
+                    if (y >= tau) { cy[pos] = y; cid[pos] = key0 + k; ++pos; }
                 }
-            __syncthreads();                                 // every key index of this step is read before hits land in cid
+            };
+            if constexpr (KEEP) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (it0 + u * nwarps < n_items) {
-                    const uint32_t s4[4] = {e[u].x, e[u].y, e[u].z, e[u].w};
-                    unsigned bal[4];
-                    hit_ballots(e[u], bal);
-                    int pos = item_off[it0 + u * nwarps] + __popc(bal[0] & lt_mask) + __popc(bal[1] & lt_mask) + __popc(bal[2] & lt_mask) +
-                              __popc(bal[3] & lt_mask);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float y = __uint_as_float(s4[k]);
-                        if (y >= tau) {
-                            cy[pos] = y;
-                            cid[pos] = col[u] + k;
-                            ++pos;
-                            hmin = fminf(hmin, y);
-                            hmax = fmaxf(hmax, y);
-                        }
-                    }
-                }
+                for (int u = 0; u < EMAX; ++u)
+                    if (e0 + u < e1) emit(ent[u]);
+            } else {
+                for (int e = e0; e < e1; ++e) emit(*entry_ptr(e, sl));
+            }
         }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) {
-            hmin = fminf(hmin, __shfl_xor_sync(0xffffffffu, hmin, off));
-            hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, off));
-        }
-        if (lane == 0) { S.red[warp] = hmin; S.red[32 + warp] = hmax; }
         __syncthreads();
-        for (int w = 0; w < nwarps; ++w) { hmin = fminf(hmin, S.red[w]); hmax = fmaxf(hmax, S.red[32 + w]); }
 
-        const SmemValues src{cy, n};
-        const float theta = select_rth(src, n, Z, S, true, hmin, hmax);
+        // ---- 4. theta ---------------------------------------------------------------------------------------------
+        bool exact = true;
+        const float theta = select_rth_fine(SmemValues{cy, n}, Z, hmin, hmax, S, exact);
         const float eps = kBandEps * s_anorm * __uint_as_float(sg.kmax_bits);
         const float lo = theta - eps, hi = theta + eps;
         // everything at or above lo has to be among the candidates, i.e. the threshold was low enough
-        if (t == 0 && !(tau <= lo) && n < sg.n_keys) s_fail = 1;
-        // warp w owns positions [w * per, (w + 1) * per): it counts its certain entries (score > hi) and lists the
-        // band [lo, hi]
-        const int per = (n + nwarps - 1) / nwarps;
-        const int w_begin = min(n, warp * per), w_end = min(n, w_begin + per);
+        if (t == 0 && (!exact || (!(tau <= lo) && n < sg.n_keys))) s_fail = 1;
+
+        // ---- 5. certain entries (score > hi) and the band [lo, hi], per stretch of positions --------------------------
+        const int per = ((n + nthreads - 1) / nthreads) | 1;               // odd: stretches start in different banks
+        const int i0 = min(n, t * per), i1 = min(n, i0 + per);
         int my_in = 0;
-        for (int i = w_begin + lane; i < w_end; i += 32) {
+        for (int i = i0; i < i1; ++i) {
             const float y = cy[i];
             if (y > hi) ++my_in;
             else if (y >= lo) {
@@ -605,11 +909,9 @@ candidate_select_kernel(SelParams p)
                 if (slot < kMaxBand) band[slot] = i;
             }
         }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) my_in += __shfl_xor_sync(0xffffffffu, my_in, off);
-        if (lane == 0) { warp_in[warp] = my_in; atomicAdd(&warp_in[32], my_in); }
-        __syncthreads();
-        const int n_band = s_nband, need = Z - warp_in[32];
+        int total_in;
+        block_exclusive_scan(my_in, scan_ws, total_in);
+        const int n_band = s_nband, need = Z - total_in;
         if (t == 0 && (n_band > kMaxBand || need < 0 || need > n_band)) s_fail = 1;
         __syncthreads();
         if (!s_fail) {
@@ -658,29 +960,26 @@ candidate_select_kernel(SelParams p)
             }
             __syncthreads();
             for (int b = t; b < n_band; b += nthreads)
-                if (band_rank[b] < need) {
-                    cid[band[b]] |= int(0x80000000u);
-                    atomicAdd(&warp_in[band[b] / per], 1);
-                }
+                if (band_rank[b] < need) cid[band[b]] |= int(0x80000000u);
             __syncthreads();
-            // ordered compaction, one warp per range: the candidates are in key order, so is the table row
-            int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
-            int base_out = 0;
-            for (int w = 0; w < warp; ++w) base_out += warp_in[w];
-            for (int i0 = w_begin; i0 < w_end; i0 += 32) {
-                const int i = i0 + lane;
-                bool sel = false;
-                int id = 0;
-                if (i < w_end) {
-                    const float y = cy[i];
-                    id = cid[i];
-                    sel = y > hi || (y >= lo && id < 0);
-                }
-                const unsigned bal = __ballot_sync(0xffffffffu, sel);
-                const int pos = base_out + __popc(bal & ((1u << lane) - 1u));
-                if (sel && pos < Z) out[pos] = sg.kb + (id & 0x7fffffff);
-                base_out += __popc(bal);
+            // ---- 6. ordered write: the candidates are in key order, so is the table row ------------------------------
+            int my_sel = 0;
+            for (int i = i0; i < i1; ++i) {
+                const float y = cy[i];
+                my_sel += (y > hi || (y >= lo && cid[i] < 0)) ? 1 : 0;
             }
+            int total_sel;
+            int out_pos = block_exclusive_scan(my_sel, scan_ws, total_sel);
+            int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
+            for (int i = i0; i < i1; ++i) {
+                const float y = cy[i];
+                const int id = cid[i];
+                if (y > hi || (y >= lo && id < 0)) {
+                    if (out_pos < Z) out[out_pos] = sg.kb + (id & 0x7fffffff);
+                    ++out_pos;
+                }
+            }
+            if (t == 0 && total_sel != Z) s_fail = 1;
         }
     }
     __syncthreads();
@@ -688,6 +987,15 @@ candidate_select_kernel(SelParams p)
         const int slot = atomicAdd(p.fail_count, 1);
         if (slot < kMaxFail) p.fail_list[slot] = row;
     }
+}
+
+template <typename T, int THREADS, int EMAX, bool KEEP>
+static int launch_select(const SelParams &sp, unsigned rows, size_t dyn, cudaStream_t st)
+{
+    FM_CUDA_OK(cudaFuncSetAttribute(candidate_select_kernel<T, THREADS, EMAX, KEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    candidate_select_kernel<T, THREADS, EMAX, KEEP><<<rows, THREADS, dyn, st>>>(sp);
+    FM_LAUNCHED("candidate_select_kernel");
+    return FM_OK;
 }
 
 // ---- 6. fallback: canonical scores of a whole segment for the listed buckets, then the exact row select ---------
@@ -724,10 +1032,6 @@ bool fused_eligible(int dtype, int d, int64_t n_keys, int64_t zc)
     return (dtype == FM_BF16 || dtype == FM_F16) && (d == 64 || d == 128) && n_keys >= 8192 && zc * 4 <= n_keys && zc >= 64 &&
            n_keys <= zc * 4096 && zc <= 12288;      // and a bucket's candidates have to fit the selection bitmap
 }
-
-// CTA size of the selection kernels: what they hold in shared memory decides how many CTAs share an SM, so a
-// large footprint gets more threads per CTA.
-static int sel_threads(size_t dyn_smem) { return dyn_smem <= (48u << 10) ? kSelCThreads : (dyn_smem <= (100u << 10) ? 512 : 1024); }
 
 // Key ranges per bucket tile for the candidate pass: units = mtiles * ranges CTAs of one tile row each.  The fewest
 // ranges that fill the last wave of CTAs to 95 % (else the best found), never cutting a segment below 16 key tiles
@@ -766,6 +1070,8 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
         P.ld_sample = std::max<int64_t>(P.ld_sample, n_keys[i] / P.step + 2);
     }
     P.cap = (cap + 7) / 8 * 8;
+    // shared memory of the selection kernel: candidate scores + key indices, tile masks, entries before each tile
+    P.sel_smem = size_t(P.cap) * 8 + size_t(ceil_div(P.max_keys, kTcBN)) * 12 + 32;
     P.ld_sample = (P.ld_sample + 31) / 32 * 32;              // the dense scores are stored in 32 x 32 blocks
     const size_t per_bucket = size_t(P.ld_sample) * 4 + size_t(P.cap) * 16 + size_t(ceil_div(P.max_keys, kTcBN)) * 8;
     // rows of a group: every segment starts on a multiple of 32 rows
@@ -788,21 +1094,64 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
     return P;
 }
 
-// One extra stream per device for work that may run beside the main sequence of a build (nullptr if it cannot be made:
-// the work then stays on the caller's stream).
-static cudaStream_t side_stream()
+// Per-device helpers of a build, made once: an extra stream for work that may run beside the main sequence with the two
+// events that fork and join it (stream == nullptr if they cannot be made: the work then stays on the caller's stream),
+// and a small ring of pinned staging buffers for the segment descriptors, so that their copies to the device never
+// make the host wait for the stream (a copy from pageable memory may).  A slot is reused only after the copies that
+// read it have run (its event).
+constexpr int kStageSlots = 4;
+constexpr size_t kStageBytes = 64 << 10;
+struct BuildSide {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    char *stage[kStageSlots] = {};
+    cudaEvent_t stage_done[kStageSlots] = {};
+    int next = 0;
+    bool tried = false;
+};
+static std::mutex g_side_mu;
+static BuildSide g_side[64];
+
+static BuildSide *build_side()
 {
-    static std::mutex mu;
-    static cudaStream_t tab[64] = {};
-    static bool tried[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    std::lock_guard<std::mutex> lock(mu);
-    if (!tried[dev]) {
-        tried[dev] = true;
-        if (cudaStreamCreateWithFlags(&tab[dev], cudaStreamNonBlocking) != cudaSuccess) { tab[dev] = nullptr; cudaGetLastError(); }
+    std::lock_guard<std::mutex> lock(g_side_mu);
+    BuildSide &b = g_side[dev];
+    if (!b.tried) {
+        b.tried = true;
+        bool ok = cudaStreamCreateWithFlags(&b.stream, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&b.fork, cudaEventDisableTiming) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&b.join, cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) { b.stream = nullptr; cudaGetLastError(); }
+        for (int i = 0; i < kStageSlots; ++i) {
+            if (cudaMallocHost((void **)&b.stage[i], kStageBytes) != cudaSuccess ||
+                cudaEventCreateWithFlags(&b.stage_done[i], cudaEventDisableTiming) != cudaSuccess) {
+                b.stage[i] = nullptr;
+                cudaGetLastError();
+            }
+        }
     }
-    return tab[dev];
+    return &b;
+}
+
+// Copies `bytes` of host data to the device on `st` through a pinned staging slot when one is to be had.
+static int stage_to_device(BuildSide *side, void *dst, const void *src, size_t bytes, cudaStream_t st)
+{
+    int slot = -1;
+    if (side && bytes <= kStageBytes) {
+        std::lock_guard<std::mutex> lock(g_side_mu);
+        if (side->stage[side->next]) { slot = side->next; side->next = (side->next + 1) % kStageSlots; }
+    }
+    if (slot < 0) {
+        FM_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st));
+        return FM_OK;
+    }
+    FM_CUDA_OK(cudaEventSynchronize(side->stage_done[slot]));             // the slot's previous copy has run (long ago, as a rule)
+    memcpy(side->stage[slot], src, bytes);
+    FM_CUDA_OK(cudaMemcpyAsync(dst, side->stage[slot], bytes, cudaMemcpyHostToDevice, st));
+    FM_CUDA_OK(cudaEventRecord(side->stage_done[slot], st));
+    return FM_OK;
 }
 
 // Builds the table rows of the listed segments.  status word (ws + 0): 0 = ok, 1-3 = a tensor-core pipeline
@@ -846,9 +1195,11 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         const int ng = g1 - g0;
         FusedSeg *dsegs = (FusedSeg *)(ws + P.off_segs) + g0;
         TcSeg *dtc_s = (TcSeg *)(ws + P.off_tcseg) + g0, *dtc_m = (TcSeg *)(ws + P.off_tcseg) + n + g0;
-        FM_CUDA_OK(cudaMemcpyAsync(dsegs, hs.data() + g0, sizeof(FusedSeg) * ng, cudaMemcpyHostToDevice, st));
-        FM_CUDA_OK(cudaMemcpyAsync(dtc_s, ht.data() + g0, sizeof(TcSeg) * ng, cudaMemcpyHostToDevice, st));
-        FM_CUDA_OK(cudaMemcpyAsync(dtc_m, ht.data() + n + g0, sizeof(TcSeg) * ng, cudaMemcpyHostToDevice, st));
+        BuildSide *bs = build_side();
+        rc = stage_to_device(bs, dsegs, hs.data() + g0, sizeof(FusedSeg) * ng, st);
+        if (rc == FM_OK) rc = stage_to_device(bs, dtc_s, ht.data() + g0, sizeof(TcSeg) * ng, st);
+        if (rc == FM_OK) rc = stage_to_device(bs, dtc_m, ht.data() + n + g0, sizeof(TcSeg) * ng, st);
+        if (rc != FM_OK) return rc;
         FM_CUDA_OK(cudaMemsetAsync(ws + P.off_fail, 0, 256, st));
         float *tau = (float *)(ws + P.off_tau);
         int *counts = (int *)(ws + P.off_count);
@@ -860,11 +1211,9 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
 
         // The key norms are only needed by the selection: they are taken on a second stream, under the sample pass and
         // the threshold selection (which leave most of the memory bandwidth idle), and joined before the selection.
-        cudaStream_t side = side_stream();
-        cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+        cudaStream_t side = bs ? bs->stream : nullptr;
+        cudaEvent_t ev_fork = bs ? bs->fork : nullptr, ev_join = bs ? bs->join : nullptr;
         if (side) {
-            FM_CUDA_OK(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
-            FM_CUDA_OK(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
             FM_CUDA_OK(cudaEventRecord(ev_fork, st));
             FM_CUDA_OK(cudaStreamWaitEvent(side, ev_fork, 0));
         }
@@ -883,7 +1232,29 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
             if (rc != FM_OK) return rc;
         }
         {
-            sample_tau_kernel<<<(unsigned)rows, kTauThreads, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau);
+            // the row sits in the CTA's registers: 16 pieces of four scores per thread; enough threads for the pre-filter's
+            // thread maxima to outnumber the rank where that is possible
+            int64_t n4_max = 0, rank_max = 0;
+            for (int i = g0; i < g1; ++i) { n4_max = std::max<int64_t>(n4_max, (hs[i].ns + 3) / 4); rank_max = std::max<int64_t>(rank_max, hs[i].rank); }
+            const int64_t by_rank = ceil_div(rank_max, 2) + 32;          // threads whose two maxima each comfortably outnumber the rank
+            if (n4_max > 12 * 1024) {
+                set_error("fused index build: a sample row of %lld scores does not fit the threshold kernel", (long long)n4_max * 4);
+                return FM_ERR_UNSUPPORTED;
+            }
+            // eight rows per CTA first (whole 128-byte lines); the rows it leaves unset (tau = NaN) go to the one-row kernel
+            bool first = false;
+            if (rank_max <= 200 && n4_max >= 256) {
+                const size_t dyn8 = size_t(kTau8Rows) * kTau8List * 4 + 8 * sizeof(Tau8Warp);
+                FM_CUDA_OK(cudaFuncSetAttribute(sample_tau8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn8));
+                sample_tau8_kernel<<<(unsigned)(rows / kTau8Rows), kTau8Threads, dyn8, st>>>(Ys, P.ld_sample, dsegs, ng, tau);
+                FM_LAUNCHED("sample_tau8_kernel");
+                first = true;
+            }
+            const unsigned grid1 = first ? (unsigned)ceil_div(rows, kTauStretch) : (unsigned)rows;
+            if (n4_max <= 8 * 256 && by_rank <= 256) sample_tau_kernel<256, 8><<<grid1, 256, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau, (int)rows, first);
+            else if (n4_max <= 16 * 256 && by_rank <= 256) sample_tau_kernel<256, 16><<<grid1, 256, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau, (int)rows, first);
+            else if (n4_max <= 16 * 512) sample_tau_kernel<512, 16><<<grid1, 512, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau, (int)rows, first);
+            else sample_tau_kernel<1024, 12><<<grid1, 1024, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau, (int)rows, first);
         }
         FM_LAUNCHED("sample_tau_kernel");
 
@@ -897,18 +1268,21 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         rc = tc_project_launch(tmA, tmK, tp, int(mtiles) * tp.n_ranges, d, false, dtype == FM_BF16, st);
         if (rc != FM_OK) return rc;
 
-        if (side) {
-            FM_CUDA_OK(cudaStreamWaitEvent(st, ev_join, 0));
-            cudaEventDestroy(ev_fork);                       // released once the work that uses them has run
-            cudaEventDestroy(ev_join);
-        }
-        SelParams sp = {dsegs, ng, tp.n_ranges, P.cap, cand, cand_mask, P.group_buckets, counts, tau, A, K, d, table, fail_count, fail_list};
+        if (side) FM_CUDA_OK(cudaStreamWaitEvent(st, ev_join, 0));
+        const int max_tiles = (int)ceil_div(P.max_keys, kTcBN);
+        SelParams sp = {dsegs, ng, tp.n_ranges, P.cap, cand, cand_mask, P.group_buckets, counts, tau, A, K, d, table, fail_count, fail_list,
+                        max_tiles};
         {
-            const size_t dyn = size_t(P.cap) * 8;
-            FM_CUDA_OK(cudaFuncSetAttribute(candidate_select_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-            candidate_select_kernel<T><<<(unsigned)rows, sel_threads(dyn), dyn, st>>>(sp);
+            // candidate scores + key indices, tile masks, entries before each tile
+            const size_t dyn = P.sel_smem;
+            // entries in registers where a CTA's threads can hold them.  Measured on the 32-head benchmark build: 512
+            // threads x 9 entries 1.21 ms, 256 x 18 1.42 ms, 128 x 40 read twice 2.11 ms - the CTA's steps are chains of
+            // memory round trips and barriers, and fewer warps hide less of them
+            if (P.cap <= 9 * 512) rc = launch_select<T, 512, 9, true>(sp, (unsigned)rows, dyn, st);
+            else if (P.cap <= 8 * 1024) rc = launch_select<T, 1024, 8, true>(sp, (unsigned)rows, dyn, st);
+            else rc = launch_select<T, 1024, 25, false>(sp, (unsigned)rows, dyn, st);
+            if (rc != FM_OK) return rc;
         }
-        FM_LAUNCHED("candidate_select_kernel");
 
         fallback_scores_kernel<T><<<dim3((unsigned)std::min<int64_t>(ceil_div(P.max_keys, 256), 4 * sms), kMaxFail), 256, 0, st>>>(
             dsegs, ng, fail_count, fail_list, (const T *)A, (const T *)K, d, Yf, P.max_keys);

@@ -5,7 +5,8 @@
 
 namespace fm {
 
-constexpr int kFusedMaxCap = 25000;        // candidate slots per bucket the selection can hold in shared memory
+constexpr int kFusedMaxCap = 25000;        // candidate slots per bucket the selection can deal out to its threads
+constexpr size_t kFusedMaxSelSmem = 208u << 10;   // dynamic shared memory the selection may ask for (beside ~17 KB static)
 
 struct FusedPlan {
     int step;                  // every step-th key is sampled for the threshold estimate
@@ -13,6 +14,7 @@ struct FusedPlan {
     int64_t ld_sample;         // columns of the sample score matrix
     int64_t max_keys;          // longest segment
     int64_t group_buckets;     // buckets processed per group of segments
+    size_t sel_smem;           // dynamic shared memory of the selection kernel
     size_t off_status, off_segs, off_tcseg, off_tau, off_count, off_fail, off_ys, off_cand, off_mask, off_yf, total;
 };
 

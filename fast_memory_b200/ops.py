@@ -239,7 +239,7 @@ def shard_filter(k_hashes: torch.Tensor, lo: int, hi: int) -> Tuple[torch.Tensor
     assert k_hashes.dim() == 3 and k_hashes.dtype == torch.int64
     k_hashes = k_hashes.contiguous()
     C, H, Z = k_hashes.shape
-    flat = torch.empty(C * H * Z, dtype=torch.int64, device=dev)
+    flat = torch.zeros(C * H * Z, dtype=torch.int64, device=dev)      # the unused tail reads 0, not leftovers
     counts = torch.empty(H, C, dtype=torch.int64, device=dev)
     ws = _ws.get("shard_filter", L.lib().fm_shard_filter_workspace_bytes(C, H), dev)
     L.check(L.lib().fm_shard_filter(L.ptr(k_hashes), C, H, Z, int(lo), int(hi), L.ptr(flat), L.ptr(counts), L.ptr(ws),

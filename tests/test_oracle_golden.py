@@ -34,6 +34,27 @@ def test_gathered_oracle_matches_reference_kernel(golden_dir, name):
     assert torch.allclose(ref_like, c["lse"], atol=tol_l, rtol=0)
 
 
+NATIVE_CASES = ["attn_bf16_ragged", "attn_bf16_d128", "attn_f16_native_d64"]
+
+
+@pytest.mark.parametrize("name", NATIVE_CASES)
+def test_gathered_oracle_matches_native_reference_kernel(golden_dir, name):
+    """Vectors of the reference's wrapper + Triton kernel compiled natively on a B200 (``make_golden.py --native-bf16``):
+    the only way to get the reference's bf16 results.  O within one bf16 / fp16 ulp of values below 0.25, the fp32 LSE
+    as the kernel wrote it within 5e-6, empty buckets as o = 0 / -inf, and the wrapper's rounded LSE (tk:111) exactly."""
+    c = load_attn(golden_dir, name)
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    lse_f32 = torch.from_numpy(z["lse_f32"])
+    o, lse = O.hashed_attention(c["q"], c["k"], c["v"], c["k_hashes"], c["k_hash_counts"], c["q_hashes"], c["sm_scale"])
+    ulp = 2.0 ** -11 if c["dtype"] == torch.bfloat16 else 2.0 ** -14
+    assert (o.float() - c["o"]).abs().max() <= ulp
+    fin = torch.isfinite(lse_f32)
+    assert (~fin).any() and torch.equal(torch.isfinite(lse), fin)
+    assert (c["o"][~fin] == 0).all() and (o[~fin] == 0).all()
+    assert (lse[fin] - lse_f32[fin]).abs().max() <= 5e-6
+    assert torch.equal(O.dropin_lse(lse, c["dtype"]).float(), c["lse"])
+
+
 @pytest.mark.parametrize("name", ["attn_f32_tiny", "attn_f32_ragged", "attn_f32_d128", "attn_f32_empty_buckets"])
 def test_dense_oracle_matches_reference_kernel(golden_dir, name):
     c = load_attn(golden_dir, name)
