@@ -29,7 +29,9 @@ struct AttnParams {
     int nkc_max;
     float scale2;                          // sm_scale * log2(e)
     // workspace
-    int *counters;                         // [0] = number of items, [1] = next item to hand out
+    int *counters;                         // [0] = number of items, [1] = next item to hand out, [2] = a bucket longer than the
+                                           // workspace was sized for, [3] = a bounded wait gave up; [8], [9] = the same pair as
+                                           // [0], [1] for the list of items to serve again (`redo`)
     int4 *items;                           // {bucket, first query position, key chunk, chunks of the bucket}
     int max_items;
     int q_block;                            // queries per work item: 16 (CUDA-core kernel) or 32 (tensor-core kernel)
@@ -46,7 +48,7 @@ __device__ __forceinline__ int64_t load_index(const void *table, int idx_bytes, 
 struct AttnLayout {
     int key_chunk, nkc_max;
     int64_t max_items;
-    size_t off_items, off_qparts, off_partials, total;
+    size_t off_items, off_redo, off_qparts, off_partials, total;
 };
 
 inline AttnLayout attn_layout(int64_t n_q_rows, int64_t total_buckets, int64_t max_bucket_len, int d, int64_t key_chunk,
@@ -71,6 +73,8 @@ inline AttnLayout attn_layout(int64_t n_q_rows, int64_t total_buckets, int64_t m
     L.max_items = (ceil_div(n_q_rows, kQB) + std::min(total_buckets, n_q_rows)) * L.nkc_max;
     size_t off = 256;                                      // counters
     L.off_items = off;
+    off += align_up(size_t(L.max_items) * sizeof(int4), 256);
+    L.off_redo = off;                                      // items the tcgen05 kernel hands back (same capacity)
     off += align_up(size_t(L.max_items) * sizeof(int4), 256);
     L.off_qparts = off;
     off += align_up(size_t(n_q_rows) * 4, 256);

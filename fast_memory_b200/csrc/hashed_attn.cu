@@ -11,10 +11,30 @@
 // and a bucket may be cut into key chunks whose partials are combined afterwards.
 #include "attn_common.cuh"
 
+#include <cstdlib>
+#include <cstring>
+
 namespace fm {
 
 int launch_attn_mma(const AttnParams &p, int dtype, int d, int grid, cudaStream_t st);   // hashed_attn_mma.cu
 bool attn_mma_supported(int dtype, int d);
+int launch_attn_tc(const AttnParams &p, int dtype, int grid, int4 *redo_items, int *redo_count, cudaStream_t st);   // hashed_attn_tc.cu
+bool attn_tc_supported(int dtype, int d);
+
+// Which tensor-core kernel serves 16-bit inputs with head dim 128: the mma.sync kernel (0, the default: it is the faster
+// one, see hashed_attn_tc.cu) or the tcgen05 kernel (1).  Set by fm_set_attn_kernel, initially from FASTMEM_ATTN_KERNEL
+// (= mma | tc).
+static std::atomic<int> g_attn_kernel{-1};
+static bool prefer_tc_kernel()
+{
+    int c = g_attn_kernel.load(std::memory_order_relaxed);
+    if (c < 0) {
+        const char *e = getenv("FASTMEM_ATTN_KERNEL");
+        c = (e && !strcmp(e, "tc")) ? 1 : 0;
+        g_attn_kernel.store(c, std::memory_order_relaxed);
+    }
+    return c == 1;
+}
 
 // ---- planning -----------------------------------------------------------------------------------
 __global__ void attn_plan_kernel(AttnParams p)
@@ -308,6 +328,16 @@ static int dispatch_simt(const AttnParams &p, int d, int grid, cudaStream_t st)
 
 }  // namespace fm
 
+extern "C" int fm_set_attn_kernel(int which)
+{
+    if (which != 0 && which != 1) {
+        fm::set_error("fm_set_attn_kernel: 0 (mma.sync) or 1 (tcgen05), got %d", which);
+        return FM_ERR_BAD_ARG;
+    }
+    fm::g_attn_kernel.store(which, std::memory_order_relaxed);
+    return FM_OK;
+}
+
 extern "C" size_t fm_hashed_attn_workspace_bytes(int64_t n_q_rows, int64_t total_buckets, int64_t max_bucket_len, int d,
                                                  int64_t key_chunk)
 {
@@ -361,14 +391,25 @@ extern "C" int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, i
     const int64_t groups_bound = std::min<int64_t>(total_buckets, n_q_rows);
     p.q_block = use_mma ? (groups_bound >= int64_t(24) * sms ? 32 : 16) : kQB;
 
-    FM_CUDA_OK(cudaMemsetAsync(p.counters, 0, 12, st));
+    FM_CUDA_OK(cudaMemsetAsync(p.counters, 0, 64, st));
     if (L.nkc_max > 1) FM_CUDA_OK(cudaMemsetAsync(p.qparts, 0, size_t(n_q_rows) * 4, st));
     attn_plan_kernel<<<(unsigned)ceil_div(total_buckets, 256), 256, 0, st>>>(p);
     FM_LAUNCHED("attn_plan_kernel");
 
     int rc;
     int grid = (int)std::min<int64_t>(L.max_items, int64_t(sms) * (use_mma ? 3 : 4));
-    if (use_mma) rc = launch_attn_mma(p, dtype, d, grid, st);
+    if (use_mma && attn_tc_supported(dtype, d) && prefer_tc_kernel()) {
+        // tcgen05 kernel, one CTA per SM; the items it hands back (a later score far above the first tile's best) are
+        // served again by the mma.sync kernel, which reads their count from the device
+        int4 *redo = (int4 *)(ws + L.off_redo);
+        rc = launch_attn_tc(p, dtype, (int)std::min<int64_t>(L.max_items, sms), redo, p.counters + 8, st);
+        if (rc == FM_OK) {
+            AttnParams again = p;
+            again.items = redo;
+            again.counters = p.counters + 8;
+            rc = launch_attn_mma(again, dtype, d, (int)std::min<int64_t>(L.max_items, 2 * int64_t(sms)), st);
+        }
+    } else if (use_mma) rc = launch_attn_mma(p, dtype, d, grid, st);
     else if (dtype == FM_F32) rc = dispatch_simt<float>(p, d, grid, st);
     else if (dtype == FM_BF16) rc = dispatch_simt<__nv_bfloat16>(p, d, grid, st);
     else rc = dispatch_simt<__half>(p, d, grid, st);

@@ -40,6 +40,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// has the phase with the given parity completed?  Never blocks.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns()
 {
     uint64_t t;
@@ -56,6 +66,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 255u) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) return false;
+        }
+    }
+}
+
+// The same wait that also gives up as soon as `*abort` is set (another role of the CTA failed): checked every 64 polls.
+__device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity, const volatile int *abort)
+{
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u) {
+            if (*abort) return false;
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
             else if (now - t0 > kWaitLimitNs) return false;
@@ -112,6 +137,21 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32])
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
+// 16 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :: "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // The same wait, naming the registers an earlier load fills: their uses cannot be scheduled above it.
 __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32])
@@ -124,6 +164,47 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32])
                  :: "memory");
 }
 
+// 32 consecutive fp32 columns of this thread's TMEM lane, written from registers
+__device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+                    "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+                    "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+                    "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Arrives on the mbarrier once every cp.async copy this thread has issued so far has landed (the barrier's count must
+// include this arrival: .noinc).
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar)
+{
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Makes shared-memory writes of this thread (plain stores, completed cp.async copies) visible to the async proxy,
+// i.e. to tcgen05.mma operand reads and TMA; executed by the writer before it signals the consumer.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Named barrier over `count` threads (a multiple of 32) that also ANDs a predicate over them: every participant
+// gets the same verdict, so a give-up after a bounded wait is taken by all of them together.
+__device__ __forceinline__ bool named_barrier_and(int id, int count, bool pred)
+{
+    uint32_t out;
+    asm volatile("{\n\t.reg .pred p, q;\n\t"
+                 "setp.ne.b32 p, %3, 0;\n\t"
+                 "barrier.cta.red.and.pred q, %1, %2, p;\n\t"
+                 "selp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(out) : "r"(id), "r"(count), "r"(pred ? 1u : 0u) : "memory");
+    return out != 0;
+}
+__device__ __forceinline__ void named_barrier(int id, int count)
+{
+    asm volatile("barrier.cta.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 // ---- descriptors -----------------------------------------------------------------------------------------
 // K-major, 128-byte swizzle: start address >> 4 in bits [0,14); LBO (unused with swizzle) = 1 in [16,30);
 // SBO = 1024 B >> 4 in [32,46); descriptor version 1 in [46,48); layout type SWIZZLE_128B = 2 in [61,64).
@@ -132,11 +213,27 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
     return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
            (uint64_t(2) << 61);
 }
+// MN-major operand (the contraction index is the ROW index of the shared-memory tile): rows of 64 elements (128 bytes,
+// 128-byte swizzle), 8-row groups 1024 bytes apart (SBO), the next 64 elements along M / N `lbo_bytes` away (LBO).
+// One MMA step (K = 16) takes 16 rows: the start address advances by 16 * 128 bytes.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr, uint32_t lbo_bytes)
+{
+    return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+           (uint64_t(2) << 61);
+}
+// MN-major operand whose rows hold 32 elements (64 bytes, 64-byte swizzle: chunk ^= (row >> 1) & 3), 8-row groups 512
+// bytes apart; used for an N = 32 operand, so there is no second block along N.  K = 16 takes 16 rows = 1024 bytes.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw64(uint32_t saddr)
+{
+    return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(512 >> 4) << 32) | (uint64_t(1) << 46) |
+           (uint64_t(4) << 61);
+}
 // kind::f16 instruction descriptor: fp32 accumulate (bits [4,6) = 1), A/B format in [7,10) / [10,13)
 // (0 = fp16, 1 = bf16), both operands K-major (bits 15, 16 = 0), N >> 3 in [17,23), M >> 4 in [24,29).
-__host__ __device__ constexpr uint32_t instr_desc_f16(bool bf16, int M, int N)
+__host__ __device__ constexpr uint32_t instr_desc_f16(bool bf16, int M, int N, bool a_mn_major = false, bool b_mn_major = false)
 {
-    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+           ((b_mn_major ? 1u : 0u) << 16) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
 }
 
 }  // namespace tc

@@ -117,6 +117,14 @@ def hashed_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: t
     return out, lse
 
 
+def set_attention_kernel(which: str) -> None:
+    """Which tensor-core kernel serves bf16 / fp16 queries with head dim 128: ``"mma"`` (mma.sync, the default and the
+    faster one) or ``"tc"`` (tcgen05 with TMEM accumulators).  Process-wide."""
+    if which not in ("mma", "tc"):
+        raise ValueError("set_attention_kernel: 'mma' or 'tc'")
+    L.check(L.lib().fm_set_attn_kernel(1 if which == "tc" else 0), "fm_set_attn_kernel")
+
+
 def hashed_attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: torch.Tensor, bucket_off: torch.Tensor,
                               group_off: torch.Tensor, perm: torch.Tensor, sm_scale: float, out: torch.Tensor, lse: torch.Tensor,
                               d_out: torch.Tensor, bucket_kbase: Optional[torch.Tensor] = None,

@@ -118,7 +118,13 @@ int fm_group_rows_static(const int32_t *hash, int64_t n_rows, int64_t total_buck
  *              longer bucket beyond the bound are left out, and the third int32 of the workspace
  *              reads 1 after the launch.  Query rows that no group of group_off / perm lists are not
  *              written: start o / lse at 0 / -inf if the hashes are not known to be in range.
+ *
+ * Two tensor-core kernels serve 16-bit inputs with head dim 128: mma.sync (0, the default and the
+ * faster of the two on every workload measured) and tcgen05 / TMEM (1).  fm_set_attn_kernel selects
+ * one for the process (initial value from the environment variable FASTMEM_ATTN_KERNEL = mma | tc);
+ * other shapes are unaffected.  It has no counterpart in the reference (Triton picks its own code).
  * ------------------------------------------------------------------------------------------- */
+int fm_set_attn_kernel(int which);
 size_t fm_hashed_attn_workspace_bytes(int64_t n_q_rows, int64_t total_buckets, int64_t max_bucket_len, int d,
                                       int64_t key_chunk);
 int fm_hashed_attn_fwd(const void *q, const void *k, const void *v, int dtype, int d, int64_t n_q_rows,
