@@ -655,6 +655,18 @@ def run_ring(args, rank, world):
 
     steps = min(args.steps, args.sharded_steps) if args.workload != "cfg5" else args.steps
     warmup = min(args.warmup, 5) if args.workload != "cfg5" else args.warmup
+    if world > 1 and args.exchange == "peer":
+        # symmetric memory may be unavailable on a box (no peer access): every rank must take the same path
+        try:
+            mem.query(q, sm_scale, exchange="peer")
+            torch.cuda.synchronize()
+            fine = torch.ones(1, device=dev)
+        except Exception as e:                                   # noqa: BLE001 - reported below, the run goes on
+            print(f"rank {rank}: peer exchange unavailable ({type(e).__name__}: {str(e)[:120]}); using all-reduce", file=sys.stderr)
+            fine = torch.zeros(1, device=dev)
+        torch.distributed.all_reduce(fine, op=torch.distributed.ReduceOp.MIN)
+        if fine.item() == 0:
+            args.exchange = "allreduce"
     with ClockSampler(dev.index or 0) as clocks:             # samples span the warm-up and the timed region (both under load)
         for _ in range(warmup):
             mem.query(q, sm_scale, exchange=args.exchange)
@@ -674,6 +686,26 @@ def run_ring(args, rank, world):
     part_ms = time_events(lambda: mem.query_partial(q, sm_scale), steps, warmup=2)
     n_buckets_total = H * cfg.n_buckets
     attn_bytes = n_buckets_total * per * min(cfg.bucket_size, shard_len) * (4 + 2 * d * 2) + H * S * (2 * d * 2 + 8)
+
+    # the exchange alone: the merge of partials that are already there, every rank at once
+    exch_ms = 0.0
+    if world > 1:
+        from fast_memory_b200 import dist as fmd
+        o_p, l_p = mem.query_partial(q, sm_scale)
+        rows = o_p.shape[0] * o_p.shape[1]
+        if args.exchange == "peer":
+            px = mem._peer
+            px.o.copy_(o_p.reshape(rows, d))
+            px.lse.copy_(l_p.reshape(rows))
+            fn = px.merge
+        elif args.exchange == "allreduce":
+            fn = lambda: fmd.allreduce_merge_partials(o_p.reshape(rows, d), l_p.reshape(rows))
+        else:
+            of, lf = o_p.reshape(rows, d).float(), l_p.reshape(rows).clone()
+            fn = lambda: fmd.all_gather_chunks(fmd.ring_reduce_scatter_partials(of, lf)[0], 0)
+        barrier()
+        exch_ms = time_events(fn, steps, warmup=3)
+        del o_p, l_p
 
     # parity of the merged multi-rank result (outside the timed regions)
     o_full, l_full = mem.query(q, sm_scale, exchange=args.exchange)
@@ -708,9 +740,9 @@ def run_ring(args, rank, world):
     build_med = statistics.median(build_ms)
     clk = clocks.summary()
     if world > 1:
-        t = torch.tensor([step_ms, e2e_ms, build_med, part_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([step_ms, e2e_ms, build_med, part_ms, exch_ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        step_ms, e2e_ms, build_med, part_ms = t.tolist()
+        step_ms, e2e_ms, build_med, part_ms, exch_ms = t.tolist()
         mhz = torch.tensor([float(clk["sm_mhz"] or 0)], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(mhz, op=torch.distributed.ReduceOp.MIN)
         clk["sm_mhz_min_over_ranks"] = mhz.item()
@@ -729,7 +761,8 @@ def run_ring(args, rank, world):
                    "parallelism": f"{per} shard(s) per GPU, partial (O, LSE) merged across ranks ({args.exchange})",
                    "l2": f"a head's local K+V is {kv_mb:.0f} MB per GPU, beyond the 126 MB L2: the gather is served by DRAM"},
         "clocks": clk,
-        "local_ms": part_ms, "exchange_ms": step_ms - part_ms, "exchange": args.exchange if world > 1 else "none",
+        "local_ms": part_ms, "exchange_ms": exch_ms, "step_minus_local_ms": step_ms - part_ms,
+        "exchange": args.exchange if world > 1 else "none",
         "ms_x_ghz": step_ms * (clk["sm_mhz"] or 0) / 1e3,
         "parity": parity,
         "e2e": {"value": n_queries / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
@@ -755,6 +788,7 @@ def sharded_record(full):
     return {"workload": full["config"]["workload"], "parallelism": full["config"]["parallelism"], "scaling": "strong",
             "n_gpus": full["n_gpus"], "steps": full["steps"], "value": full["value"], "unit": UNIT,
             "ms_per_step": full["ms_per_step"], "local_ms": full["local_ms"], "exchange_ms": full["exchange_ms"],
+            "step_minus_local_ms": full["step_minus_local_ms"],
             "exchange": full["exchange"], "build_ms": full["index_build"]["ms"], "ms_x_ghz": full["ms_x_ghz"],
             "clocks": full["clocks"], "parity": full["parity"], "e2e_value": full["e2e"]["value"],
             "roofline": {"bound": r["bound"], "achieved": r["achieved"], "peak": r["peak"], "unit": r["unit"], "frac": r["frac"],
@@ -866,8 +900,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2")
-    ap.add_argument("--exchange", default="allreduce", choices=["ring", "allreduce"],
-                    help="cfg5: how the ranks' partial (O, LSE) are merged (ring of send/recv + merge steps, or MAX + SUM all-reduce)")
+    ap.add_argument("--exchange", default="peer", choices=["ring", "allreduce", "peer"],
+                    help="cfg5: how the ranks' partial (O, LSE) are merged (ring of send/recv + merge steps, MAX + SUM "
+                         "all-reduce, or one pull-merge-push kernel per rank over peer memory)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--build-steps", type=int, default=2)
     ap.add_argument("--cpu-seconds", type=float, default=15.0)

@@ -57,6 +57,7 @@ _SIGNATURES = {
     "fm_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_void_p]),
     "fm_lse_merge_out": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int,
                                  c_void_p]),
+    "fm_merge_peer_partials": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_void_p]),
     "fm_project": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),
     "fm_project_tc_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "fm_project_tc": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_void_p, c_int64, c_void_p,

@@ -126,6 +126,80 @@ static int launch_merge_out(const float *acc_out, const float *acc_lse, const vo
     return FM_OK;
 }
 
+
+// ---- merge of the partial results of several ranks over peer memory ------------------------------------------------
+// Every rank holds, in memory its peers can address, its partial (o, lse) over ITS keys for all query rows.  Rank r owns
+// the rows [row0, row1): it pulls those rows of every rank's partial, merges them -
+//     M = max_p lse_p,  w_p = e^(lse_p - M),  out = sum_p w_p o_p / sum_p w_p,  lse = M + log sum_p w_p
+// (the pairwise merge of memory.py:54-71 written as one sum; a rank whose LSE is -inf has weight 0) - and pushes the
+// finished rows to the result buffers of all ranks, so that everyone ends up with the complete result: one kernel in the
+// place of the W - 1 send / receive + merge steps of the reference's ring (memory.py:307-338).  Loads and stores to peer
+// memory are plain ones.  Thread = 8 consecutive elements (16 bytes of a 16-bit o) of one row.
+constexpr int kMaxPeers = 8;
+struct PeerMergeParams {
+    const void *o[kMaxPeers];
+    const float *lse[kMaxPeers];
+    float *out[kMaxPeers];
+    float *lse_out[kMaxPeers];
+    int world;
+    int d;
+    int64_t row0, row1;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+peer_merge_kernel(PeerMergeParams p)
+{
+    const int tpr = p.d / 8;                                 // threads per row
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t r = p.row0 + t / tpr;
+    const int c = int(t % tpr) * 8;
+    if (r >= p.row1) return;
+    float l[kMaxPeers];
+    uint4 raw[kMaxPeers][sizeof(T) == 4 ? 2 : 1];
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMaxPeers; ++w)
+        if (w < p.world) {
+            l[w] = p.lse[w][r];
+            const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.o[w]) + r * p.d + c);
+            raw[w][0] = src[0];
+            if constexpr (sizeof(T) == 4) raw[w][1] = src[1];
+        }
+#pragma unroll
+    for (int w = 0; w < kMaxPeers; ++w)
+        if (w < p.world) M = fmaxf(M, l[w]);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMaxPeers; ++w)
+        if (w < p.world) {
+            const float wt = l[w] > -INFINITY ? expf(l[w] - M) : 0.f;      // (M = -inf only if every l is)
+            den += wt;
+            float f[8];
+            if constexpr (sizeof(T) == 4) {
+                const float *g = reinterpret_cast<const float *>(&raw[w][0]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = g[e];
+            } else {
+                widen8(raw[w][0], f, T());
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(wt, f[e], acc[e]);
+        }
+    const float inv = den > 0.f ? 1.f / den : 0.f;           // no rank has a key for this row: zeros and -inf
+    const float4 lo = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+    const float4 hi = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+    const float L = den > 0.f ? M + logf(den) : -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMaxPeers; ++w)
+        if (w < p.world) {
+            float4 *dst = reinterpret_cast<float4 *>(p.out[w] + r * p.d + c);
+            dst[0] = lo;
+            dst[1] = hi;
+            if (c == 0) p.lse_out[w][r] = L;
+        }
+}
+
 }  // namespace fm
 
 extern "C" int fm_lse_merge(float *out, float *lse, const void *blk_out, int blk_dtype, const void *blk_lse,
@@ -178,4 +252,34 @@ extern "C" int fm_lse_merge_out(const float *acc_out, const float *acc_lse, cons
     case FM_F16: return launch_merge_out<__half>(acc_out, acc_lse, blk_out, blk_lse, dst, dst_dtype, dst_lse, n_rows, d, st);
     default: set_error("fm_lse_merge_out: unknown dtype %d", blk_dtype); return FM_ERR_UNSUPPORTED;
     }
+}
+
+extern "C" int fm_merge_peer_partials(const void *const *o_ptrs, const float *const *lse_ptrs, float *const *out_ptrs,
+                                      float *const *lse_out_ptrs, int world, int o_dtype, int64_t row0, int64_t row1, int d,
+                                      fm_stream_t stream)
+{
+    using namespace fm;
+    FM_REQUIRE(o_ptrs && lse_ptrs && out_ptrs && lse_out_ptrs, "fm_merge_peer_partials: null pointer");
+    FM_REQUIRE(world >= 1 && world <= kMaxPeers, "fm_merge_peer_partials: 1 to %d ranks, got %d", kMaxPeers, world);
+    FM_REQUIRE(row0 >= 0 && row1 >= row0 && d > 0 && d % 8 == 0, "fm_merge_peer_partials: bad sizes");
+    if (row1 == row0) return FM_OK;
+    PeerMergeParams p = {};
+    for (int w = 0; w < world; ++w) {
+        FM_REQUIRE(o_ptrs[w] && lse_ptrs[w] && out_ptrs[w] && lse_out_ptrs[w], "fm_merge_peer_partials: null buffer of rank %d", w);
+        FM_REQUIRE(((uintptr_t)o_ptrs[w] | (uintptr_t)out_ptrs[w]) % 16 == 0, "fm_merge_peer_partials: buffers must be 16-byte aligned");
+        p.o[w] = o_ptrs[w]; p.lse[w] = lse_ptrs[w]; p.out[w] = out_ptrs[w]; p.lse_out[w] = lse_out_ptrs[w];
+    }
+    p.world = world; p.d = d; p.row0 = row0; p.row1 = row1;
+    const int64_t threads = (row1 - row0) * (d / 8);
+    const unsigned grid = (unsigned)ceil_div(threads, 256);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (o_dtype == FM_F32) peer_merge_kernel<float><<<grid, 256, 0, st>>>(p);
+    else if (o_dtype == FM_BF16) peer_merge_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+    else if (o_dtype == FM_F16) peer_merge_kernel<__half><<<grid, 256, 0, st>>>(p);
+    else {
+        set_error("fm_merge_peer_partials: unknown dtype %d", o_dtype);
+        return FM_ERR_UNSUPPORTED;
+    }
+    FM_LAUNCHED("peer_merge_kernel");
+    return FM_OK;
 }

@@ -125,6 +125,48 @@ def allreduce_merge_partials(o: torch.Tensor, lse: torch.Tensor, group: Optional
     return out, M + torch.log(den)
 
 
+class PeerExchange:
+    """Buffers every rank of the group can address (PyTorch symmetric memory over NVLink) for the merge of partial
+    results in one kernel: this rank's partial (o, lse) and the result buffers all ranks push finished rows into.
+    ``merge`` pulls the rows this rank owns from every rank, merges them and pushes them to everyone
+    (``fm_merge_peer_partials``); two small all-reduces on the same stream order the ranks around it (all partials
+    complete before, all results complete after).  No multicast object is bound (plain peer loads and stores)."""
+
+    def __init__(self, rows: int, d: int, dtype: torch.dtype, device, group: Optional[dist.ProcessGroup] = None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("PeerExchange serves up to 8 ranks")
+        self.rows, self.d, self.dtype = rows, d, dtype
+        self.o = symm.empty(rows, d, dtype=dtype, device=device)
+        self.lse = symm.empty(rows, dtype=torch.float32, device=device)
+        self.out = symm.empty(rows, d, dtype=torch.float32, device=device)
+        self.lse_out = symm.empty(rows, dtype=torch.float32, device=device)
+        import ctypes
+        self._ptrs, self._handles = [], []
+        for t in (self.o, self.lse, self.out, self.lse_out):
+            h = symm.rendezvous(t, self.group)
+            self._handles.append(h)                                           # keeps the peer mappings alive
+            self._ptrs.append((ctypes.c_void_p * self.world)(*[int(x) for x in h.buffer_ptrs]))
+        self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+        n = -(-rows // self.world)
+        self.row0, self.row1 = min(rows, self.rank * n), min(rows, (self.rank + 1) * n)
+
+    def merge(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Merge what the ranks have written into ``self.o`` / ``self.lse``; returns fp32 ``(out [rows, d], lse [rows])``,
+        complete on every rank.  The tensors are this object's buffers: they hold the result until the next merge."""
+        dev = self.o.device
+        dist.all_reduce(self._flag, group=self.group)                      # every rank's partial is complete
+        L.check(L.lib().fm_merge_peer_partials(self._ptrs[0], self._ptrs[1], self._ptrs[2], self._ptrs[3], self.world,
+                                               L.dtype_id(self.dtype), self.row0, self.row1, self.d, L.stream_ptr(dev)),
+                "fm_merge_peer_partials")
+        dist.all_reduce(self._flag, group=self.group)                      # every rank's rows have been pushed
+        return self.out, self.lse_out
+
+
 def reduce_scatter_merge_partials(o: torch.Tensor, lse: torch.Tensor, group: Optional[dist.ProcessGroup] = None
                                   ) -> Tuple[torch.Tensor, torch.Tensor]:
     """:func:`allreduce_merge_partials` for a caller that needs only its own rows: ``o`` ``[W, n, d]`` and ``lse`` fp32
@@ -169,6 +211,7 @@ class ShardedMemory:
         self.local: Optional[Memory] = None
         self.group = None
         self.n_shards = self.n_local = 0
+        self._peer: Optional["PeerExchange"] = None
 
     @classmethod
     def build(cls, k_local: torch.Tensor, v_local: torch.Tensor, shard_len: int, *, A: torch.Tensor, bucket_size: int,
@@ -221,11 +264,23 @@ class ShardedMemory:
 
         ``exchange="ring"``: the partial results go around the ring (send/recv + merge per step, then an all-gather),
         as the reference moves its blocks (mem:307-338).  ``exchange="allreduce"``: the merge written as one MAX and
-        one SUM all-reduce (:func:`allreduce_merge_partials`)."""
+        one SUM all-reduce (:func:`allreduce_merge_partials`).  ``exchange="peer"``: the attention writes its partial
+        into memory the other GPUs can address and ONE kernel per rank pulls, merges and pushes the rows it owns
+        (:class:`PeerExchange`; CUDA ranks of one node) - the returned tensors are then the exchange's own buffers,
+        valid until the next query."""
         Hq, S, d = q.shape
-        o, lse = self.local.query(q, sm_scale)
         W = dist.get_world_size(self.group) if dist.is_initialized() else 1
         rows = Hq * S
+        if W > 1 and exchange == "peer":
+            if not gather:
+                raise ValueError("exchange='peer' returns the complete result on every rank")
+            px = self._peer
+            if px is None or px.rows != rows or px.d != d or px.dtype != q.dtype:
+                px = self._peer = PeerExchange(rows, d, q.dtype, q.device, self.group)
+            self.local.query(q, sm_scale, out=px.o.view(Hq, S, d), lse_out=px.lse.view(Hq, S))
+            out, l = px.merge()
+            return out.view(Hq, S, d), l.view(Hq, S)
+        o, lse = self.local.query(q, sm_scale)
         if W == 1:
             return o.float(), lse
         if exchange == "allreduce":

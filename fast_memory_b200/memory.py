@@ -305,10 +305,13 @@ class Memory:
 
     def query(self, q: torch.Tensor, sm_scale: float, cu_seqlens_q: Optional[Sequence[int]] = None,
               q_hashes: Optional[torch.Tensor] = None, key_chunk: int = 0,
-              head_range: Optional[Tuple[int, int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+              head_range: Optional[Tuple[int, int]] = None, out: Optional[torch.Tensor] = None,
+              lse_out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """q ``[Hq, S, d]`` -> (o ``[Hq, S, d]`` in q's dtype, lse ``[Hq, S]`` fp32 natural log; ``-inf``
         and o = 0 where the query's bucket is empty).  ``head_range = (h0, h1)``: ``q`` holds only the queries of
-        KV heads ``h0 .. h1-1`` (uniform memories; heads are independent, so a batch can be served in slices)."""
+        KV heads ``h0 .. h1-1`` (uniform memories; heads are independent, so a batch can be served in slices).
+        ``out`` / ``lse_out``: contiguous tensors of the result's shapes and dtypes to write into (e.g. buffers other
+        GPUs can address)."""
         dev = L.require_cuda(q)
         n_heads = self.n_heads if head_range is None else head_range[1] - head_range[0]
         if head_range is not None and (self.n_seq != 1 or cu_seqlens_q is not None or not 0 <= head_range[0] < head_range[1] <= self.n_heads):
@@ -337,8 +340,17 @@ class Memory:
         else:
             hashes = q_hashes.reshape(-1).to(torch.int32).contiguous()
         group_off, perm = ops.group_rows(hashes, self.total_buckets, seg_xb, seg_cb)
+        if out is not None or lse_out is not None:
+            if out is None or lse_out is None or out.dtype != q.dtype or lse_out.dtype != torch.float32 or \
+                    out.numel() != q.numel() or lse_out.numel() != Hq * S or not out.is_contiguous() or not lse_out.is_contiguous():
+                raise ValueError("out / lse_out must both be given, contiguous, shaped like the result, in q's dtype / float32")
+            if q_hashes is not None:                             # caller-made hashes may fall outside the buckets
+                out.zero_()
+                lse_out.fill_(float("-inf"))
         o, lse = ops.hashed_attention(qf, self.k.reshape(-1, d), self.v.reshape(-1, d), self.table, self.bucket_off,
                                       group_off, perm, sm_scale, self.max_bucket_len, key_chunk=key_chunk,
+                                      out=None if out is None else out.view(Hq * S, d),
+                                      lse=None if lse_out is None else lse_out.view(Hq * S),
                                       prefill=q_hashes is not None)       # caller-made hashes may fall outside the buckets
         return o.reshape(Hq, S, d), lse.reshape(Hq, S)
 

@@ -167,6 +167,19 @@ int fm_shard_filter(const int64_t *k_hashes, int64_t C, int64_t H, int64_t Z, in
 int fm_lse_merge(float *out, float *lse, const void *blk_out, int blk_dtype, const void *blk_lse, int lse_dtype,
                  int64_t n_rows, int d, fm_stream_t stream);
 
+/* Merge of the partial results of `world` ranks (<= 8) over peer memory, for keys sharded over the ranks:
+ * o_ptrs[w] / lse_ptrs[w] address rank w's partial (o [rows, d] in `o_dtype`, lse [rows] fp32) over its own keys for
+ * all query rows, out_ptrs[w] / lse_out_ptrs[w] rank w's result buffers (fp32) - all of them addresses THIS GPU can
+ * load from / store to (peer mappings of symmetric allocations; the arrays of pointers are host arrays).  The caller
+ * owns rows [row0, row1): it pulls them from every rank, merges them (lse = log sum_w e^lse_w, out = the e^lse_w
+ * weighted mean) and pushes the finished rows to every rank's result buffers.
+ * Replaces: the ring of K / V blocks with its per-step update_out_and_lse, mem:307-338 (the keys stay where they are;
+ * what travels is one pull of partial rows and one push of finished rows).  The caller orders the launches of the
+ * ranks: all partials complete before, all results complete after (e.g. a small collective on the same stream). */
+int fm_merge_peer_partials(const void *const *o_ptrs, const float *const *lse_ptrs, float *const *out_ptrs,
+                           float *const *lse_out_ptrs, int world, int o_dtype, int64_t row0, int64_t row1, int d,
+                           fm_stream_t stream);
+
 /* The same merge out of place, for a caller that keeps its accumulator (e.g. a local-window result merged with a new
  * memory result per request, mem:332): reads (acc_out fp32, acc_lse fp32) and (blk_out in `blk_dtype`, blk_lse fp32),
  * writes the merged rows to `dst` in `dst_dtype` (FM_F32 or `blk_dtype`) and their LSE to `dst_lse`. */

@@ -63,6 +63,12 @@ def _rank_main(rank, world, port, n_shards, H, L, S, C, Z, result):
     o2, lse2 = mem.query(q.to(dev), cfg.d ** -0.5, exchange="allreduce")
     torch.cuda.synchronize()
     assert (o2 - o).abs().max() <= 1e-4 and (lse2 - lse).abs().max() <= 1e-4       # two ways to merge the same partials
+    # the third: one kernel per rank over peer memory (pull the partial rows, merge, push the finished rows), twice in a
+    # row (the second query reuses the exchange buffers)
+    for _ in range(2):
+        o4, lse4 = mem.query(q.to(dev), cfg.d ** -0.5, exchange="peer")
+        torch.cuda.synchronize()
+        assert (o4 - o).abs().max() <= 1e-4 and (lse4 - lse).abs().max() <= 1e-4
     # queries sequence-sharded like the keys (the reference's layout): this rank's slice in, its rows of the result out
     n = S // world
     o3, lse3 = mem.query_sharded(q[:, rank * n:(rank + 1) * n].contiguous().to(dev), cfg.d ** -0.5)
