@@ -45,6 +45,7 @@ _SIGNATURES = {
                                      c_void_p]),
     "fm_hashed_attn_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int, c_int64]),
     "fm_set_attn_kernel": (c_int, [c_int]),
+    "fm_test_set_tc_hooks": (c_int, [c_int, c_int]),
     "fm_hashed_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p,
                                    c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p,
                                    c_void_p, c_int64, c_void_p, c_size_t, c_void_p]),

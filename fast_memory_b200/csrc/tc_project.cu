@@ -127,6 +127,7 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = tmem_slot;
+    const uint64_t limit = p.wait_limit_ns ? p.wait_limit_ns : tc::kWaitLimitNs;
 
     if (warp == 0) {
         // ---- TMA producer ---------------------------------------------------------------------------------
@@ -135,23 +136,32 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tc::prefetch_tensormap(&tmK);
             tc::mbar_arrive_expect_tx(a_bar, A_BYTES);
             for (int kb = 0; kb < KB; ++kb) tc::tma_load_2d(a_smem + kb * (kBM * 128), &tmA, kb * 64, sg.a_row0 + m0, a_bar);
+            int issued = 0;                                  // tiles whose loads were started
             for (int t = 0; t < n_tiles; ++t) {
                 const int s = t % STAGES;
-                if (!tc::mbar_wait(empty_bar(s), ((t / STAGES) & 1) ^ 1)) { atomicExch(p.status, 1); s_abort = 1; break; }
+                if (!tc::mbar_wait(empty_bar(s), ((t / STAGES) & 1) ^ 1, limit)) { atomicExch(p.status, 1); s_abort = 1; break; }
                 if (*(volatile int *)&s_abort) break;
+                if (t == p.skip_tile) continue;              // test hook: this tile never arrives, its consumers give up
                 tc::mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
                 const int key_row = sg.k_row0 + (t_begin + tile_of(t)) * kBN;
                 for (int kb = 0; kb < KB; ++kb)
                     tc::tma_load_2d(k_smem + s * STAGE_BYTES + kb * (kBN * 128), &tmK, kb * 64, key_row, full_bar(s));
+                issued = t + 1;
             }
+            // No copy of this thread may still be in flight when the CTA's shared memory is handed on, whether the
+            // consumers took the tiles or gave up before them: wait (bounded) until the last loads have landed.  A stage's
+            // barrier leaves the phase of tile t only when this thread arms it again, so the parities are unambiguous.
+            tc::mbar_wait(a_bar, 0, limit);
+            for (int t = max(0, issued - STAGES); t < issued; ++t)
+                if (t != p.skip_tile) tc::mbar_wait(full_bar(t % STAGES), (t / STAGES) & 1, limit);
         }
     } else if (warp == 1) {
         // ---- MMA issuer -------------------------------------------------------------------------------------
         if (lane == 0 && n_tiles > 0) {
-            bool ok = tc::mbar_wait(a_bar, 0);
+            bool ok = tc::mbar_wait(a_bar, 0, limit);
             for (int t = 0; ok && t < n_tiles; ++t) {
                 const int s = t % STAGES, acc = t & 1;
-                ok = tc::mbar_wait(tempty_bar(acc), ((t >> 1) & 1) ^ 1) && tc::mbar_wait(full_bar(s), (t / STAGES) & 1);
+                ok = tc::mbar_wait(tempty_bar(acc), ((t >> 1) & 1) ^ 1, limit) && tc::mbar_wait(full_bar(s), (t / STAGES) & 1, limit);
                 if (!ok || *(volatile int *)&s_abort) { ok = false; break; }
                 tc::fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kBN;
@@ -192,7 +202,7 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         bool ok = true;
         for (int t = g; t < n_tiles; t += 2) {
-            ok = tc::mbar_wait(tfull_bar(g), (t >> 1) & 1) && !*(volatile int *)&s_abort;
+            ok = tc::mbar_wait(tfull_bar(g), (t >> 1) & 1, limit) && !*(volatile int *)&s_abort;
             ok = __all_sync(0xffffffffu, ok);                // the TMEM loads below need the whole warp
             if (!ok) break;
             tc::fence_after_sync();
@@ -262,6 +272,15 @@ tc_project_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 // ---- host ----------------------------------------------------------------------------------------------------
+static std::atomic<uint64_t> g_test_wait_limit_ns{0};
+static std::atomic<int> g_test_skip_tile{-1};
+
+void tc_apply_test_hooks(TcParams &p)
+{
+    p.wait_limit_ns = g_test_wait_limit_ns.load(std::memory_order_relaxed);
+    p.skip_tile = g_test_skip_tile.load(std::memory_order_relaxed);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -309,7 +328,9 @@ static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmK, const TcPar
 {
     constexpr size_t smem = size_t(D / 64) * (kBM * 128 + TcCfg<DENSE>::STAGES * kBN * 128) + 1024;
     FM_CUDA_OK(cudaFuncSetAttribute(tc_project_kernel<D, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tc_project_kernel<D, DENSE><<<units, kTcThreads, smem, st>>>(tmA, tmK, p, tc::instr_desc_f16(bf16, kBM, kBN));
+    TcParams q = p;
+    tc_apply_test_hooks(q);
+    tc_project_kernel<D, DENSE><<<units, kTcThreads, smem, st>>>(tmA, tmK, q, tc::instr_desc_f16(bf16, kBM, kBN));
     FM_LAUNCHED("tc_project_kernel");
     return FM_OK;
 }
@@ -385,5 +406,16 @@ extern "C" int fm_project_tc(const void *A, const void *K, int dtype, int64_t C,
     if (rc != FM_OK) return rc;
     unblock_scores_kernel<<<(unsigned)ceil_div(C * n_cols, 256), 256, 0, st>>>(p.Y, p.ldy, C, n_cols, Y, ldy);
     FM_LAUNCHED("unblock_scores_kernel");
+    return FM_OK;
+}
+
+extern "C" int fm_test_set_tc_hooks(int wait_limit_ms, int skip_tile)
+{
+    if (wait_limit_ms < 0 || skip_tile < -1) {
+        fm::set_error("fm_test_set_tc_hooks: bad arguments");
+        return FM_ERR_BAD_ARG;
+    }
+    fm::g_test_wait_limit_ns.store(uint64_t(wait_limit_ms) * 1000000ull, std::memory_order_relaxed);
+    fm::g_test_skip_tile.store(skip_tile, std::memory_order_relaxed);
     return FM_OK;
 }

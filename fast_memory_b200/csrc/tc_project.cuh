@@ -36,7 +36,14 @@ struct TcParams {
     int cap;
     int *cand_count;       // [total buckets][n_ranges][2]; cap / n_ranges + 1 marks an overflow
     int *status;           // set non-zero when a wait gave up
+    // how long a pipeline wait may take before the CTA gives up (0: the library's two seconds), and - a hook for the
+    // test of that path only - the tile of every CTA whose load the producer leaves out (-1: none)
+    uint64_t wait_limit_ns;
+    int skip_tile;
 };
+
+// The test hooks above as set by fm_test_set_tc_hooks (process-wide, host side).
+void tc_apply_test_hooks(TcParams &p);
 
 // Dense scores are stored in blocks of 32 rows x 32 columns (4 KB); inside a block the element (r, c) sits at
 // (c / 4) * 128 + r * 4 + c % 4, so that the 32 threads of an epilogue warp (one row each) write 512 contiguous

@@ -60,7 +60,7 @@ __device__ __forceinline__ uint64_t global_timer_ns()
 // timer every 256 polls).  Returns false on give-up; the caller records the failure and unwinds: no wait in
 // this library is unbounded.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns = kWaitLimitNs)
 {
     uint64_t t0 = 0;
     for (uint32_t i = 0;; ++i) {
@@ -68,7 +68,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
         if ((i & 255u) == 255u) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) return false;
+            else if (now - t0 > limit_ns) return false;
         }
     }
 }

@@ -266,6 +266,15 @@ int fm_unit_rows(const void *X, int dtype, int64_t n_rows, int d, float *U, fm_s
 int fm_gather_mean(const float *U, int64_t n_rows, int d, const int32_t *rows, int64_t n_out, int64_t per_out, float *out,
                    fm_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Test hooks (no counterpart in the reference).  Every wait of the tensor-core projection kernel on a pipeline
+ * barrier is bounded (two seconds); when one runs out the CTA records a status, waits for its own copies in flight,
+ * frees its TMEM and returns.  fm_test_set_tc_hooks makes that path testable without any fault: wait_limit_ms
+ * shortens the bound (0 = the library's), skip_tile makes the producer of every CTA leave out the load of its tile
+ * number skip_tile (-1 = none), so that the consumers' waits run out.  Process-wide; reset with (0, -1).
+ * ------------------------------------------------------------------------------------------- */
+int fm_test_set_tc_hooks(int wait_limit_ms, int skip_tile);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import fast_memory_b200 as fm
-from fast_memory_b200 import synth
+from fast_memory_b200 import ops, synth
 from oracle import oracle as O
 from tests.util import assert_attn_close, oracle_for_sampled_queries, tables_equal_as_sets
 
@@ -419,3 +419,24 @@ def test_append_equals_full_build():
     m3 = fm.Memory.from_state_dict(mem.state_dict(), kd, vd)
     o3, l3 = m3.query(q.to(DEV), 0.1)
     assert torch.equal(o3, o1) and torch.equal(l3, l1)
+
+
+def test_bounded_pipeline_wait_gives_up_and_the_next_call_is_fine():
+    """Every mbarrier wait of the tcgen05 projection kernel is bounded.  With the test hook the producer leaves out its
+    tile, the consumers' waits run out after 20 ms, the CTA records a status, frees its TMEM and returns normally (no
+    trap, no fault); the next ordinary call on the same context gives the right scores."""
+    from fast_memory_b200 import _lib as L
+    g = torch.Generator().manual_seed(3)
+    A = torch.randn(128, 128, generator=g).bfloat16().to(DEV)
+    K = torch.randn(256, 128, generator=g).bfloat16().to(DEV)              # one bucket tile x one key tile: a single CTA
+    lib = L.lib()
+    assert lib.fm_test_set_tc_hooks(20, 0) == 0
+    try:
+        with pytest.raises(fm.FastMemError, match="pipeline wait gave up"):
+            ops.project_tc(A, K)
+    finally:
+        assert lib.fm_test_set_tc_hooks(0, -1) == 0
+    torch.cuda.synchronize()                                               # the context is intact
+    Y = ops.project_tc(A, K)
+    ref = A.float() @ K.float().T
+    assert (Y - ref).abs().max() <= 1e-3 * ref.abs().max()
