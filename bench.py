@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -670,6 +671,12 @@ def run_ring(args, rank, world):
     with ClockSampler(dev.index or 0) as clocks:             # samples span the warm-up and the timed region (both under load)
         for _ in range(warmup):
             mem.query(q, sm_scale, exchange=args.exchange)
+        # short steps (many GPUs): enough of them for half a second, so that the clock samples fall inside the region
+        est = torch.tensor([time_events(lambda: mem.query(q, sm_scale, exchange=args.exchange), 3, warmup=0)], device=dev)
+        if world > 1:
+            torch.distributed.all_reduce(est, op=torch.distributed.ReduceOp.MAX)
+        if args.workload != "cfg5":                          # (run as the workload itself, exactly --steps are timed)
+            steps = max(steps, min(400, int(math.ceil(500.0 / max(est.item(), 1e-3)))))
         barrier()
         launches0 = fm.launch_count()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -743,9 +750,9 @@ def run_ring(args, rank, world):
         t = torch.tensor([step_ms, e2e_ms, build_med, part_ms, exch_ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         step_ms, e2e_ms, build_med, part_ms, exch_ms = t.tolist()
-        mhz = torch.tensor([float(clk["sm_mhz"] or 0)], device=dev, dtype=torch.float64)
+        mhz = torch.tensor([float(clk["sm_mhz"] or 1e9)], device=dev, dtype=torch.float64)       # a rank without samples does not count
         torch.distributed.all_reduce(mhz, op=torch.distributed.ReduceOp.MIN)
-        clk["sm_mhz_min_over_ranks"] = mhz.item()
+        clk["sm_mhz_min_over_ranks"] = mhz.item() if mhz.item() < 1e9 else None
     if rank != 0:
         return None
     peaks = measured_peaks()

@@ -30,8 +30,10 @@ namespace fm {
 
 // eps = kBandEps * ||a_b|| * kmax.  A tensor-core score is within 2^-16 M of the exact dot product and the
 // canonical chain within 2^-17 M (M = ||a|| ||k|| >= sum |a_i k_i|, d <= 128), so two keys can compare
-// differently under the two orders only if their tensor-core scores differ by less than 3 * 2^-16 M.
-constexpr float kBandEps = 1.0f / 4096.0f;
+// differently under the two orders only if their tensor-core scores differ by less than 3 * 2^-16 M; the band's
+// half-width is 4 * 2^-16 M.  (Measured on 2.7e8 scores of the benchmark data: the two differ by at most 2^-21.9 M.)
+// The band is what the selection re-scores with the canonical chain, about 20 keys per bucket on the benchmark.
+constexpr float kBandEps = 1.0f / 16384.0f;
 constexpr int kMaxBand = 512;               // largest band re-scored exactly; beyond it the bucket goes to the fallback
 constexpr int kMaxFail = 64;                // buckets the fallback can take per group of segments
 constexpr int kMaxSample = 49152;           // sample scores of one bucket the threshold kernel can hold in its registers
@@ -49,39 +51,68 @@ struct FusedSeg {
 };
 
 // ---- 1. max key norm per segment ---------------------------------------------------------------------------
-template <typename T>
-__global__ void key_norm_max_kernel(const T *__restrict__ K, int d, FusedSeg *__restrict__ segs)
+// Sum of squares of the eight elements of a 16-byte piece, never more than 2 % below the exact value.  bf16: packed
+// multiply-adds (four instructions for the eight elements; every step rounds to 8 bits: at most 2^-9 relative each).
+__device__ __forceinline__ float piece_norm2(const uint4 &raw, __nv_bfloat16)
 {
-    FusedSeg &sg = segs[blockIdx.y];
-    const int lanes_per_row = d / 8;                         // 16-byte pieces per row
+    const __nv_bfloat162 *x = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+    __nv_bfloat162 acc = __hmul2(x[0], x[0]);
+    acc = __hfma2(x[1], x[1], acc);
+    acc = __hfma2(x[2], x[2], acc);
+    acc = __hfma2(x[3], x[3], acc);
+    return __low2float(acc) + __high2float(acc);
+}
+__device__ __forceinline__ float piece_norm2(const uint4 &raw, __half)      // (fp16 sums would overflow: fp32)
+{
+    float f[8];
+    widen8(raw, f, __half());
+    float n2 = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) n2 = fmaf(f[e], f[e], n2);
+    return n2;
+}
+
+// One CTA per SM, no shared memory: the kernel runs on a second stream beside the candidate projection, whose CTAs take
+// nearly all of an SM's shared memory (one CTA of this kernel still fits) but leave most of the memory bandwidth idle.
+// What it costs the projection is issue slots (the projection's epilogue warps are its bottleneck), so the kernel is
+// written for few instructions per byte: packed squares, and ONE reduction over the lanes for four rows (a butterfly
+// that halves the number of live values at each of its first two steps).  The result only scales the band of the
+// selection and is inflated by 3 %.
+template <typename T>
+__global__ void __launch_bounds__(512) key_norm_max_kernel(const T *__restrict__ K, int d, FusedSeg *__restrict__ segs, int n_seg)
+{
+    const int lanes_per_row = d / 8;                         // 16-byte pieces per row: 8 or 16
     const int rows_per_warp = 32 / lanes_per_row;
     const int lane = threadIdx.x & 31, sub = lane % lanes_per_row, rsel = lane / lanes_per_row;
     const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int n_warps = gridDim.x * (blockDim.x >> 5);
-    float best = 0.f;
     const int stride = n_warps * rows_per_warp;
-    // four rows per iteration: the loads are issued together, which is what keeps enough bytes in flight
-    for (int r0 = warp_global * rows_per_warp + rsel; r0 < sg.n_keys; r0 += 4 * stride) {
-        uint4 raw[4];
+    for (int s = 0; s < n_seg; ++s) {
+        const int kb = segs[s].kb, n_keys = segs[s].n_keys;
+        float best = 0.f;
+        // four rows per iteration: the loads are issued together, which is what keeps enough bytes in flight
+        for (int r0 = warp_global * rows_per_warp + rsel; r0 < n_keys; r0 += 4 * stride) {
+            uint4 raw[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int r = r0 + u * stride;
-            raw[u] = r < sg.n_keys ? *reinterpret_cast<const uint4 *>(K + size_t(sg.kb + r) * d + sub * 8) : make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < 4; ++u) {
+                const int r = r0 + u * stride;
+                // (streaming loads: the rows are marked to leave L2 first, where the projection keeps the key tiles its CTAs share)
+                raw[u] = r < n_keys ? __ldcs(reinterpret_cast<const uint4 *>(K + size_t(kb + r) * d + sub * 8)) : make_uint4(0, 0, 0, 0);
+            }
+            float n0 = piece_norm2(raw[0], T()), n1 = piece_norm2(raw[1], T()), n2 = piece_norm2(raw[2], T()), n3 = piece_norm2(raw[3], T());
+            // lanes with bit 0 clear go on with rows 0 and 1, the others with rows 2 and 3; then bit 1 splits again
+            const bool odd = sub & 1;
+            const float k0 = odd ? n2 : n0, k1 = odd ? n3 : n1, s0 = odd ? n0 : n2, s1 = odd ? n1 : n3;
+            const float a0 = k0 + __shfl_xor_sync(0xffffffffu, s0, 1), a1 = k1 + __shfl_xor_sync(0xffffffffu, s1, 1);
+            const bool hi = sub & 2;
+            float b = (hi ? a1 : a0) + __shfl_xor_sync(0xffffffffu, hi ? a0 : a1, 2);
+            for (int off = 4; off < lanes_per_row; off <<= 1) b += __shfl_xor_sync(0xffffffffu, b, off);
+            best = fmaxf(best, b);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            float f[8];
-            widen8(raw[u], f, T());
-            float n2 = 0.f;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) n2 = fmaf(f[e], f[e], n2);
-            for (int off = 1; off < lanes_per_row; off <<= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, off);
-            best = fmaxf(best, n2);
-        }
+        for (int off = 16; off >= 1; off >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, off));
+        if (lane == 0 && best > 0.f) atomicMax(&segs[s].kmax_bits, __float_as_uint(sqrtf(best) * 1.03f));
     }
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, off));
-    if (lane == 0 && best > 0.f) atomicMax(&sg.kmax_bits, __float_as_uint(sqrtf(best) * 1.0001f));
 }
 
 __device__ __forceinline__ int seg_of_out_row(const FusedSeg *__restrict__ segs, int n_seg, int row)
@@ -134,6 +165,30 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int *ws, int &total)
     __syncthreads();
     total = ws[32];
     return ws[warp] + incl - v;
+}
+
+// The same with ONE barrier: every warp adds up the warp totals for itself.  `ws` holds 32 ints; two calls in a row
+// without a barrier between them must use different arrays (a slow warp may still be reading the first).
+__device__ __forceinline__ int block_exclusive_scan1(int v, int *ws, int &total)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += o;
+    }
+    if (lane == 31) ws[warp] = incl;
+    __syncthreads();
+    const int w = lane < nw ? ws[lane] : 0;
+    int winc = w;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, winc, off);
+        if (lane >= off) winc += o;
+    }
+    total = __shfl_sync(0xffffffffu, winc, 31);
+    return __shfl_sync(0xffffffffu, winc - w, warp) + incl - v;
 }
 
 // The r-th largest of the n floats in shared memory `vals` (n >= r >= 1, all inside [lo, hi]) by ONE warp, without a
@@ -728,7 +783,7 @@ struct SelParams {
 //   6. every thread counts the selected hits of its stretch of positions, a prefix sum places them, and the table row
 //      comes out in ascending key order.
 template <typename T, int THREADS, int EMAX, bool KEEP>
-__global__ void __launch_bounds__(THREADS, 1024 / THREADS)
+__global__ void __launch_bounds__(THREADS, (KEEP ? 1024 : 1536) / THREADS)
 candidate_select_kernel(SelParams p)
 {
     extern __shared__ __align__(16) unsigned char sel_dyn[];
@@ -742,8 +797,8 @@ candidate_select_kernel(SelParams p)
     __shared__ int band_rank[kMaxBand];
     __shared__ float a_f32[256];
     __shared__ float red_s[64];
-    __shared__ int scan_ws[33];
-    __shared__ int s_fail, s_nband, s_nent;
+    __shared__ int scan_ws[2][32];
+    __shared__ int s_fail, s_nband, s_nent, s_in;
     __shared__ int s_start[2 * kMaxRanges + 1];                         // entries before each sub-list
     __shared__ float s_anorm;
 
@@ -774,6 +829,7 @@ candidate_select_kernel(SelParams p)
         s_nent = fail ? 0 : n;
         s_fail = fail;
         s_nband = 0;
+        s_in = 0;
     }
     for (int i = t; i < p.d; i += nthreads) a_f32[i] = Elem<T>::to_f32(a_row[i]);
     {
@@ -803,13 +859,23 @@ candidate_select_kernel(SelParams p)
     };
     uint4 ent[KEEP ? EMAX : 1];
     int my_hits = 0;
-    float hmin = INFINITY, hmax = -INFINITY;
+    float hmax = -INFINITY;
     if constexpr (KEEP) {                                    // ask for the entries now: they arrive while the masks are summed up
-        int sl = 0;
 #pragma unroll
-        for (int u = 0; u < EMAX; ++u) {
-            ent[u] = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
-            if (e0 + u < e1) ent[u] = *entry_ptr(e0 + u, sl);
+        for (int u = 0; u < EMAX; ++u) ent[u] = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
+        if (e0 < e1) {
+            int sl = 0;
+            const uint4 *first = entry_ptr(e0, sl);
+            if (e1 <= s_start[sl + 1]) {                     // the usual case: one sub-list holds the whole stretch
+                const int step = (sl & 1) ? -1 : 1;
+#pragma unroll
+                for (int u = 0; u < EMAX; ++u)
+                    if (e0 + u < e1) ent[u] = first[u * step];
+            } else {
+#pragma unroll
+                for (int u = 0; u < EMAX; ++u)
+                    if (e0 + u < e1) ent[u] = *entry_ptr(e0 + u, sl);
+            }
         }
     }
     {
@@ -819,20 +885,22 @@ candidate_select_kernel(SelParams p)
         int c = 0;
         for (int tile = t0; tile < t1; ++tile) c += __popcll(m64[tile]);
         int total;
-        int before = block_exclusive_scan(c, scan_ws, total);
+        int before = block_exclusive_scan1(c, scan_ws[0], total);
         for (int tile = t0; tile < t1; ++tile) { tile_pre[tile] = before; before += __popcll(m64[tile]); }
         if (t == 0) {
             tile_pre[n_tiles] = total;
             if (total != n_ent) s_fail = 1;                  // masks and list lengths disagree (an overflowed list)
         }
     }
+    // hits = scores that reach tau.  Their range for the selection is [tau, largest score]: no score below tau is
+    // larger than a hit, so the maximum needs no predicate.
     if constexpr (KEEP) {
 #pragma unroll
         for (int u = 0; u < EMAX; ++u) {
             const float f[4] = {__uint_as_float(ent[u].x), __uint_as_float(ent[u].y), __uint_as_float(ent[u].z), __uint_as_float(ent[u].w)};
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (f[k] >= tau) { ++my_hits; hmin = fminf(hmin, f[k]); hmax = fmaxf(hmax, f[k]); }
+            for (int k = 0; k < 4; ++k) my_hits += f[k] >= tau ? 1 : 0;
+            hmax = fmaxf(fmaxf(hmax, fmaxf(f[0], f[1])), fmaxf(f[2], f[3]));
         }
     } else {
         int sl = 0;
@@ -840,19 +908,19 @@ candidate_select_kernel(SelParams p)
             const uint4 x = *entry_ptr(e, sl);
             const float f[4] = {__uint_as_float(x.x), __uint_as_float(x.y), __uint_as_float(x.z), __uint_as_float(x.w)};
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (f[k] >= tau) { ++my_hits; hmin = fminf(hmin, f[k]); hmax = fmaxf(hmax, f[k]); }
+            for (int k = 0; k < 4; ++k) my_hits += f[k] >= tau ? 1 : 0;
+            hmax = fmaxf(fmaxf(hmax, fmaxf(f[0], f[1])), fmaxf(f[2], f[3]));
         }
     }
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-        hmin = fminf(hmin, __shfl_xor_sync(0xffffffffu, hmin, off));
-        hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, off));
-    }
-    if (lane == 0) { red_s[warp] = hmin; red_s[32 + warp] = hmax; }
+    for (int off = 16; off >= 1; off >>= 1) hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, off));
+    if (lane == 0) red_s[warp] = hmax;
     int n;
-    int pos = block_exclusive_scan(my_hits, scan_ws, n);     // (its barriers also publish red_s and s_fail)
-    for (int w = 0; w < nwarps; ++w) { hmin = fminf(hmin, red_s[w]); hmax = fmaxf(hmax, red_s[32 + w]); }
+    int pos = block_exclusive_scan1(my_hits, scan_ws[1], n);    // (its barrier also publishes red_s and s_fail)
+    hmax = lane < nwarps ? red_s[lane] : -INFINITY;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) hmax = fmaxf(hmax, __shfl_xor_sync(0xffffffffu, hmax, off));
+    const float hmin = tau;
     if (t == 0 && (n < Z || n > p.cap)) s_fail = 1;
     __syncthreads();
 
@@ -909,8 +977,10 @@ candidate_select_kernel(SelParams p)
                 if (slot < kMaxBand) band[slot] = i;
             }
         }
-        int total_in;
-        block_exclusive_scan(my_in, scan_ws, total_in);
+        my_in = __reduce_add_sync(0xffffffffu, my_in);
+        if (lane == 0 && my_in) atomicAdd(&s_in, my_in);
+        __syncthreads();
+        const int total_in = s_in;
         const int n_band = s_nband, need = Z - total_in;
         if (t == 0 && (n_band > kMaxBand || need < 0 || need > n_band)) s_fail = 1;
         __syncthreads();
@@ -921,6 +991,7 @@ candidate_select_kernel(SelParams p)
             // chain runs through the quarters in order, handed from lane to lane
             const int quarter = p.d / 4, sub = lane & 3;
             for (int b0 = 0; b0 < n_band; b0 += nthreads / 4) {
+                if (b0 + warp * 8 >= n_band) break;          // this warp's eight entries lie beyond the band
                 const int b = b0 + (t >> 2);
                 const T *krow = Kseg + size_t(cid[band[min(b, n_band - 1)]]) * p.d + sub * quarter;
                 uint4 raw[4];
@@ -969,7 +1040,7 @@ candidate_select_kernel(SelParams p)
                 my_sel += (y > hi || (y >= lo && cid[i] < 0)) ? 1 : 0;
             }
             int total_sel;
-            int out_pos = block_exclusive_scan(my_sel, scan_ws, total_sel);
+            int out_pos = block_exclusive_scan1(my_sel, scan_ws[0], total_sel);
             int32_t *out = p.table + sg.table_off + size_t(row - sg.out_row0) * Z;
             for (int i = i0; i < i1; ++i) {
                 const float y = cy[i];
@@ -1004,12 +1075,14 @@ __global__ void fallback_scores_kernel(const FusedSeg *__restrict__ segs, int n_
                                        const int *__restrict__ fail_list, const T *__restrict__ A, const T *__restrict__ K, int d,
                                        float *__restrict__ Yf, int64_t ldf)
 {
-    if ((int)blockIdx.y >= min(*fail_count, kMaxFail)) return;
-    const int row = fail_list[blockIdx.y];
-    const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
-    const T *a_row = A + size_t(sg.cb + (row - sg.out_row0)) * d;
-    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < sg.n_keys; j += gridDim.x * blockDim.x)
-        Yf[size_t(blockIdx.y) * ldf + j] = canonical_dot(a_row, K + size_t(sg.kb + j) * d, d);
+    const int n_fail = min(*fail_count, kMaxFail);
+    for (int f = blockIdx.y; f < n_fail; f += gridDim.y) {   // (no failures as a rule: the grid is kept small)
+        const int row = fail_list[f];
+        const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
+        const T *a_row = A + size_t(sg.cb + (row - sg.out_row0)) * d;
+        for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < sg.n_keys; j += gridDim.x * blockDim.x)
+            Yf[size_t(f) * ldf + j] = canonical_dot(a_row, K + size_t(sg.kb + j) * d, d);
+    }
 }
 
 __global__ void __launch_bounds__(kSelThreads)
@@ -1081,11 +1154,11 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
     P.group_buckets = std::max<int64_t>(max_b, std::min<int64_t>(total_pad, int64_t((size_t(3) << 30) / per_bucket)));
     size_t off = 0;
     P.off_status = off; off += 256;
+    P.off_fail = off;   off += align_up(size_t(kMaxFail + 1) * 4, 256);
     P.off_segs = off;   off += align_up(size_t(n) * sizeof(FusedSeg), 256);
     P.off_tcseg = off;  off += align_up(size_t(n) * sizeof(TcSeg) * 2, 256);
     P.off_tau = off;    off += align_up(size_t(P.group_buckets) * 4, 256);
     P.off_count = off;  off += align_up(size_t(P.group_buckets) * kMaxRanges * 2 * 4, 256);
-    P.off_fail = off;   off += align_up(size_t(kMaxFail + 1) * 4, 256);
     P.off_ys = off;     off += align_up(size_t(P.group_buckets) * P.ld_sample * 4, 256);
     P.off_cand = off;   off += align_up(size_t(P.group_buckets) * P.cap * 16, 256);
     P.off_mask = off;   off += align_up(size_t(ceil_div(P.max_keys, kTcBN)) * P.group_buckets * 8, 256);
@@ -1120,7 +1193,11 @@ static BuildSide *build_side()
     BuildSide &b = g_side[dev];
     if (!b.tried) {
         b.tried = true;
-        bool ok = cudaStreamCreateWithFlags(&b.stream, cudaStreamNonBlocking) == cudaSuccess &&
+        // the side stream has the highest priority: its one small CTA per SM is placed as soon as it may run, not
+        // after the last CTA of a long grid on the caller's stream has been placed
+        int prio_least = 0, prio_greatest = 0;
+        if (cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest) != cudaSuccess) { prio_greatest = 0; cudaGetLastError(); }
+        bool ok = cudaStreamCreateWithPriority(&b.stream, cudaStreamNonBlocking, prio_greatest) == cudaSuccess &&
                   cudaEventCreateWithFlags(&b.fork, cudaEventDisableTiming) == cudaSuccess &&
                   cudaEventCreateWithFlags(&b.join, cudaEventDisableTiming) == cudaSuccess;
         if (!ok) { b.stream = nullptr; cudaGetLastError(); }
@@ -1170,10 +1247,12 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
     if (rc != FM_OK) return rc;
     rc = make_tensor_map_2d(&tmKs, K, dtype, (uint64_t)ceil_div(total_key_rows, P.step), (uint64_t)d, (uint64_t)d * 2 * P.step, kTcBN);
     if (rc != FM_OK) return rc;
-    FM_CUDA_OK(cudaMemsetAsync(ws + P.off_status, 0, 256, st));
-
-    std::vector<FusedSeg> hs(n);
-    std::vector<TcSeg> ht(2 * n);
+    // (the status word at ws + 0 has been cleared by the caller)
+    // host mirror of the descriptor area [FusedSeg x n | pad | TcSeg x 2n]: one copy when a group covers every segment
+    const size_t desc_bytes = (P.off_tcseg - P.off_segs) + size_t(2 * n) * sizeof(TcSeg);
+    std::vector<char> hdesc(desc_bytes, 0);
+    FusedSeg *hs = reinterpret_cast<FusedSeg *>(hdesc.data());
+    TcSeg *ht = reinterpret_cast<TcSeg *>(hdesc.data() + (P.off_tcseg - P.off_segs));
     int g0 = 0;
     while (g0 < n) {
         // one group: consecutive segments whose buckets fit the group arrays
@@ -1196,11 +1275,15 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         FusedSeg *dsegs = (FusedSeg *)(ws + P.off_segs) + g0;
         TcSeg *dtc_s = (TcSeg *)(ws + P.off_tcseg) + g0, *dtc_m = (TcSeg *)(ws + P.off_tcseg) + n + g0;
         BuildSide *bs = build_side();
-        rc = stage_to_device(bs, dsegs, hs.data() + g0, sizeof(FusedSeg) * ng, st);
-        if (rc == FM_OK) rc = stage_to_device(bs, dtc_s, ht.data() + g0, sizeof(TcSeg) * ng, st);
-        if (rc == FM_OK) rc = stage_to_device(bs, dtc_m, ht.data() + n + g0, sizeof(TcSeg) * ng, st);
+        if (ng == n) {
+            rc = stage_to_device(bs, ws + P.off_segs, hdesc.data(), desc_bytes, st);
+        } else {
+            rc = stage_to_device(bs, dsegs, hs + g0, sizeof(FusedSeg) * ng, st);
+            if (rc == FM_OK) rc = stage_to_device(bs, dtc_s, ht + g0, sizeof(TcSeg) * ng, st);
+            if (rc == FM_OK) rc = stage_to_device(bs, dtc_m, ht + n + g0, sizeof(TcSeg) * ng, st);
+        }
         if (rc != FM_OK) return rc;
-        FM_CUDA_OK(cudaMemsetAsync(ws + P.off_fail, 0, 256, st));
+        FM_CUDA_OK(cudaMemsetAsync(ws + P.off_fail, 0, 512, st));
         float *tau = (float *)(ws + P.off_tau);
         int *counts = (int *)(ws + P.off_count);
         int *fail_count = (int *)(ws + P.off_fail), *fail_list = fail_count + 1;
@@ -1209,17 +1292,8 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         uint2 *cand_mask = (uint2 *)(ws + P.off_mask);
         float *Yf = (float *)(ws + P.off_yf);
 
-        // The key norms are only needed by the selection: they are taken on a second stream, under the sample pass and
-        // the threshold selection (which leave most of the memory bandwidth idle), and joined before the selection.
         cudaStream_t side = bs ? bs->stream : nullptr;
         cudaEvent_t ev_fork = bs ? bs->fork : nullptr, ev_join = bs ? bs->join : nullptr;
-        if (side) {
-            FM_CUDA_OK(cudaEventRecord(ev_fork, st));
-            FM_CUDA_OK(cudaStreamWaitEvent(side, ev_fork, 0));
-        }
-        key_norm_max_kernel<T><<<dim3(std::max(1, 8 * sm_count() / ng), ng), 256, 0, side ? side : st>>>((const T *)K, d, dsegs);
-        FM_LAUNCHED("key_norm_max_kernel");
-        if (side) FM_CUDA_OK(cudaEventRecord(ev_join, side));
 
         const int sms = sm_count();
         TcParams tp = {};
@@ -1265,26 +1339,41 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
             for (int i = g0; i < g1; ++i) min_tiles = std::min(min_tiles, ceil_div(nk[i], kTcBN));
             tp.n_ranges = single_range ? 1 : choose_ranges(mtiles, min_tiles, sms);
         }
+        // The key norms are only needed by the selection.  They are taken on a second stream beside the candidate
+        // projection - tensor-bound, it leaves most of the memory bandwidth idle - and joined before the selection:
+        // the fork is recorded before the projection is launched, so both start when the thresholds are done.
+        if (side) {
+            FM_CUDA_OK(cudaEventRecord(ev_fork, st));
+            FM_CUDA_OK(cudaStreamWaitEvent(side, ev_fork, 0));
+        }
         rc = tc_project_launch(tmA, tmK, tp, int(mtiles) * tp.n_ranges, d, false, dtype == FM_BF16, st);
         if (rc != FM_OK) return rc;
-
-        if (side) FM_CUDA_OK(cudaStreamWaitEvent(st, ev_join, 0));
+        // (the projection's CTAs configure their SMs for the largest shared memory: ask for the same, or this kernel's
+        // CTAs would wait for SMs to drain)
+        FM_CUDA_OK(cudaFuncSetAttribute(key_norm_max_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        key_norm_max_kernel<T><<<sms, 512, 0, side ? side : st>>>((const T *)K, d, dsegs, ng);
+        FM_LAUNCHED("key_norm_max_kernel");
+        if (side) {
+            FM_CUDA_OK(cudaEventRecord(ev_join, side));
+            FM_CUDA_OK(cudaStreamWaitEvent(st, ev_join, 0));
+        }
         const int max_tiles = (int)ceil_div(P.max_keys, kTcBN);
         SelParams sp = {dsegs, ng, tp.n_ranges, P.cap, cand, cand_mask, P.group_buckets, counts, tau, A, K, d, table, fail_count, fail_list,
                         max_tiles};
         {
             // candidate scores + key indices, tile masks, entries before each tile
             const size_t dyn = P.sel_smem;
-            // entries in registers where a CTA's threads can hold them.  Measured on the 32-head benchmark build: 512
-            // threads x 9 entries 1.21 ms, 256 x 18 1.42 ms, 128 x 40 read twice 2.11 ms - the CTA's steps are chains of
-            // memory round trips and barriers, and fewer warps hide less of them
-            if (P.cap <= 9 * 512) rc = launch_select<T, 512, 9, true>(sp, (unsigned)rows, dyn, st);
+            // The CTA's steps are chains of memory round trips and barriers, so what counts is how many CTAs an SM holds.
+            // Measured on the 32-head benchmark build: 512 threads reading their 9 entries twice (40 registers, 3 CTAs
+            // per SM) 1.03 ms; the entries kept in registers (64 registers, 2 CTAs) 1.10 ms; 256 threads x 18 entries
+            // 1.42 ms; 128 x 40 2.11 ms.
+            if (P.cap <= 9 * 512) rc = launch_select<T, 512, 9, false>(sp, (unsigned)rows, dyn, st);
             else if (P.cap <= 8 * 1024) rc = launch_select<T, 1024, 8, true>(sp, (unsigned)rows, dyn, st);
             else rc = launch_select<T, 1024, 25, false>(sp, (unsigned)rows, dyn, st);
             if (rc != FM_OK) return rc;
         }
 
-        fallback_scores_kernel<T><<<dim3((unsigned)std::min<int64_t>(ceil_div(P.max_keys, 256), 4 * sms), kMaxFail), 256, 0, st>>>(
+        fallback_scores_kernel<T><<<dim3((unsigned)std::min<int64_t>(ceil_div(P.max_keys, 256), 4 * sms), 4), 256, 0, st>>>(
             dsegs, ng, fail_count, fail_list, (const T *)A, (const T *)K, d, Yf, P.max_keys);
         FM_LAUNCHED("fallback_scores_kernel");
         fallback_select_kernel<<<kMaxFail, kSelThreads, 0, st>>>(dsegs, ng, fail_count, fail_list, Yf, P.max_keys, table,
