@@ -2,7 +2,9 @@
 #include "common.cuh"
 
 #include <cstring>
+#include <map>
 #include <mutex>
+#include <tuple>
 
 namespace fm {
 
@@ -30,6 +32,24 @@ int sm_count()
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+// cudaFuncSetAttribute costs several microseconds of host time per call and the launch paths would repeat it with the
+// same value before every launch: the last value set per (kernel, device, attribute) is remembered instead.
+cudaError_t func_attr_cached(const void *func, cudaFuncAttribute attr, int value)
+{
+    static std::mutex mu;
+    static std::map<std::tuple<const void *, int, int>, int> last;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_tuple(func, dev, (int)attr);
+    auto it = last.find(key);
+    if (it != last.end() && it->second == value) return cudaSuccess;
+    e = cudaFuncSetAttribute(func, attr, value);
+    if (e == cudaSuccess) last[key] = value;
+    return e;
 }
 
 }  // namespace fm

@@ -50,6 +50,7 @@ inline int cuda_fail(cudaError_t e, const char *what)
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 int sm_count();                                // SMs of the current device (cached per device)
+cudaError_t func_attr_cached(const void *func, cudaFuncAttribute attr, int value);   // cudaFuncSetAttribute, skipped when unchanged
 
 // ---- element types -------------------------------------------------------------------------------
 template <typename T> struct Elem;

@@ -550,7 +550,7 @@ static int launch_hash_mma(const void *x, const void *A, int64_t n_rows, int64_t
         rc = make_tensor_map_2d(&tmA, A, Elem<T>::id, (uint64_t)total_buckets, D, (uint64_t)D * 2, kThBN);
         if (rc != FM_OK) return rc;
         const size_t smem = size_t(D / 64) * (kThBM * 128 + kThStages * kThBN * 128) + 1024;
-        FM_CUDA_OK(cudaFuncSetAttribute(hash_rows_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FM_CUDA_OK(func_attr_cached((const void *)hash_rows_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dim3 grid((unsigned)ceil_div(max_seg_rows, kThBM), (unsigned)n_seg);
         hash_rows_tc_kernel<T, D><<<grid, kThThreads, smem, st>>>(tmX, tmA, (const T *)x, (const T *)A, (int)n_rows, (int)total_buckets,
                                                                 seg_xb, seg_cb, amax, hash_out, list, count,
@@ -558,7 +558,7 @@ static int launch_hash_mma(const void *x, const void *A, int64_t n_rows, int64_t
         FM_LAUNCHED("hash_rows_tc_kernel");
     } else {
         const size_t smem = 2 * size_t(kTile) * D * 2;
-        FM_CUDA_OK(cudaFuncSetAttribute(hash_rows_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FM_CUDA_OK(func_attr_cached((const void *)hash_rows_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dim3 grid((unsigned)ceil_div(max_seg_rows, kTile), (unsigned)n_seg);
         hash_rows_mma_kernel<T, D><<<grid, kHashThreads, smem, st>>>((const T *)x, (const T *)A, (int)n_rows, (int)total_buckets,
                                                                    seg_xb, seg_cb, amax, hash_out, list, count);
@@ -577,7 +577,7 @@ static int launch_hash(const void *x, const void *A, int64_t n_rows, int64_t tot
                        cudaStream_t st)
 {
     size_t smem = tile_smem_bytes(d);
-    FM_CUDA_OK(cudaFuncSetAttribute(hash_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FM_CUDA_OK(func_attr_cached((const void *)hash_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)ceil_div(max_seg_rows, kTile), (unsigned)n_seg);
     hash_rows_kernel<T><<<grid, kTileThreads, smem, st>>>((const T *)x, (const T *)A, d, (int)n_rows,
                                                          (int)total_buckets, seg_xb, seg_cb, hash_out);

@@ -305,7 +305,7 @@ template <typename T, int D>
 static int launch_simt(const AttnParams &p, int grid, cudaStream_t st)
 {
     size_t smem = SimtCfg<T, D>::smem;
-    FM_CUDA_OK(cudaFuncSetAttribute(attn_simt_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FM_CUDA_OK(func_attr_cached((const void *)attn_simt_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attn_simt_kernel<T, D><<<grid, kSimtThreads, smem, st>>>(p);
     FM_LAUNCHED("attn_simt_kernel");
     return FM_OK;

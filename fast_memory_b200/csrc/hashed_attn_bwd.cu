@@ -197,10 +197,10 @@ template <typename T> static int launch_bwd(const BwdParams &p, int d, int64_t t
 {
     const size_t smem = sizeof(float) * (2 * size_t(kBwdQ) * d + 2 * size_t(kBwdK) * (d + 1) + 2 * kBwdQ * kPLd + 2 * kBwdQ);
     if (d <= 128) {
-        FM_CUDA_OK(cudaFuncSetAttribute(attn_bwd_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FM_CUDA_OK(func_attr_cached((const void *)attn_bwd_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_bwd_kernel<T, 1><<<(unsigned)total_buckets, kBwdThreads, smem, st>>>(p, d);
     } else {
-        FM_CUDA_OK(cudaFuncSetAttribute(attn_bwd_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FM_CUDA_OK(func_attr_cached((const void *)attn_bwd_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_bwd_kernel<T, 2><<<(unsigned)total_buckets, kBwdThreads, smem, st>>>(p, d);
     }
     FM_LAUNCHED("attn_bwd_kernel");

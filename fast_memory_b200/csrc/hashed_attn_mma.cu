@@ -356,7 +356,7 @@ template <typename T, int D>
 int launch_mma(const AttnParams &p, int grid, cudaStream_t st)
 {
     const size_t smem = MmaCfg<D>::smem;
-    FM_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FM_CUDA_OK(func_attr_cached((const void *)attn_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attn_mma_kernel<T, D><<<grid, kThreads, smem, st>>>(p);
     FM_LAUNCHED("attn_mma_kernel");
     return FM_OK;

@@ -619,10 +619,10 @@ int launch_attn_tc(const AttnParams &p, int dtype, int grid, int4 *redo_items, i
     const uint32_t idesc_s = tc::instr_desc_f16(bf16, kTileKeys, kNQ);                    // K-major A and B
     const uint32_t idesc_o = tc::instr_desc_f16(bf16, kD, kNQ, true, true);               // MN-major A and B
     if (bf16) {
-        FM_CUDA_OK(cudaFuncSetAttribute(attn_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FM_CUDA_OK(func_attr_cached((const void *)attn_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_tc_kernel<__nv_bfloat16><<<grid, kTcAttnThreads, smem, st>>>(p, idesc_s, idesc_o, redo_items, redo_count);
     } else {
-        FM_CUDA_OK(cudaFuncSetAttribute(attn_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FM_CUDA_OK(func_attr_cached((const void *)attn_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attn_tc_kernel<__half><<<grid, kTcAttnThreads, smem, st>>>(p, idesc_s, idesc_o, redo_items, redo_count);
     }
     FM_LAUNCHED("attn_tc_kernel");

@@ -55,7 +55,7 @@ static int launch_project(const void *A, const void *K, int64_t C, int64_t N, in
                           cudaStream_t st)
 {
     size_t smem = tile_smem_bytes(d);
-    FM_CUDA_OK(cudaFuncSetAttribute(project_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FM_CUDA_OK(func_attr_cached((const void *)project_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     project_kernel<T><<<(unsigned)ceil_div(N, kTile), kTileThreads, smem, st>>>((const T *)A, (const T *)K, (int)C, N, d, Y, ldy);
     FM_LAUNCHED("project_kernel");
     return FM_OK;

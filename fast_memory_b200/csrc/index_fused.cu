@@ -36,7 +36,7 @@ namespace fm {
 constexpr float kBandEps = 1.0f / 16384.0f;
 constexpr int kMaxBand = 512;               // largest band re-scored exactly; beyond it the bucket goes to the fallback
 constexpr int kMaxFail = 64;                // buckets the fallback can take per group of segments
-constexpr int kMaxSample = 49152;           // sample scores of one bucket the threshold kernel can hold in its registers
+constexpr int kMaxSample = 49152;           // sample scores of one bucket (the key step is raised to stay below it)
 constexpr int kMaxRanges = 8;               // key ranges a bucket tile's keys may be split into (one CTA each)
 
 struct FusedSeg {
@@ -125,7 +125,7 @@ __device__ __forceinline__ int seg_of_out_row(const FusedSeg *__restrict__ segs,
     return lo;
 }
 
-// ---- 3. thresholds from the sample scores -----------------------------------------------------------------------
+// ---- 3. (the thresholds come from tc_tau.cu) helpers of the selection --------------------------------------------------
 // Values held in shared memory.
 struct SmemValues {
     const float *v;
@@ -386,369 +386,6 @@ __device__ __forceinline__ float select_rth_fine(const Source &src, int r, float
     }
     ok = false;                                              // masses of nearly equal values
     return lo;
-}
-
-// ---- 3a. thresholds, eight rows per CTA ----------------------------------------------------------------------------
-// The blocked layout of the sample scores puts the same four columns of eight consecutive rows into one 128-byte line,
-// so a CTA takes eight rows and reads whole lines: lane = (row, one of four column pieces), 8 warps side by side.
-//   pass 1: every lane keeps eight maxima over interleaved classes of its pieces - 256 maxima per row; the r-th
-//           largest of a row's maxima is a lower bound of its tau (r different scores reach it), found as the lower
-//           edge of a bin of a 256-bin histogram of the maxima (warp w serves row w);
-//   pass 2: the lines are read again (from L2) and the scores at or above the bound - a few hundred per row - go to
-//           the row's list in shared memory;
-//   rank:   warp w ranks the list of row w (warp_select_small) and writes tau.
-// Rows for which this does not work out (rank beyond the maxima, a list that overflows: masses of equal scores) get
-// tau = NaN and are served by the one-row-per-CTA kernel below, which exits at once for every other row.
-constexpr int kTau8Rows = 8;
-constexpr int kTau8Threads = 256;
-constexpr int kTau8List = 1024;             // scores at or above the bound a row's list holds
-
-struct Tau8Warp {
-    int hist[256];
-    float small[kWarpSmall];
-    int ctl[2];
-};
-
-__global__ void __launch_bounds__(kTau8Threads)
-sample_tau8_kernel(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg, float *__restrict__ tau)
-{
-    extern __shared__ __align__(16) unsigned char tau8_dyn[];
-    float *top = reinterpret_cast<float *>(tau8_dyn);                      // [8 rows][kTau8List]
-    Tau8Warp *ws = reinterpret_cast<Tau8Warp *>(top + kTau8Rows * kTau8List);   // one per warp
-    __shared__ float red_hi[kTau8Rows][8], red_lo[kTau8Rows][8];
-    __shared__ float s_hi[kTau8Rows], s_lo[kTau8Rows], s_bound[kTau8Rows];
-    __shared__ int s_cnt[kTau8Rows];
-
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const int rr = lane & 7, cc = lane >> 3;                 // row of the eight, column piece of the four
-    const int row0 = blockIdx.x * kTau8Rows;
-    const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row0)];
-    const bool row_ok = row0 + rr - sg.out_row0 < sg.n_buckets;           // rows past the segment's buckets are padding
-    if (row0 - sg.out_row0 >= sg.n_buckets) return;
-    const int n = sg.ns, n4 = (n + 3) >> 2, r = min(sg.rank, n);
-    // piece g of row R sits at block base + (g >> 3) * 1024 + (g & 7) * 128 + (R & 31) * 4 floats
-    const float *base = Ys + dense_block_offset(row0, 0, ldy) + size_t((row0 + rr) & 31) * 4;
-    auto piece = [&](int g) { return *reinterpret_cast<const float4 *>(base + size_t(g >> 3) * 1024 + size_t(g & 7) * 128); };
-    const int n_steps = (n4 + 31) >> 5;                      // 32 pieces of a row per step of the CTA: piece g = step * 32 + warp * 4 + cc
-    float mx[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) mx[k] = -INFINITY;
-    for (int s0 = 0; s0 < n_steps; s0 += 8) {
-        float4 v[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const int g = (s0 + k) * 32 + warp * 4 + cc;
-            v[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-            if (g < n4) v[k] = piece(g);
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const int g = (s0 + k) * 32 + warp * 4 + cc;
-            if (g < n4) {
-                if (4 * g + 1 >= n) v[k].y = -INFINITY;      // columns past the row's end
-                if (4 * g + 2 >= n) v[k].z = -INFINITY;
-                if (4 * g + 3 >= n) v[k].w = -INFINITY;
-                mx[k] = fmaxf(mx[k], fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
-            }
-        }
-    }
-    // range of the row's maxima: over the lane's eight, the four lanes of the row in this warp, then the warps
-    float hi = -INFINITY, lo = INFINITY;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        hi = fmaxf(hi, mx[k]);
-        if (mx[k] > -INFINITY) lo = fminf(lo, mx[k]);
-    }
-#pragma unroll
-    for (int off = 8; off <= 16; off <<= 1) {
-        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
-        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-    }
-    if (cc == 0) { red_hi[rr][warp] = hi; red_lo[rr][warp] = lo; }
-    for (int i = lane; i < 256; i += 32) ws[warp].hist[i] = 0;            // warp w's histogram serves row w
-    if (t < kTau8Rows) s_cnt[t] = 0;
-    __syncthreads();
-    if (t < kTau8Rows) {
-        float h = -INFINITY, l = INFINITY;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) { h = fmaxf(h, red_hi[t][w]); l = fminf(l, red_lo[t][w]); }
-        s_hi[t] = h;
-        s_lo[t] = l;
-    }
-    __syncthreads();
-    hi = s_hi[rr];
-    lo = s_lo[rr];
-    const float bscale = hi > lo ? 256.f / (hi - lo) : 0.f;
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-        if (mx[k] > -INFINITY && row_ok) atomicAdd(&ws[rr].hist[min(255, int((mx[k] - lo) * bscale))], 1);
-    __syncthreads();
-    {
-        // warp w: the bin of the r-th largest maximum of row w; the bound is a little below the bin's lower edge, so that
-        // every score of that bin and the bins above passes a plain comparison
-        const float h = s_hi[warp], l = s_lo[warp];
-        int mine = 0;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) mine += ws[warp].hist[255 - (lane * 8 + k)];
-        int incl = mine;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const int o = __shfl_up_sync(0xffffffffu, incl, off);
-            if (lane >= off) incl += o;
-        }
-        const int total = __shfl_sync(0xffffffffu, incl, 31);
-        int acc = incl - mine;
-        float bnd = NAN;
-        if (acc < r && r <= incl) {
-            for (int k = 0; k < 8; ++k) {
-                const int b = 255 - (lane * 8 + k);
-                acc += ws[warp].hist[b];
-                if (r <= acc) { bnd = l + (float(b) - 0.25f) * ((h - l) * (1.f / 256.f)); break; }
-            }
-        }
-        const unsigned owner = __ballot_sync(0xffffffffu, bnd == bnd);
-        if (owner) bnd = __shfl_sync(0xffffffffu, bnd, __ffs(owner) - 1);
-        if (total < r || !(h > l)) bnd = NAN;                // no bound: the row goes to the other kernel
-        if (lane == 0) s_bound[warp] = bnd;
-    }
-    __syncthreads();
-    const float bound = s_bound[rr];
-    if (bound == bound && row_ok) {                          // pass 2 (rows without a bound take no part)
-        float *list = top + rr * kTau8List;
-        for (int s0 = 0; s0 < n_steps; s0 += 8) {
-            float4 v[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int g = (s0 + k) * 32 + warp * 4 + cc;
-                v[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-                if (g < n4) v[k] = piece(g);
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int g = (s0 + k) * 32 + warp * 4 + cc;
-                const float f[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (f[e] >= bound && 4 * g + e < n) {
-                        const int pos = atomicAdd(&s_cnt[rr], 1);
-                        if (pos < kTau8List) list[pos] = f[e];
-                    }
-            }
-        }
-    }
-    __syncthreads();
-    {
-        // warp w ranks row w
-        const int row = row0 + warp;
-        if (row - sg.out_row0 < sg.n_buckets) {
-            const float b = s_bound[warp];
-            const int cnt = s_cnt[warp];
-            float th = NAN;
-            if (b == b && cnt >= r && cnt <= kTau8List) {
-                bool exact;
-                th = warp_select_small(top + warp * kTau8List, cnt, r, b, s_hi[warp], ws[warp].hist, ws[warp].small, ws[warp].ctl, exact);
-                // (not exact: the smallest member of a crowded bin, at most the order statistic - a few more candidates pass)
-            }
-            if (lane == 0) tau[row] = th;
-        }
-    }
-}
-
-// One CTA per bucket: tau = the r-th largest score of the bucket's row of the blocked sample scores (four consecutive
-// columns are 16 contiguous bytes).  The whole row is loaded into registers at once (kTauGroups 16-byte pieces per
-// thread, all in flight together), so the row is read exactly once and nothing below waits on memory again.  r is small
-// against the row, so most of it is discarded cheaply: every thread keeps the maxima of two halves of what it holds; the
-// r-th largest of these maxima is a lower bound of tau (r different scores reach it), found with one small histogram
-// (its bin's lower edge: still a lower bound).  Only the scores at or above the bound - a few hundred - are put into
-// shared memory and ranked.
-// The scores a thread holds in registers (-inf marks "no score").
-template <int G> struct RowRegs {
-    const float4 (&v)[G];
-    template <class F> __device__ __forceinline__ void for_each(F f) const
-    {
-#pragma unroll
-        for (int u = 0; u < G; ++u) {
-            if (v[u].x > -INFINITY) f(0, v[u].x);
-            if (v[u].y > -INFINITY) f(0, v[u].y);
-            if (v[u].z > -INFINITY) f(0, v[u].z);
-            if (v[u].w > -INFINITY) f(0, v[u].w);
-        }
-    }
-};
-constexpr int kTopCap = 2048;               // sample scores that may lie at or above the lower bound
-constexpr int kBoundBins = 256;
-
-// THREADS x G 16-byte pieces cover the row: 256 x 8 (rows of up to 8192 scores), 256 x 16, 512 x 16, 1024 x 12 (49152).
-struct TauRowScratch {
-    FineScratch S;
-    float top_s[kTopCap];
-    float red_s[64];
-    int bound_hist[kBoundBins];
-    int s_top, s_bbin;
-};
-
-template <int THREADS, int G>
-__device__ __forceinline__ void tau_of_row(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg,
-                                           float *__restrict__ tau, int row, TauRowScratch &W)
-{
-    constexpr int kTauGroups = G;
-    FineScratch &S = W.S;
-    float *top_s = W.top_s, *red_s = W.red_s;
-    int *bound_hist = W.bound_hist;
-    int &s_top = W.s_top, &s_bbin = W.s_bbin;
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nthreads = blockDim.x, nw = nthreads >> 5;
-    const FusedSeg sg = segs[seg_of_out_row(segs, n_seg, row)];
-    if (row - sg.out_row0 >= sg.n_buckets) return;           // padding between segments
-    const float *blk = Ys + dense_block_offset(row, 0, ldy) + size_t(row & 31) * 4;
-    const int n = sg.ns, n4 = (n + 3) >> 2, r = min(sg.rank, n);
-
-    float4 v[kTauGroups];
-#pragma unroll
-    for (int u = 0; u < kTauGroups; ++u) {
-        const int g = t + u * nthreads;
-        v[u] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-        if (g < n4) v[u] = *reinterpret_cast<const float4 *>(blk + size_t(g >> 3) * 1024 + size_t(g & 7) * 128);
-    }
-    float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-    for (int u = 0; u < kTauGroups; ++u) {
-        const int g = t + u * nthreads;
-        if (g < n4) {
-            if (4 * g + 1 >= n) v[u].y = -INFINITY;          // columns past the row's end
-            if (4 * g + 2 >= n) v[u].z = -INFINITY;
-            if (4 * g + 3 >= n) v[u].w = -INFINITY;
-            const float m4 = fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w));
-            if (u & 1) mx1 = fmaxf(mx1, m4); else mx0 = fmaxf(mx0, m4);
-        }
-    }
-    // range of the thread maxima
-    float hi = fmaxf(mx0, mx1), lo = fminf(mx0 > -INFINITY ? mx0 : INFINITY, mx1 > -INFINITY ? mx1 : INFINITY);
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
-        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-    }
-    if (lane == 0) { red_s[warp] = hi; red_s[32 + warp] = lo; }
-    for (int i = t; i < kBoundBins; i += nthreads) bound_hist[i] = 0;
-    if (t == 0) { s_top = 0; s_bbin = -1; }
-    __syncthreads();
-    hi = -INFINITY; lo = INFINITY;
-    for (int w = 0; w < nw; ++w) { hi = fmaxf(hi, red_s[w]); lo = fminf(lo, red_s[32 + w]); }
-    // a score passes the pre-filter when it falls into the bin of the r-th largest thread maximum or above: at least r
-    // scores do (the maxima themselves), and passing is monotone in the score, so the r-th largest of the row is among them
-    const float bscale = hi > lo ? float(kBoundBins) / (hi - lo) : 0.f;
-    auto bound_bin = [&](float f) { return min(kBoundBins - 1, int((f - lo) * bscale)); };
-    const int n_max = min(nthreads, n4) + max(0, min(nthreads, n4 - nthreads));      // thread maxima that exist
-    if (r <= n_max && hi > lo) {
-        if (mx0 > -INFINITY) atomicAdd(&bound_hist[bound_bin(mx0)], 1);
-        if (mx1 > -INFINITY) atomicAdd(&bound_hist[bound_bin(mx1)], 1);
-        __syncthreads();
-        if (warp == 0) {                                     // suffix sums over the 256 bins, 8 per lane, top bins in lane 0
-            int mine = 0;
-#pragma unroll
-            for (int k = 0; k < kBoundBins / 32; ++k) mine += bound_hist[kBoundBins - 1 - (lane * (kBoundBins / 32) + k)];
-            int incl = mine;
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int o = __shfl_up_sync(0xffffffffu, incl, off);
-                if (lane >= off) incl += o;
-            }
-            int acc = incl - mine;
-            if (acc < r && r <= incl) {
-                for (int k = 0; k < kBoundBins / 32; ++k) {
-                    const int b = kBoundBins - 1 - (lane * (kBoundBins / 32) + k);
-                    acc += bound_hist[b];
-                    if (r <= acc) { s_bbin = b; break; }
-                }
-            }
-        }
-        __syncthreads();
-    }
-    const int bbin = s_bbin;                                 // -1: no pre-filter
-    float th = 0.f;
-    bool ok = true, listed = false;
-    if (bbin > 0) {
-        float top_min = INFINITY;
-#pragma unroll
-        for (int u = 0; u < kTauGroups; ++u) {
-            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (f[k] > -INFINITY && bound_bin(f[k]) >= bbin) {
-                    const int pos = atomicAdd(&s_top, 1);
-                    if (pos < kTopCap) top_s[pos] = f[k];
-                    top_min = fminf(top_min, f[k]);
-                }
-        }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) top_min = fminf(top_min, __shfl_xor_sync(0xffffffffu, top_min, off));
-        if (lane == 0) red_s[warp] = top_min;
-        __syncthreads();
-        listed = s_top >= r && s_top <= kTopCap;             // uniform; more than the list holds: the plain way
-        if (listed) {
-            top_min = INFINITY;
-            for (int w = 0; w < nw; ++w) top_min = fminf(top_min, red_s[w]);
-            if (s_top <= 1024) {
-                // a few hundred scores: one warp ranks them while the others are done (no barrier follows)
-                if (warp == 0) {
-                    th = warp_select_small(top_s, s_top, r, top_min, hi, S.hist, S.wsmall, S.ctl, ok);
-                    if (lane == 0) tau[row] = th;
-                }
-                return;
-            }
-            th = select_rth_fine(SmemValues{top_s, s_top}, r, top_min, hi, S, ok);
-        }
-    }
-    if (!listed) {
-        // no pre-filter (r beyond the number of thread maxima, equal scores in masses): rank the row from the registers
-        float mn = INFINITY;
-#pragma unroll
-        for (int u = 0; u < kTauGroups; ++u) {
-            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (f[k] > -INFINITY) mn = fminf(mn, f[k]);
-        }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
-        __syncthreads();
-        if (lane == 0) red_s[warp] = mn;
-        __syncthreads();
-        mn = INFINITY;
-        for (int w = 0; w < nw; ++w) mn = fminf(mn, red_s[w]);
-        th = select_rth_fine(RowRegs<G>{v}, r, mn, hi, S, ok);
-    }
-    // (when the crowd around the order statistic never thins out `th` is a lower edge below it: a few more candidates pass)
-    if (t == 0) tau[row] = th;
-}
-
-// only_unset = false: one row per CTA (grid = rows).  only_unset = true: a CTA looks through a stretch of kTauStretch rows
-// and serves just the ones whose tau is still NaN (the eight-row kernel leaves those): grid = rows / kTauStretch.
-constexpr int kTauStretch = 128;
-
-template <int THREADS, int G>
-__global__ void __launch_bounds__(THREADS)
-sample_tau_kernel(const float *__restrict__ Ys, int64_t ldy, const FusedSeg *__restrict__ segs, int n_seg, float *__restrict__ tau,
-                  int n_rows, bool only_unset)
-{
-    __shared__ TauRowScratch W;
-    __shared__ int todo[kTauStretch];
-    __shared__ int n_todo;
-    if (!only_unset) {
-        tau_of_row<THREADS, G>(Ys, ldy, segs, n_seg, tau, blockIdx.x, W);
-        return;
-    }
-    if (threadIdx.x == 0) n_todo = 0;
-    __syncthreads();
-    const int r0 = blockIdx.x * kTauStretch, r1 = min(n_rows, r0 + kTauStretch);
-    for (int row = r0 + threadIdx.x; row < r1; row += THREADS)
-        if (!(tau[row] == tau[row])) todo[atomicAdd(&n_todo, 1)] = row;
-    __syncthreads();
-    const int n = n_todo;
-    for (int i = 0; i < n; ++i) {
-        tau_of_row<THREADS, G>(Ys, ldy, segs, n_seg, tau, todo[i], W);
-        __syncthreads();
-    }
 }
 
 // ---- 5. exact selection among the candidates ---------------------------------------------------------------------
@@ -1063,7 +700,7 @@ candidate_select_kernel(SelParams p)
 template <typename T, int THREADS, int EMAX, bool KEEP>
 static int launch_select(const SelParams &sp, unsigned rows, size_t dyn, cudaStream_t st)
 {
-    FM_CUDA_OK(cudaFuncSetAttribute(candidate_select_kernel<T, THREADS, EMAX, KEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    FM_CUDA_OK(func_attr_cached((const void *)candidate_select_kernel<T, THREADS, EMAX, KEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     candidate_select_kernel<T, THREADS, EMAX, KEEP><<<rows, THREADS, dyn, st>>>(sp);
     FM_LAUNCHED("candidate_select_kernel");
     return FM_OK;
@@ -1124,15 +761,15 @@ static int choose_ranges(int64_t mtiles, int64_t min_tiles, int sms)
 
 static int sample_rank(double z) { return (int)std::ceil(z + 5.0 * std::sqrt(z) + 2.0); }
 
-// Layout of the workspace for the eligible segments.  Groups are sized so that the sample scores and the candidate
-// lists of one group stay within ~3 GB.
+// Layout of the workspace for the eligible segments.  Groups are sized so that the candidate lists of one group stay
+// within ~3 GB.
 FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, const int64_t *zc)
 {
     FusedPlan P = {};
     int64_t zmin = INT64_MAX, total_b = 0;
     for (int i = 0; i < n; ++i) { zmin = std::min(zmin, zc[i]); P.max_keys = std::max(P.max_keys, n_keys[i]); total_b += n_buckets[i]; }
-    // about 128 of a bucket's keys in the sample; a coarser step when the sampled row would not fit in shared memory
-    // (kMaxSample scores), never so coarse that fewer than 8 of them are expected
+    // about 128 of a bucket's keys in the sample; a coarser step for very long segments (at most kMaxSample sampled keys),
+    // never so coarse that fewer than 8 of a bucket's keys are expected in the sample
     P.step = (int)std::max<int64_t>(std::min<int64_t>(64, zmin / 128), ceil_div(P.max_keys, kMaxSample));
     P.step = (int)std::max<int64_t>(1, std::min<int64_t>(P.step, zmin / 8));
     int cap = 0;
@@ -1140,13 +777,11 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
         const double z = double(zc[i]) / P.step;
         const double r = sample_rank(z);
         cap = std::max(cap, (int)std::ceil(P.step * (r + 6.0 * std::sqrt(r))) + 64);
-        P.ld_sample = std::max<int64_t>(P.ld_sample, n_keys[i] / P.step + 2);
     }
     P.cap = (cap + 7) / 8 * 8;
     // shared memory of the selection kernel: candidate scores + key indices, tile masks, entries before each tile
     P.sel_smem = size_t(P.cap) * 8 + size_t(ceil_div(P.max_keys, kTcBN)) * 12 + 32;
-    P.ld_sample = (P.ld_sample + 31) / 32 * 32;              // the dense scores are stored in 32 x 32 blocks
-    const size_t per_bucket = size_t(P.ld_sample) * 4 + size_t(P.cap) * 16 + size_t(ceil_div(P.max_keys, kTcBN)) * 8;
+    const size_t per_bucket = size_t(P.cap) * 16 + size_t(ceil_div(P.max_keys, kTcBN)) * 8;
     // rows of a group: every segment starts on a multiple of 32 rows
     int64_t max_b = 0, total_pad = 0;
     for (int i = 0; i < n; ++i) { max_b = std::max(max_b, ceil_div(n_buckets[i], 32) * 32); total_pad += ceil_div(n_buckets[i], 32) * 32; }
@@ -1159,7 +794,6 @@ FusedPlan fused_plan(int n, const int64_t *n_keys, const int64_t *n_buckets, con
     P.off_tcseg = off;  off += align_up(size_t(n) * sizeof(TcSeg) * 2, 256);
     P.off_tau = off;    off += align_up(size_t(P.group_buckets) * 4, 256);
     P.off_count = off;  off += align_up(size_t(P.group_buckets) * kMaxRanges * 2 * 4, 256);
-    P.off_ys = off;     off += align_up(size_t(P.group_buckets) * P.ld_sample * 4, 256);
     P.off_cand = off;   off += align_up(size_t(P.group_buckets) * P.cap * 16, 256);
     P.off_mask = off;   off += align_up(size_t(ceil_div(P.max_keys, kTcBN)) * P.group_buckets * 8, 256);
     P.off_yf = off;     off += align_up(size_t(kMaxFail) * P.max_keys * 4, 256);
@@ -1265,8 +899,8 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
             s.ns0 = (int)ceil_div(kb[g1], P.step);
             s.ns = (int)(ceil_div(kb[g1] + nk[g1], P.step) - s.ns0);
             s.out_row0 = (int)rows; s.kmax_bits = 0; s.table_off = table_off[g1];
-            ht[g1] = TcSeg{s.cb, s.n_buckets, s.ns0, s.ns, (int)mtiles, s.out_row0};            // sample pass
-            ht[n + g1] = TcSeg{s.cb, s.n_buckets, s.kb, s.n_keys, (int)mtiles, s.out_row0};      // candidate pass
+            ht[g1] = TcSeg{s.cb, s.n_buckets, s.ns0, s.ns, (int)mtiles, s.out_row0, s.rank};    // threshold pass (sampled rows)
+            ht[n + g1] = TcSeg{s.cb, s.n_buckets, s.kb, s.n_keys, (int)mtiles, s.out_row0, 0};      // candidate pass
             rows += ceil_div(nbk[g1], 32) * 32;
             mtiles += ceil_div(nbk[g1], kTcBM);
             ++g1;
@@ -1287,7 +921,6 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         float *tau = (float *)(ws + P.off_tau);
         int *counts = (int *)(ws + P.off_count);
         int *fail_count = (int *)(ws + P.off_fail), *fail_list = fail_count + 1;
-        float *Ys = (float *)(ws + P.off_ys);
         uint4 *cand = (uint4 *)(ws + P.off_cand);
         uint2 *cand_mask = (uint2 *)(ws + P.off_mask);
         float *Yf = (float *)(ws + P.off_yf);
@@ -1298,39 +931,12 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         const int sms = sm_count();
         TcParams tp = {};
         tp.segs = dtc_s; tp.n_seg = ng; tp.status = (int *)(ws + P.off_status);
-        tp.Y = Ys; tp.ldy = P.ld_sample;
         {
-            const int64_t tiles = ceil_div(P.ld_sample, kTcBN);
-            tp.n_ranges = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, ceil_div(2 * sms, mtiles)));
-            rc = tc_project_launch(tmA, tmKs, tp, int(mtiles) * tp.n_ranges, d, true, dtype == FM_BF16, st);
+            // thresholds: the sample projection three times over with reducing epilogues (tc_tau.cu), no score matrix
+            TauParams tq = {dtc_s, ng, tau, (int *)(ws + P.off_status), 0};
+            rc = tc_tau_launch(tmA, tmKs, tq, int(mtiles), d, dtype == FM_BF16, st);
             if (rc != FM_OK) return rc;
         }
-        {
-            // the row sits in the CTA's registers: 16 pieces of four scores per thread; enough threads for the pre-filter's
-            // thread maxima to outnumber the rank where that is possible
-            int64_t n4_max = 0, rank_max = 0;
-            for (int i = g0; i < g1; ++i) { n4_max = std::max<int64_t>(n4_max, (hs[i].ns + 3) / 4); rank_max = std::max<int64_t>(rank_max, hs[i].rank); }
-            const int64_t by_rank = ceil_div(rank_max, 2) + 32;          // threads whose two maxima each comfortably outnumber the rank
-            if (n4_max > 12 * 1024) {
-                set_error("fused index build: a sample row of %lld scores does not fit the threshold kernel", (long long)n4_max * 4);
-                return FM_ERR_UNSUPPORTED;
-            }
-            // eight rows per CTA first (whole 128-byte lines); the rows it leaves unset (tau = NaN) go to the one-row kernel
-            bool first = false;
-            if (rank_max <= 200 && n4_max >= 256) {
-                const size_t dyn8 = size_t(kTau8Rows) * kTau8List * 4 + 8 * sizeof(Tau8Warp);
-                FM_CUDA_OK(cudaFuncSetAttribute(sample_tau8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn8));
-                sample_tau8_kernel<<<(unsigned)(rows / kTau8Rows), kTau8Threads, dyn8, st>>>(Ys, P.ld_sample, dsegs, ng, tau);
-                FM_LAUNCHED("sample_tau8_kernel");
-                first = true;
-            }
-            const unsigned grid1 = first ? (unsigned)ceil_div(rows, kTauStretch) : (unsigned)rows;
-            if (n4_max <= 8 * 256 && by_rank <= 256) sample_tau_kernel<256, 8><<<grid1, 256, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau, (int)rows, first);
-            else if (n4_max <= 16 * 256 && by_rank <= 256) sample_tau_kernel<256, 16><<<grid1, 256, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau, (int)rows, first);
-            else if (n4_max <= 16 * 512) sample_tau_kernel<512, 16><<<grid1, 512, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau, (int)rows, first);
-            else sample_tau_kernel<1024, 12><<<grid1, 1024, 0, st>>>(Ys, P.ld_sample, dsegs, ng, tau, (int)rows, first);
-        }
-        FM_LAUNCHED("sample_tau_kernel");
 
         tp.segs = dtc_m;
         tp.tau = tau; tp.cand = cand; tp.cand_mask = cand_mask; tp.mask_ld = P.group_buckets; tp.cap = P.cap; tp.cand_count = counts;
@@ -1350,7 +956,7 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         if (rc != FM_OK) return rc;
         // (the projection's CTAs configure their SMs for the largest shared memory: ask for the same, or this kernel's
         // CTAs would wait for SMs to drain)
-        FM_CUDA_OK(cudaFuncSetAttribute(key_norm_max_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        FM_CUDA_OK(func_attr_cached((const void *)key_norm_max_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         key_norm_max_kernel<T><<<sms, 512, 0, side ? side : st>>>((const T *)K, d, dsegs, ng);
         FM_LAUNCHED("key_norm_max_kernel");
         if (side) {

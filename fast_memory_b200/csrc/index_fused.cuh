@@ -11,11 +11,10 @@ constexpr size_t kFusedMaxSelSmem = 208u << 10;   // dynamic shared memory the s
 struct FusedPlan {
     int step;                  // every step-th key is sampled for the threshold estimate
     int cap;                   // candidate slots per bucket
-    int64_t ld_sample;         // columns of the sample score matrix
     int64_t max_keys;          // longest segment
     int64_t group_buckets;     // buckets processed per group of segments
     size_t sel_smem;           // dynamic shared memory of the selection kernel
-    size_t off_status, off_segs, off_tcseg, off_tau, off_count, off_fail, off_ys, off_cand, off_mask, off_yf, total;
+    size_t off_status, off_segs, off_tcseg, off_tau, off_count, off_fail, off_cand, off_mask, off_yf, total;
 };
 
 // Can a segment of n_keys keys with buckets of zc keys take the fused path?

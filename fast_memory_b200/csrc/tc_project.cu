@@ -327,7 +327,7 @@ template <int D, bool DENSE>
 static int launch_tc(const CUtensorMap &tmA, const CUtensorMap &tmK, const TcParams &p, int units, bool bf16, cudaStream_t st)
 {
     constexpr size_t smem = size_t(D / 64) * (kBM * 128 + TcCfg<DENSE>::STAGES * kBN * 128) + 1024;
-    FM_CUDA_OK(cudaFuncSetAttribute(tc_project_kernel<D, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FM_CUDA_OK(func_attr_cached((const void *)tc_project_kernel<D, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     TcParams q = p;
     tc_apply_test_hooks(q);
     tc_project_kernel<D, DENSE><<<units, kTcThreads, smem, st>>>(tmA, tmK, q, tc::instr_desc_f16(bf16, kBM, kBN));

@@ -15,6 +15,7 @@ struct TcSeg {
     int n_keys;        // columns of this segment's projection (keys, or sampled keys)
     int mtile0;        // index of the segment's first bucket tile in the global list
     int out_row0;      // row of the segment's first bucket in Y / tau / cand / cand_count
+    int rank;          // threshold pass: which order statistic of the sample scores the threshold is (1 = largest)
 };
 
 struct TcParams {
@@ -57,6 +58,17 @@ __host__ __device__ inline size_t dense_offset(int64_t row, int64_t col, int64_t
 {
     return dense_block_offset(row, col, ldy) + size_t((col & 31) >> 2) * 128 + size_t(row & 31) * 4 + size_t(col & 3);
 }
+
+// Thresholds straight from the projection of the key sample (tc_tau.cu): tau[row] = a lower bound, tight to 2^-15 of the
+// row's score range, of the rank-th largest sample score of the bucket.  One CTA per bucket tile.
+struct TauParams {
+    const TcSeg *segs;     // k_row0 / n_keys in sampled rows
+    int n_seg;
+    float *tau;
+    int *status;
+    uint64_t wait_limit_ns;
+};
+int tc_tau_launch(const CUtensorMap &tmA, const CUtensorMap &tmKs, const TauParams &p, int mtiles, int d, bool bf16, cudaStream_t st);
 
 // units = (total bucket tiles) * n_ranges CTAs
 int tc_project_launch(const CUtensorMap &tmA, const CUtensorMap &tmK, const TcParams &p, int units, int d, bool dense, bool bf16,

@@ -87,6 +87,9 @@ def compute_centroids(kq: torch.Tensor, centroids: torch.Tensor, n_hashes: int, 
     return out.reshape(n_hashes, k_heads, d).to(kq.dtype)
 
 
+# (bucket_off, seg_cb) device tensors per (device, stream, heads, buckets per sequence, keys per bucket): see Memory.build
+_PREFIX_CACHE: dict = {}
+
 class Memory:
     """An indexed set of keys/values.  Create with :meth:`build`.
 
@@ -205,12 +208,20 @@ class Memory:
 
         self.build_status = launch(flags)
         self.table = table
-        # the host-side prefix arrays are made while the device builds the table
-        bucket_off = np.zeros(total_c + 1, dtype=np.int64)
-        np.cumsum(np.repeat(seg_zc, seg_c), out=bucket_off[1:])
-        self.bucket_off = torch.from_numpy(bucket_off).to(dev, non_blocking=True)
+        # the prefix arrays are made on the host while the device builds the table; they depend on the shape of the memory
+        # only, so memories of a shape seen before (on this stream) share them and their copies leave the build's tail
+        key = (dev, torch.cuda.current_stream(dev).cuda_stream, H, tuple(Cs), tuple(seq_zc))
+        hit = _PREFIX_CACHE.get(key)
+        if hit is None:
+            bucket_off = np.zeros(total_c + 1, dtype=np.int64)
+            np.cumsum(np.repeat(seg_zc, seg_c), out=bucket_off[1:])
+            hit = (torch.from_numpy(bucket_off).to(dev, non_blocking=True),
+                   torch.tensor(seg_cb, dtype=torch.int32).to(dev, non_blocking=True))
+            if len(_PREFIX_CACHE) >= 16:
+                _PREFIX_CACHE.pop(next(iter(_PREFIX_CACHE)))
+            _PREFIX_CACHE[key] = hit
+        self.bucket_off, self._seg_cb_dev = hit                # (never written: compaction and append make new tensors)
         self.max_bucket_len = int(seg_zc.max()) if total_c else 0
-        self._seg_cb_dev = torch.tensor(seg_cb, dtype=torch.int32).to(dev, non_blocking=True)
         if check:
             if fallback_exact and not exact_only and int(self.build_status.item()) == 4:
                 # first with one candidate buffer per bucket (key positions far from stationary overflow the per-range
