@@ -40,6 +40,8 @@ _SIGNATURES = {
     "fm_group_rows_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "fm_group_rows": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_size_t, c_void_p]),
+    "fm_group_rows_segmented": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p,
+                                        c_void_p, c_void_p, c_size_t, c_void_p]),
     "fm_group_rows_static_max_buckets": (c_int64, []),
     "fm_group_rows_static": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p]),

@@ -80,6 +80,69 @@ __global__ void bucket_scatter_kernel(const int32_t *__restrict__ hash, int n_ro
     }
 }
 
+// ---- one launch: a CTA per segment -------------------------------------------------------------------------------------
+// When every hash is known to lie inside its segment's buckets (the hashes of fm_hash_rows do), the rows of segment s
+// fill perm[seg_xb[s] .. seg_xb[s + 1]) exactly, so a segment's part of the result depends on nothing outside the
+// segment: one CTA counts the segment's rows per bucket in shared memory, scans the counts, writes group_off and
+// scatters the rows - the memset and the three launches of the general path become one launch.  A hash outside the
+// segment's buckets is clamped into them (memory-safe; callers with untrusted hashes use fm_group_rows).
+constexpr int kSegGroupThreads = 1024;
+constexpr int kSegGroupMaxBuckets = 12288;  // counts + cursors of one segment in shared memory (96 KB)
+constexpr int kSegGroupMaxRows = 32768;     // beyond this a single CTA per segment is slower than the general path
+
+__global__ void __launch_bounds__(kSegGroupThreads)
+group_rows_segment_kernel(const int32_t *__restrict__ hash, int n_rows, int total_buckets, int n_seg,
+                          const int32_t *__restrict__ seg_xb, const int32_t *__restrict__ seg_cb,
+                          int32_t *__restrict__ group_off, int32_t *__restrict__ perm)
+{
+    extern __shared__ int32_t seg_sm[];
+    __shared__ int warp_sums[32];
+    __shared__ int carry_s;
+    const int s = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int r0 = seg_xb ? seg_xb[s] : 0, r1 = seg_xb ? seg_xb[s + 1] : n_rows;
+    const int c0 = seg_cb ? seg_cb[s] : 0, C = (seg_cb ? seg_cb[s + 1] : total_buckets) - c0;
+    int32_t *counts = seg_sm, *cursor = seg_sm + C;
+    for (int c = t; c < C; c += kSegGroupThreads) counts[c] = 0;
+    if (t == 0) carry_s = 0;
+    __syncthreads();
+    for (int r = r0 + t; r < r1; r += kSegGroupThreads) atomicAdd(&counts[min(max(hash[r], 0), C - 1)], 1);
+    __syncthreads();
+    for (int base = 0; base < C; base += kSegGroupThreads) {
+        const int c = base + t;
+        const int v = c < C ? counts[c] : 0;
+        int inc = v;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= off) inc += o;
+        }
+        if (lane == 31) warp_sums[warp] = inc;
+        __syncthreads();
+        if (warp == 0) {
+            const int w = warp_sums[lane];
+            int winc = w;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, winc, off);
+                if (lane >= off) winc += o;
+            }
+            warp_sums[lane] = winc - w;
+        }
+        __syncthreads();
+        const int excl = carry_s + warp_sums[warp] + inc - v;
+        if (c < C) { cursor[c] = excl; group_off[c0 + c] = r0 + excl; }
+        __syncthreads();
+        if (t == kSegGroupThreads - 1) carry_s = excl + v;
+        __syncthreads();
+    }
+    for (int r = r0 + t; r < r1; r += kSegGroupThreads) perm[r0 + atomicAdd(&cursor[min(max(hash[r], 0), C - 1)], 1)] = r;
+    // buckets outside the listed segments (a caller serving a slice of the heads) hold no rows
+    if (s == 0)
+        for (int c = t; c < c0; c += kSegGroupThreads) group_off[c] = 0;
+    if (s == n_seg - 1)
+        for (int c = c0 + C + t; c <= total_buckets; c += kSegGroupThreads) group_off[c] = n_rows;
+}
+
 // ---- scratch that lives in the library image, for callers that must not allocate ---------------------
 // Counts and cursors of fm_group_rows_static.  Every GPU that loads the library carries these 512 KiB
 // until the process exits.
@@ -145,6 +208,28 @@ extern "C" int fm_group_rows(const int32_t *hash, int64_t n_rows, int64_t total_
         bucket_scatter_kernel<<<blocks, 256, 0, st>>>(hash, (int)n_rows, (int)total_buckets, n_seg, seg_xb, seg_cb, cursor, perm);
         FM_LAUNCHED("bucket_scatter_kernel");
     }
+    return FM_OK;
+}
+
+extern "C" int fm_group_rows_segmented(const int32_t *hash, int64_t n_rows, int64_t total_buckets, int n_seg,
+                                       const int32_t *seg_xb, const int32_t *seg_cb, int64_t max_seg_rows, int64_t max_seg_buckets,
+                                       int32_t *group_off, int32_t *perm, void *workspace, size_t workspace_bytes,
+                                       fm_stream_t stream)
+{
+    using namespace fm;
+    FM_REQUIRE(group_off && (n_rows == 0 || (hash && perm)), "fm_group_rows_segmented: null pointer");
+    FM_REQUIRE(n_rows >= 0 && total_buckets > 0 && n_seg >= 1, "fm_group_rows_segmented: bad sizes");
+    FM_REQUIRE(n_rows < (int64_t(1) << 31) && total_buckets < (int64_t(1) << 31), "fm_group_rows_segmented: sizes exceed int32");
+    FM_REQUIRE((seg_xb == nullptr) == (seg_cb == nullptr), "fm_group_rows_segmented: pass both segment arrays or neither");
+    FM_REQUIRE(seg_xb || n_seg == 1, "fm_group_rows_segmented: n_seg > 1 needs segment arrays");
+    if (n_rows == 0 || max_seg_rows > kSegGroupMaxRows || max_seg_buckets > kSegGroupMaxBuckets || max_seg_buckets <= 0)
+        return fm_group_rows(hash, n_rows, total_buckets, n_seg, seg_xb, seg_cb, group_off, perm, workspace, workspace_bytes, stream);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t dyn = size_t(max_seg_buckets) * 8;
+    FM_CUDA_OK(func_attr_cached((const void *)group_rows_segment_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    group_rows_segment_kernel<<<n_seg, kSegGroupThreads, dyn, st>>>(hash, (int)n_rows, (int)total_buckets, n_seg, seg_xb, seg_cb,
+                                                                  group_off, perm);
+    FM_LAUNCHED("group_rows_segment_kernel");
     return FM_OK;
 }
 

@@ -350,7 +350,9 @@ class Memory:
             hashes = ops.hash_rows(qf, self.A, seg_xb, seg_cb, max_rows)
         else:
             hashes = q_hashes.reshape(-1).to(torch.int32).contiguous()
-        group_off, perm = ops.group_rows(hashes, self.total_buckets, seg_xb, seg_cb)
+        # hashes made by the hash kernel lie inside their segment's buckets: the one-launch grouping applies
+        group_off, perm = ops.group_rows(hashes, self.total_buckets, seg_xb, seg_cb, in_range=q_hashes is None,
+                                         max_seg_rows=max_rows, max_seg_buckets=max(self.seq_buckets))
         if out is not None or lse_out is not None:
             if out is None or lse_out is None or out.dtype != q.dtype or lse_out.dtype != torch.float32 or \
                     out.numel() != q.numel() or lse_out.numel() != Hq * S or not out.is_contiguous() or not lse_out.is_contiguous():

@@ -65,8 +65,13 @@ def hash_rows(x: torch.Tensor, A: torch.Tensor, seg_xb: Optional[torch.Tensor] =
 
 
 def group_rows(hashes: torch.Tensor, total_buckets: int, seg_xb: Optional[torch.Tensor] = None,
-               seg_cb: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Counting sort of rows by global bucket -> (group_off int32 ``[buckets+1]``, perm int32 ``[rows]``)."""
+               seg_cb: Optional[torch.Tensor] = None, in_range: bool = False, max_seg_rows: int = 0,
+               max_seg_buckets: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Counting sort of rows by global bucket -> (group_off int32 ``[buckets+1]``, perm int32 ``[rows]``).
+
+    ``in_range=True`` (with the size of the largest segment in rows and buckets): the caller vouches that every hash
+    lies inside its segment's buckets - the output of :func:`hash_rows` does - and the sort runs as ONE launch, a CTA
+    per segment; hashes from elsewhere go through the general path, which drops rows whose hash is out of range."""
     dev = L.require_cuda(hashes, seg_xb, seg_cb)
     assert hashes.dtype == torch.int32 and hashes.is_contiguous()
     n = hashes.numel()
@@ -75,9 +80,14 @@ def group_rows(hashes: torch.Tensor, total_buckets: int, seg_xb: Optional[torch.
     need = L.lib().fm_group_rows_workspace_bytes(n, total_buckets)
     ws = _ws.get("group", need, dev)
     n_seg = 1 if seg_xb is None else seg_xb.numel() - 1
-    L.check(L.lib().fm_group_rows(L.ptr(hashes), n, total_buckets, n_seg, L.ptr(seg_xb), L.ptr(seg_cb),
-                                  L.ptr(group_off), L.ptr(perm), L.ptr(ws), ws.numel(), L.stream_ptr(dev)),
-            "fm_group_rows")
+    if in_range and max_seg_rows > 0 and max_seg_buckets > 0:
+        L.check(L.lib().fm_group_rows_segmented(L.ptr(hashes), n, total_buckets, n_seg, L.ptr(seg_xb), L.ptr(seg_cb),
+                                                int(max_seg_rows), int(max_seg_buckets), L.ptr(group_off), L.ptr(perm),
+                                                L.ptr(ws), ws.numel(), L.stream_ptr(dev)), "fm_group_rows_segmented")
+    else:
+        L.check(L.lib().fm_group_rows(L.ptr(hashes), n, total_buckets, n_seg, L.ptr(seg_xb), L.ptr(seg_cb),
+                                      L.ptr(group_off), L.ptr(perm), L.ptr(ws), ws.numel(), L.stream_ptr(dev)),
+                "fm_group_rows")
     return group_off, perm[:n]
 
 

@@ -78,6 +78,17 @@ int fm_group_rows(const int32_t *hash, int64_t n_rows, int64_t total_buckets, in
                   const int32_t *seg_xb, const int32_t *seg_cb, int32_t *group_off, int32_t *perm,
                   void *workspace, size_t workspace_bytes, fm_stream_t stream);
 
+/* The same result in ONE launch (a CTA per segment: counts, scan and scatter in shared memory) for hashes that are
+ * known to lie in [0, buckets of their segment) - the output of fm_hash_rows does.  Then the rows of a segment fill
+ * exactly their own stretch of perm and no segment depends on another.  A hash outside its segment's buckets is
+ * clamped into them (memory-safe, but not the dropping fm_group_rows does): pass untrusted hashes to fm_group_rows.
+ * max_seg_rows / max_seg_buckets: the largest segment (rows, buckets); segments too large for one CTA (more than
+ * 32768 rows or 12288 buckets) are handed to fm_group_rows, which is why the workspace is still passed. */
+int fm_group_rows_segmented(const int32_t *hash, int64_t n_rows, int64_t total_buckets, int n_seg,
+                            const int32_t *seg_xb, const int32_t *seg_cb, int64_t max_seg_rows, int64_t max_seg_buckets,
+                            int32_t *group_off, int32_t *perm, void *workspace, size_t workspace_bytes,
+                            fm_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------
  * fm_group_rows for callers that cannot allocate device memory.  This entry point has no counterpart
  * in the reference: it exists for hosts that get their buffers handed to them and may not call

@@ -440,3 +440,33 @@ def test_bounded_pipeline_wait_gives_up_and_the_next_call_is_fine():
     Y = ops.project_tc(A, K)
     ref = A.float() @ K.float().T
     assert (Y - ref).abs().max() <= 1e-3 * ref.abs().max()
+
+
+@pytest.mark.parametrize("n_seg,rows,C", [(1, 5000, 300), (6, 700, 64), (4, 9000, 2000)])
+def test_segmented_grouping_equals_the_general_one(n_seg, rows, C):
+    """``fm_group_rows_segmented`` (one launch, a CTA per segment) against ``fm_group_rows`` on hashes that lie inside
+    their segments' buckets: the same group offsets, and the same rows in every group (their order inside a group is
+    free in both).  Also with a slice of the segments, as ``Memory.query(head_range=...)`` passes them."""
+    g = torch.Generator().manual_seed(n_seg * 1000 + C)
+    seg_rows = [rows + 37 * s for s in range(n_seg)]
+    seg_c = [C + 5 * s for s in range(n_seg)]
+    xb = torch.tensor([0] + list(np.cumsum(seg_rows)), dtype=torch.int32)
+    cb = torch.tensor([0] + list(np.cumsum(seg_c)), dtype=torch.int32)
+    hashes = torch.cat([torch.randint(0, seg_c[s], (seg_rows[s],), generator=g) for s in range(n_seg)]).int().to(DEV)
+    total = int(cb[-1])
+    ref_off, ref_perm = ops.group_rows(hashes, total, xb.to(DEV), cb.to(DEV))
+    off, perm = ops.group_rows(hashes, total, xb.to(DEV), cb.to(DEV), in_range=True, max_seg_rows=max(seg_rows),
+                               max_seg_buckets=max(seg_c))
+    assert torch.equal(off, ref_off)
+    o = off.cpu().numpy()
+    p, rp = perm.cpu().numpy(), ref_perm.cpu().numpy()
+    for b in range(total):
+        assert np.array_equal(np.sort(p[o[b]:o[b + 1]]), np.sort(rp[o[b]:o[b + 1]]))
+    if n_seg >= 4:                                                          # segments 1 and 2 only
+        sl_x = (xb[1:4] - xb[1]).to(DEV)
+        h2 = hashes[int(xb[1]):int(xb[3])].contiguous()
+        ref_off, ref_perm = ops.group_rows(h2, total, sl_x, cb[1:4].to(DEV))
+        off, perm = ops.group_rows(h2, total, sl_x, cb[1:4].to(DEV), in_range=True, max_seg_rows=max(seg_rows),
+                                   max_seg_buckets=max(seg_c))
+        assert torch.equal(off, ref_off)
+        assert torch.equal(torch.sort(perm)[0], torch.sort(ref_perm)[0])
