@@ -17,6 +17,7 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence, Tuple, Union
 
+import functools
 import warnings
 
 import numpy as np
@@ -85,6 +86,31 @@ def compute_centroids(kq: torch.Tensor, centroids: torch.Tensor, n_hashes: int, 
     L.check(L.lib().fm_gather_mean(L.ptr(xf), xf.shape[0], d, L.ptr(t), out.shape[0], n_groups * centroid_topk, L.ptr(out),
                                    L.stream_ptr(dev)), "fm_gather_mean")
     return out.reshape(n_hashes, k_heads, d).to(kq.dtype)
+
+
+
+class _SegmentLayout:
+    """Host arrays of a memory's shape (heads x sequences): prefix arrays of key rows, buckets and table entries, as
+    python lists and as the ctypes arrays the library takes.  Depends on the shape only, so it is made once per shape
+    (the index build is short enough for this bookkeeping to show in its time)."""
+
+    def __init__(self, H: int, cu: Tuple[int, ...], Cs: Tuple[int, ...], Zs: Tuple[int, ...]):
+        n_seq, N_total = len(cu) - 1, cu[-1]
+        self.seg_kb = [h * N_total + cu[s] for h in range(H) for s in range(n_seq)] + [H * N_total]
+        self.seq_zc = [min(Zs[s], cu[s + 1] - cu[s]) for s in range(n_seq)]
+        self.seg_c = np.tile(np.asarray(Cs, dtype=np.int64), H)                   # buckets of every segment
+        self.seg_zc = np.tile(np.asarray(self.seq_zc, dtype=np.int64), H)         # keys per bucket of every segment
+        self.seg_cb = [0] + np.cumsum(self.seg_c).tolist()
+        self.seg_z = [Zs[s] for _ in range(H) for s in range(n_seq)]
+        self.table_off = [0] + np.cumsum(self.seg_c * self.seg_zc).tolist()
+        self.c_kb, self.c_cb = L.host_i64(self.seg_kb), L.host_i64(self.seg_cb)
+        self.c_z, self.c_to = L.host_i64(self.seg_z), L.host_i64(self.table_off[:-1])
+        self.ws_need = {}                                                         # (d, dtype, flags) -> build workspace bytes
+
+
+@functools.lru_cache(maxsize=32)
+def _segment_layout(H: int, cu: Tuple[int, ...], Cs: Tuple[int, ...], Zs: Tuple[int, ...]) -> _SegmentLayout:
+    return _SegmentLayout(H, cu, Cs, Zs)
 
 
 # (bucket_off, seg_cb) device tensors per (device, stream, heads, buckets per sequence, keys per bucket): see Memory.build
@@ -159,14 +185,10 @@ class Memory:
         Cs = _per_seq(n_buckets, n_seq, "n_buckets")
         Zs = _per_seq(bucket_size, n_seq, "bucket_size")
         # segments tile the flat [H * N_total] key rows: segment (h, s) starts at h * N_total + cu[s]
-        seg_kb = [h * N_total + cu[s] for h in range(H) for s in range(n_seq)] + [H * N_total]
-        seq_zc = [min(Zs[s], cu[s + 1] - cu[s]) for s in range(n_seq)]
-        seg_c = np.tile(np.asarray(Cs, dtype=np.int64), H)                       # buckets of every segment
-        seg_zc = np.tile(np.asarray(seq_zc, dtype=np.int64), H)                  # keys per bucket of every segment
-        seg_cb = [0] + np.cumsum(seg_c).tolist()
-        seg_z = [Zs[s] for _ in range(H) for s in range(n_seq)]
-        table_off = [0] + np.cumsum(seg_c * seg_zc).tolist()
-        self.seg_kb, self.seg_cb, self.seg_z, self.table_off = seg_kb, seg_cb, seg_z, table_off
+        lay = _segment_layout(H, tuple(cu), tuple(Cs), tuple(Zs))
+        seg_kb, seg_cb, seg_z, table_off = lay.seg_kb, lay.seg_cb, lay.seg_z, lay.table_off
+        seq_zc, seg_c, seg_zc = lay.seq_zc, lay.seg_c, lay.seg_zc
+        self.seg_kb, self.seg_cb, self.seg_z, self.table_off = list(seg_kb), list(seg_cb), list(seg_z), list(table_off)
         self.seq_buckets = Cs
         total_c = seg_cb[-1]
         c_per_head = total_c // H
@@ -197,9 +219,11 @@ class Memory:
         self.A = A2
 
         table = torch.empty(max(table_off[-1], 1), dtype=torch.int32, device=dev)
-        kb, cb, zz, to = L.host_i64(seg_kb), L.host_i64(seg_cb), L.host_i64(seg_z), L.host_i64(table_off[:-1])
+        kb, cb, zz, to = lay.c_kb, lay.c_cb, lay.c_z, lay.c_to
         flags = 1 if exact_only else 0
-        need = L.lib().fm_index_build_workspace_bytes(n_seg, kb, cb, zz, d, L.dtype_id(k.dtype), flags)
+        need = lay.ws_need.get((d, k.dtype, flags))
+        if need is None:
+            need = lay.ws_need[(d, k.dtype, flags)] = L.lib().fm_index_build_workspace_bytes(n_seg, kb, cb, zz, d, L.dtype_id(k.dtype), flags)
         ws = ops._ws.get("build", need, dev)
         def launch(fl):
             L.check(L.lib().fm_index_build(L.ptr(kf), L.ptr(A2), L.dtype_id(k.dtype), d, n_seg, kb, cb, zz, to,
