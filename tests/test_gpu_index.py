@@ -470,3 +470,31 @@ def test_segmented_grouping_equals_the_general_one(n_seg, rows, C):
                                    max_seg_buckets=max(seg_c))
         assert torch.equal(off, ref_off)
         assert torch.equal(torch.sort(perm)[0], torch.sort(ref_perm)[0])
+
+
+@pytest.mark.parametrize("case", ["flat", "narrow", "outliers", "ragged_sample"])
+def test_thresholds_from_the_sample_projection_edge_cases(case):
+    """The thresholds come from histograms of the sample scores taken in the projection's epilogue.  Rows whose scores
+    are all equal (flat), crowd a range that is tiny against their magnitude (the sub-bin refinement is left out), hold
+    a few huge outliers (coarse first-level bins), or whose sample is not a multiple of the 256-key tile: the table must
+    equal the oracle's whatever threshold comes out, because a low threshold only costs candidates."""
+    g = torch.Generator().manual_seed({"flat": 1, "narrow": 2, "outliers": 3, "ragged_sample": 4}[case])
+    N, C, Z, d = 16384, 16, 256, 128
+    A = torch.nn.functional.normalize(torch.randn(1, C, d, generator=g), dim=-1)
+    if case == "flat":
+        k = torch.randn(1, d, generator=g).repeat(N, 1)
+    elif case == "narrow":
+        u = torch.nn.functional.normalize(torch.randn(d, generator=g), dim=0)
+        A = torch.nn.functional.normalize(u[None, None] + 0.3 * A, dim=-1)             # every bucket scores near |u| = 4
+        k = 4.0 * u[None] + 0.02 * torch.randn(N, d, generator=g)
+    elif case == "outliers":
+        k = torch.randn(N, d, generator=g)
+        k[torch.randperm(N, generator=g)[:5]] *= 300.0
+    else:
+        N = 8192 + 1000 + 40
+        k = torch.randn(N, d, generator=g)
+    k = k.bfloat16()[None].contiguous()
+    A = A.bfloat16()
+    mem = fm.Memory.build(k.to(DEV), k.to(DEV), A=A.to(DEV), bucket_size=Z)
+    ok, why = tables_equal_as_sets(mem.table_of(0).cpu().numpy(), O.topz(O.project(A[0], k[0]), Z))
+    assert ok, why
