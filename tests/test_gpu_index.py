@@ -498,3 +498,37 @@ def test_thresholds_from_the_sample_projection_edge_cases(case):
     mem = fm.Memory.build(k.to(DEV), k.to(DEV), A=A.to(DEV), bucket_size=Z)
     ok, why = tables_equal_as_sets(mem.table_of(0).cpu().numpy(), O.topz(O.project(A[0], k[0]), Z))
     assert ok, why
+
+
+def test_fused_build_random_shapes_and_data_equal_the_exact_build():
+    """Sixteen random combinations of dtype, head dim, segment length, bucket count and size, and of key distributions
+    (Gaussian, clustered, heavy-tailed norms, scores drifting with position, near-duplicate runs): the tensor-core
+    filter with its sampled thresholds and exact band must give the table of the all-fp32 build (oracle-pinned above)."""
+    import random
+    import warnings
+    rnd = random.Random(0)
+    for it in range(16):
+        g = torch.Generator().manual_seed(1000 + it)
+        d, dt = rnd.choice([64, 128]), rnd.choice([torch.bfloat16, torch.float16])
+        H, N = rnd.choice([1, 2, 3]), rnd.choice([8192, 12000, 20000, 40000, 65536])
+        C, Z = rnd.choice([16, 100, 128, 300]), rnd.choice([64, 200, 512, 1024, 2000])
+        Z = min(Z, N // 8)
+        kind = rnd.choice(["gauss", "mixture", "heavy", "drift", "dups"])
+        if kind == "gauss":
+            k = torch.randn(H, N, d, generator=g)
+        elif kind == "mixture":
+            cent = torch.nn.functional.normalize(torch.randn(32, d, generator=g), dim=-1)
+            k = cent[torch.randint(32, (H * N,), generator=g)].reshape(H, N, d) + 0.2 * torch.randn(H, N, d, generator=g)
+        elif kind == "heavy":
+            k = torch.randn(H, N, d, generator=g) * torch.exp(torch.randn(H, N, 1, generator=g))
+        elif kind == "drift":
+            k = torch.randn(H, N, d, generator=g) + torch.linspace(-2, 2, N)[None, :, None] * torch.randn(1, 1, d, generator=g)
+        else:
+            k = torch.randn(H, N // 16 + 1, d, generator=g).repeat_interleave(16, dim=1)[:, :N] + 0.001 * torch.randn(H, N, d, generator=g)
+        k = k.to(dt).contiguous().to(DEV)
+        A = torch.nn.functional.normalize(torch.randn(H, C, d, generator=g), dim=-1).to(dt).to(DEV)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")                 # (a data set that overflows the filter falls back with a warning)
+            fused = fm.Memory.build(k, k, A=A, bucket_size=Z)
+        exact = fm.Memory.build(k, k, A=A, bucket_size=Z, exact_only=True)
+        assert torch.equal(fused.table, exact.table), (it, kind, dt, d, H, N, C, Z)
