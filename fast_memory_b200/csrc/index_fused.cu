@@ -759,7 +759,11 @@ static int choose_ranges(int64_t mtiles, int64_t min_tiles, int sms)
     return best;
 }
 
-static int sample_rank(double z) { return (int)std::ceil(z + 5.0 * std::sqrt(z) + 2.0); }
+// Which order statistic of the sample scores serves as the threshold: z sampled keys of a bucket are expected among its
+// top Z; the threshold is too high - and the bucket goes to the fallback - when more than the chosen rank are.  Four
+// standard deviations: about one bucket in 10^5 (a fifth of a bucket per benchmark build); every half deviation more
+// costs the selection 3 % more candidates.
+static int sample_rank(double z) { return (int)std::ceil(z + 4.0 * std::sqrt(z) + 2.0); }
 
 // Layout of the workspace for the eligible segments.  Groups are sized so that the candidate lists of one group stay
 // within ~3 GB.
