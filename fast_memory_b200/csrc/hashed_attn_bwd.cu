@@ -11,7 +11,9 @@
 // A query lies in exactly one bucket, so dQ rows are written once; a key lies in several buckets, so dK and dV are
 // accumulated with fp32 (16-byte vector) atomics into buffers the caller has zeroed (or is accumulating shard after shard).
 // This is the training-time companion of the forward kernels, written for parity first: no tensor cores yet.
-#include "attn_common.cuh"
+#include "attn_bwd.cuh"
+
+#include <cstdlib>
 
 namespace fm {
 
@@ -22,18 +24,6 @@ constexpr int kBwdQ = 16;                   // queries per block
 constexpr int kBwdK = 64;                   // keys per tile
 constexpr int kPLd = kBwdK + 1;
 
-struct BwdParams {
-    const void *q, *k, *v, *o, *d_o;
-    const float *lse;
-    const void *table;
-    int idx_bytes;
-    const int64_t *bucket_off;
-    const int32_t *bucket_kbase;
-    const int32_t *group_off, *perm;
-    int64_t n_k_rows;
-    float sm_scale;
-    float *dq, *dk, *dv;
-};
 
 // PASSES = ceil(d / 128): in the d-wide phases a lane owns four consecutive columns of every 128-column pass and a warp
 // a quarter of the tile's keys, so that dK and dV go out as 16-byte vector atomics (a quarter of the atomic traffic).
@@ -231,6 +221,11 @@ extern "C" int fm_hashed_attn_bwd(const void *q, const void *k, const void *v, i
     cudaStream_t st = (cudaStream_t)stream;
     // rows of dq whose bucket is empty are never visited: start from zero
     FM_CUDA_OK(cudaMemsetAsync(dq, 0, size_t(n_q_rows) * d * sizeof(float), st));
+    // 16-bit inputs with a head dim the tensor-core kernel is built for (rows 16-byte aligned): mma.sync
+    static const bool simt_only = getenv("FASTMEM_BWD_SIMT") != nullptr;        // (the CUDA-core kernel, for comparison)
+    if ((dtype == FM_BF16 || dtype == FM_F16) && (d == 64 || d == 128) &&
+        (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o | (uintptr_t)d_o) % 16 == 0) && !simt_only)
+        return launch_bwd_mma(p, dtype, d, total_buckets, st);
     switch (dtype) {
     case FM_F32: return launch_bwd<float>(p, d, total_buckets, st);
     case FM_BF16: return launch_bwd<__nv_bfloat16>(p, d, total_buckets, st);

@@ -261,7 +261,9 @@ def test_backward_matches_reference_golden(golden_dir):
 
 
 @pytest.mark.parametrize("dtype,d,tol", [(torch.float32, 64, 2e-4), (torch.float32, 256, 2e-4), (torch.bfloat16, 128, 4e-2),
-                                         (torch.float16, 32, 1e-2)])
+                                         (torch.float16, 32, 1e-2),
+                                         # the tensor-core kernel's other three instantiations (16-bit, d = 64 / 128)
+                                         (torch.bfloat16, 64, 4e-2), (torch.float16, 128, 1e-2), (torch.float16, 64, 1e-2)])
 def test_memory_query_backward_vs_oracle(dtype, d, tol):
     """Memory.query + Memory.query_backward against the dense restatement: ragged query blocks (17 and more queries in
     a bucket), buckets nobody asks for, keys that sit in several buckets, accumulation into given dk / dv."""
