@@ -37,7 +37,7 @@ __device__ __forceinline__ void red_add_v2(float *addr, float a, float b)
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 attn_bwd_mma_kernel(BwdParams p)
 {
     constexpr int CPR = D / 8;                               // 16-byte chunks per row
@@ -71,19 +71,27 @@ attn_bwd_mma_kernel(BwdParams p)
     const int b_row = (lane & 7) + ((lane >> 4) << 3), b_chk = (lane >> 3) & 1;      // B operand, k = head dim: K / V rows
     const int c_row = (lane & 7) + (((lane >> 3) & 1) << 3), c_chk = lane >> 4;      // B operand, transposed loads (k = rows)
 
+    // table entries are fetched one tile ahead of the copies that need them, so the index load never stalls the gather
+    constexpr int PER_T = kTK * CPR / kThreads;              // 16-byte pieces per thread, matrix and tile
+    int32_t rows[PER_T];
+    auto load_rows = [&](int tile) {
+#pragma unroll
+        for (int i = 0; i < PER_T; ++i) {
+            const int j = (t + i * kThreads) / CPR;
+            const int64_t pos = int64_t(tile) * kTK + j;
+            rows[i] = (tile < n_tiles && pos < len) ? min(max(int32_t(load_index(p.table, p.idx_bytes, kb + pos) + kbase), 0), row_max) : -1;
+        }
+    };
     auto issue = [&](int tile) {
         if (tile < n_tiles) {
             const int st = tile & 1;
             const uint32_t kdst = kv0 + st * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
-            const int live = int(min(int64_t(kTK), len - int64_t(tile) * kTK));
 #pragma unroll
-            for (int i = 0; i < kTK * CPR / kThreads; ++i) {
+            for (int i = 0; i < PER_T; ++i) {
                 const int idx = t + i * kThreads, j = idx / CPR, c = idx % CPR;
-                const bool ok = j < live;
-                int32_t row = 0;
-                if (ok) row = min(max(int32_t(load_index(p.table, p.idx_bytes, kb + int64_t(tile) * kTK + j) + kbase), 0), row_max);
-                if (c == 0) rows_s[st][j] = ok ? row : -1;
-                const size_t off = size_t(row) * ROW_BYTES + c * 16;
+                const bool ok = rows[i] >= 0;
+                if (c == 0) rows_s[st][j] = rows[i];
+                const size_t off = size_t(max(rows[i], 0)) * ROW_BYTES + c * 16;
                 cp_async16(kdst + swz<D>(j, c), kg + off, ok);
                 cp_async16(vdst + swz<D>(j, c), vg + off, ok);
             }
@@ -122,7 +130,9 @@ attn_bwd_mma_kernel(BwdParams p)
                 lq_s[r] = (l > -INFINITY && l < INFINITY) ? l * 1.4426950408889634f : INFINITY;
             }
         }
+        load_rows(0);
         issue(0);
+        load_rows(1);
 
         float dq[D / 8][4];
 #pragma unroll
@@ -132,6 +142,7 @@ attn_bwd_mma_kernel(BwdParams p)
             cp_async_wait<0>();
             __syncthreads();                                 // the tile (and, first time round, Q / dO / D / LSE) landed; the other stage is free
             issue(tile + 1);
+            load_rows(tile + 2);
             const int st = tile & 1;
             const uint32_t ks = kv0 + st * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
             const int live = int(min(int64_t(kTK), len - int64_t(tile) * kTK));
