@@ -374,6 +374,19 @@ def run_ours(args, rank, world):
     else:
         build_med = statistics.median(build_ms)
 
+    # the training-time companion (not part of either metric): dQ, dK, dV of one query step over the gathered rows
+    backward = None
+    if rank == 0 and cfg.name == "cfg2" and not args.no_comparator:
+        try:
+            o_b, lse_b = mem.query(q, sm_scale)
+            g_b = torch.randn(o_b.shape, device=dev, dtype=torch.float32).to(o_b.dtype)
+            bwd_ms = time_events(lambda: mem.query_backward(q, sm_scale, o_b, lse_b, g_b), 3, warmup=1)
+            backward = {"ms": bwd_ms, "queries_per_s": Hq * S / (bwd_ms * 1e-3), "x_forward_attention": bwd_ms / attn_ms,
+                        "kernel": "attn_bwd_mma_kernel (mma.sync), fp32 dq / dk / dv"}
+            del o_b, lse_b, g_b
+        except torch.OutOfMemoryError:
+            backward = None
+        torch.cuda.empty_cache()
     comparator = None
     if rank == 0 and not args.no_comparator and cfg.name in ("cfg2", "cfg3"):
         comparator = gpu_comparator(cfg, mem, q, k, v, sm_scale, attn_ms, step, min(args.steps, 10))
@@ -432,6 +445,8 @@ def run_ours(args, rank, world):
     res["kmeans"] = {"ms": kmeans_ms, "iters": cfg.kmeans_iters, "keys_per_s": world * H * N * cfg.kmeans_iters / (kmeans_ms * 1e-3),
                      "tflops": km_flops / (kmeans_ms * 1e-3) / 1e12,
                      "frac_of_tensor_peak": km_flops / (kmeans_ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+    if backward is not None:
+        res["backward"] = backward
     if comparator is not None:
         res["gpu_comparator"] = comparator
     if world == 1 and not args.no_cpu_baseline:
