@@ -4,6 +4,9 @@
 // integer sums of the unit rows in units of 2^-40; normalisation = sequential fp64 sum of squares.
 #include "common.cuh"
 
+#include <algorithm>
+#include <vector>
+
 namespace fm {
 
 constexpr float kFixScale = 1099511627776.0f;              // 2^40
@@ -115,23 +118,20 @@ __global__ void cast_rows_kernel(const float *__restrict__ src, T *__restrict__ 
     if (i < n) dst[i] = Elem<T>::from_f32(src[i]);
 }
 
-struct KmLayout { size_t off_nrm, off_hash, off_goff, off_perm, off_group, off_hws, total; };
-
+struct KmLayout { size_t off_nrm, off_hash, off_goff, off_perm, off_group, off_hws, off_seg, total; };
 static KmLayout km_layout(int n_seg, const int64_t *seg_xb, const int64_t *seg_cb)
 {
-    int64_t max_rows = 0, max_c = 0;
-    for (int s = 0; s < n_seg; ++s) {
-        max_rows = std::max(max_rows, seg_xb[s + 1] - seg_xb[s]);
-        max_c = std::max(max_c, seg_cb[s + 1] - seg_cb[s]);
-    }
+    // every iteration handles all segments at once: one assignment (hash), one grouping, one centroid update
+    const int64_t rows = std::max<int64_t>(seg_xb[n_seg], 1), total_c = std::max<int64_t>(seg_cb[n_seg], 1);
     KmLayout L;
     size_t off = 0;
-    L.off_nrm = off;  off += align_up(size_t(seg_xb[n_seg]) * 4, 256);
-    L.off_hash = off; off += align_up(size_t(max_rows) * 4, 256);
-    L.off_goff = off; off += align_up(size_t(max_c + 1) * 4, 256);
-    L.off_perm = off; off += align_up(size_t(max_rows) * 4, 256);
-    L.off_group = off; off += fm_group_rows_workspace_bytes(max_rows, std::max<int64_t>(max_c, 1));
-    L.off_hws = off; off += fm_hash_rows_workspace_bytes(max_rows, 1);
+    L.off_nrm = off;  off += align_up(size_t(rows) * 4, 256);
+    L.off_hash = off; off += align_up(size_t(rows) * 4, 256);
+    L.off_goff = off; off += align_up(size_t(total_c + 1) * 4, 256);
+    L.off_perm = off; off += align_up(size_t(rows) * 4, 256);
+    L.off_group = off; off += fm_group_rows_workspace_bytes(rows, total_c);
+    L.off_hws = off; off += fm_hash_rows_workspace_bytes(rows, n_seg);
+    L.off_seg = off; off += 2 * align_up(size_t(n_seg + 1) * 4, 256);       // int32 copies of the segment prefixes
     L.total = off;
     return L;
 }
@@ -148,32 +148,38 @@ static int kmeans_impl(const void *Xv, int d, int n_seg, const int64_t *seg_xb, 
     int32_t *goff = (int32_t *)(ws + L.off_goff);
     int32_t *perm = (int32_t *)(ws + L.off_perm);
     void *gws = ws + L.off_group;
+    int32_t *d_xb = (int32_t *)(ws + L.off_seg), *d_cb = (int32_t *)(ws + L.off_seg + align_up(size_t(n_seg + 1) * 4, 256));
     const int64_t rows = seg_xb[n_seg], total_c = seg_cb[n_seg];
-    if (rows > 0) {
-        if (sizeof(T) == 2 && d % 32 == 0 && d <= 256) {
-            if constexpr (sizeof(T) == 2) row_norm4_kernel<T><<<(unsigned)ceil_div(rows * 4, 256), 256, 0, st>>>(X, rows, d, nrm);
-        } else {
-            row_norm_kernel<T><<<(unsigned)ceil_div(rows, 128), 128, 0, st>>>(X, rows, d, nrm, nullptr);
-        }
-        FM_LAUNCHED("row_norm_kernel");
+    if (rows <= 0 || total_c <= 0) return FM_OK;
+    int64_t max_rows = 0;
+    {
+        std::vector<int32_t> h(2 * size_t(n_seg + 1));
+        for (int s = 0; s <= n_seg; ++s) { h[s] = (int32_t)seg_xb[s]; h[n_seg + 1 + s] = (int32_t)seg_cb[s]; }
+        for (int s = 0; s < n_seg; ++s) max_rows = std::max(max_rows, seg_xb[s + 1] - seg_xb[s]);
+        FM_CUDA_OK(cudaMemcpyAsync(d_xb, h.data(), size_t(n_seg + 1) * 4, cudaMemcpyHostToDevice, st));
+        FM_CUDA_OK(cudaMemcpyAsync(d_cb, h.data() + n_seg + 1, size_t(n_seg + 1) * 4, cudaMemcpyHostToDevice, st));
+        FM_CUDA_OK(cudaStreamSynchronize(st));               // (the host vector goes away; a set-up step, once per call)
     }
+    if (sizeof(T) == 2 && d % 32 == 0 && d <= 256) {
+        if constexpr (sizeof(T) == 2) row_norm4_kernel<T><<<(unsigned)ceil_div(rows * 4, 256), 256, 0, st>>>(X, rows, d, nrm);
+    } else {
+        row_norm_kernel<T><<<(unsigned)ceil_div(rows, 128), 128, 0, st>>>(X, rows, d, nrm, nullptr);
+    }
+    FM_LAUNCHED("row_norm_kernel");
     cast_rows_kernel<T><<<(unsigned)ceil_div(total_c * d, 256), 256, 0, st>>>(cent_f32, A, total_c * d);
     FM_LAUNCHED("cast_rows_kernel");
     const int lanes = std::max(1, 512 / d);
+    const bool one = n_seg == 1;
     for (int it = 0; it < iters; ++it) {
-        for (int s = 0; s < n_seg; ++s) {
-            const int64_t r0 = seg_xb[s], n = seg_xb[s + 1] - r0, c0 = seg_cb[s], C = seg_cb[s + 1] - c0;
-            if (C <= 0) continue;
-            int rc = fm_hash_rows(X + r0 * d, A + c0 * d, Elem<T>::id, n, C, d, 1, nullptr, nullptr, n, hash,
-                                  ws + L.off_hws, fm_hash_rows_workspace_bytes(n, 1), st);
-            if (rc != FM_OK) return rc;
-            rc = fm_group_rows(hash, n, C, 1, nullptr, nullptr, goff, perm, gws,
-                               fm_group_rows_workspace_bytes(n, C), st);
-            if (rc != FM_OK) return rc;
-            centroid_update_kernel<T><<<(unsigned)C, dim3(d, lanes), size_t(lanes) * d * 8, st>>>(
-                X, nrm, d, goff, perm, (int)r0, cent_f32 + c0 * d, A + c0 * d);
-            FM_LAUNCHED("centroid_update_kernel");
-        }
+        int rc = fm_hash_rows(X, A, Elem<T>::id, rows, total_c, d, n_seg, one ? nullptr : d_xb, one ? nullptr : d_cb, max_rows, hash,
+                              ws + L.off_hws, fm_hash_rows_workspace_bytes(rows, n_seg), st);
+        if (rc != FM_OK) return rc;
+        rc = fm_group_rows(hash, rows, total_c, n_seg, one ? nullptr : d_xb, one ? nullptr : d_cb, goff, perm, gws,
+                           fm_group_rows_workspace_bytes(rows, total_c), st);
+        if (rc != FM_OK) return rc;
+        // (perm holds global row numbers and goff runs over the clusters of all segments: one launch)
+        centroid_update_kernel<T><<<(unsigned)total_c, dim3(d, lanes), size_t(lanes) * d * 8, st>>>(X, nrm, d, goff, perm, 0, cent_f32, A);
+        FM_LAUNCHED("centroid_update_kernel");
     }
     return FM_OK;
 }
