@@ -2,11 +2,11 @@
 // on the tensor cores three times over, and the epilogue threads - one bucket row each - reduce the scores as they come
 // out of TMEM instead of storing them:
 //   sweep 0: minimum and maximum of the row's sample scores;
-//   sweep 1: a histogram of 127 equal bins over [min, max]; the bin b1 that holds the r-th largest score and the rank r1
+//   sweep 1: a histogram of 121 equal bins over [min, max]; the bin b1 that holds the r-th largest score and the rank r1
 //            the score has inside that bin;
 //   sweep 2: a histogram of 127 equal sub-bins of bin b1; tau = the lower edge of the sub-bin that holds the r1-th
 //            largest of the bin's scores, less one sub-bin.
-// tau is therefore at most the r-th largest sample score and misses it by about (max - min) / 8000: the candidate
+// tau is therefore at most the r-th largest sample score and misses it by at most about (max - min) / 7500: the candidate
 // pass keeps a handful of keys more than an exact order statistic would, and nothing else depends on tau's value (the
 // selection proves completeness on its own).  The sample projection is 1/step of the full one, so running it three times
 // costs little; what it saves is writing the sample scores (rows x sample x 4 bytes) and reading them back twice.
