@@ -821,6 +821,7 @@ struct BuildSide {
     bool tried = false;
 };
 static std::mutex g_side_mu;
+static std::mutex g_enqueue_mu;                // held while one build enqueues its group: the fork / join events are per device
 static BuildSide g_side[64];
 
 static BuildSide *build_side()
@@ -913,6 +914,9 @@ static int fused_build_impl(const void *K, const void *A, int d, int64_t total_k
         FusedSeg *dsegs = (FusedSeg *)(ws + P.off_segs) + g0;
         TcSeg *dtc_s = (TcSeg *)(ws + P.off_tcseg) + g0, *dtc_m = (TcSeg *)(ws + P.off_tcseg) + n + g0;
         BuildSide *bs = build_side();
+        // two host threads building on one device share the side stream and its two events: their record / wait pairs
+        // must not interleave (the enqueue of a group takes about a hundred microseconds)
+        std::lock_guard<std::mutex> enqueue_lock(g_enqueue_mu);
         if (ng == n) {
             rc = stage_to_device(bs, ws + P.off_segs, hdesc.data(), desc_bytes, st);
         } else {

@@ -162,3 +162,39 @@ def test_against_the_reference_triton_kernel(dtype):
     assert (o_d.float() - o_w.float()).abs().max() <= TOL_O[dtype]
     ulp = 2.0 ** (-7 if dtype == torch.bfloat16 else -10)
     assert ((lse_d.float() - lse_w.float()).abs() <= 2 * ulp * lse_w.float().abs().clamp_min(1.0)).all()
+
+
+def test_builds_from_two_host_threads_on_two_streams():
+    """Two host threads build (and query) different memories on their own streams at the same time.  The fused build
+    keeps a side stream and two events per device; the enqueue of a build is serialised inside the library, the
+    scratch memory is per stream, so both tables equal those of the same builds run one after the other."""
+    import threading
+    g = torch.Generator().manual_seed(11)
+    H, N, C, Z, d = 2, 16384, 64, 256, 128
+    data = []
+    for _ in range(2):
+        k = torch.randn(H, N, d, generator=g).bfloat16().to(DEV)
+        A = torch.nn.functional.normalize(torch.randn(H, C, d, generator=g), dim=-1).bfloat16().to(DEV)
+        data.append((k, A))
+    ref = [fm.Memory.build(k, k, A=A, bucket_size=Z).table.clone() for k, A in data]
+    torch.cuda.synchronize()
+    out, errs = [None, None], []
+
+    def work(i):
+        try:
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                for _ in range(6):
+                    mem = fm.Memory.build(data[i][0], data[i][0], A=data[i][1], bucket_size=Z)
+                out[i] = mem.table.clone()
+            s.synchronize()
+        except Exception as e:                                  # noqa: BLE001 - reported by the assert below
+            errs.append(e)
+
+    th = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in th:
+        t.start()
+    for t in th:
+        t.join()
+    assert not errs, errs
+    assert torch.equal(out[0], ref[0]) and torch.equal(out[1], ref[1])
