@@ -442,11 +442,11 @@ def test_bounded_pipeline_wait_gives_up_and_the_next_call_is_fine():
     assert (Y - ref).abs().max() <= 1e-3 * ref.abs().max()
 
 
-@pytest.mark.parametrize("n_seg,rows,C", [(1, 5000, 300), (6, 700, 64), (4, 9000, 2000)])
+@pytest.mark.parametrize("n_seg,rows,C", [(1, 5000, 300), (6, 700, 64), (4, 9000, 2000), (2, 40000, 300), (2, 3000, 13000)])
 def test_segmented_grouping_equals_the_general_one(n_seg, rows, C):
     """``fm_group_rows_segmented`` (one launch, a CTA per segment) against ``fm_group_rows`` on hashes that lie inside
     their segments' buckets: the same group offsets, and the same rows in every group (their order inside a group is
-    free in both).  Also with a slice of the segments, as ``Memory.query(head_range=...)`` passes them."""
+    free in both); segments too long or with too many buckets for one CTA take the general path inside the call.  Also with a slice of the segments, as ``Memory.query(head_range=...)`` passes them."""
     g = torch.Generator().manual_seed(n_seg * 1000 + C)
     seg_rows = [rows + 37 * s for s in range(n_seg)]
     seg_c = [C + 5 * s for s in range(n_seg)]
